@@ -1,0 +1,188 @@
+// C ABI of libflagrot_kernels.so (ABI 9): the entry points, argument orders and return codes of the reference's
+// integrations/vllm_flagrot/csrc/flagrot_capi.cu, implemented on the sm_100a kernels of this directory.
+// Declarations with the reference citation of every entry: include/flagrot_kernels.h.
+//
+// Conventions (as the reference): raw device pointers, element strides, the caller's cudaStream_t as void*; every
+// launch is asynchronous and allocation-free; 0 = ok, -1 launch error, -2 shared memory, -3 unsupported variant,
+// -4 unknown format / kind, -5 page size, -8 head dim.  Formats built here: int4a (5), int2a (8), konlya (7 / kind 10),
+// konlya2 (9 / kind 11); the symmetric INT4 formats and the ablation codebooks answer -4.
+#include <cstdint>
+#include <cuda_runtime.h>
+
+#include "fr_kernels.h"
+#include "../../include/flagrot_kernels.h"
+
+namespace {
+enum { FMT_INT4 = 4, FMT_INT4A = 5, FMT_KONLY = 6, FMT_KONLYA = 7, FMT_INT2A = 8, FMT_KONLYA2 = 9 };
+enum { KIND_KONLYA = 10, KIND_KONLYA2 = 11 };
+constexpr int VAR_HD256 = 4096;
+
+bool fmt_info(int fmt, int& nb, int& ko) {
+  switch (fmt) {
+    case FMT_INT4A: nb = 4; ko = 0; return true;
+    case FMT_INT2A: nb = 2; ko = 0; return true;
+    case FMT_KONLYA: nb = 4; ko = 1; return true;
+    case FMT_KONLYA2: nb = 2; ko = 1; return true;
+    default: return false;
+  }
+}
+bool kind_info(int kind, int& nb) {
+  if (kind == KIND_KONLYA) { nb = 4; return true; }
+  if (kind == KIND_KONLYA2) { nb = 2; return true; }
+  return false;
+}
+int attn_common(int nb, int ko, const void* q, long long q_bs, const uint8_t* pool, const int* block_table, int bt_stride,
+                const int* seq_lens, int B, int Hkv, int G, int page, int nsplit, int chunk, float qscale,
+                const uint8_t* kmask, const uint8_t* vmask, const uint8_t* vmask_tail, float* opart, float* mlpart,
+                int* counter, void* out, long long o_bs, const void* tail, const int* tail_len, const int* tail_idx,
+                long long tail_bs, long long tail_ts, void* stream, int kv_start, float* part_out) {
+  fr::DecodeParams p{};
+  p.q = q; p.q_bs = q_bs; p.pool = pool; p.block_table = block_table; p.bt_stride = bt_stride; p.seq_lens = seq_lens;
+  p.B = B; p.Hkv = Hkv; p.G = G; p.page = page; p.nsplit = nsplit; p.chunk = chunk; p.qscale = qscale;
+  p.kmask = kmask; p.vmask = vmask; p.vmask_tail = vmask_tail;
+  p.opart = opart; p.mlpart = mlpart; p.counter = counter; p.out = out; p.o_bs = o_bs;
+  p.tail = tail; p.tail_len = tail_len; p.tail_idx = tail_idx; p.tail_bs = tail_bs; p.tail_ts = tail_ts;
+  p.kv_start = kv_start; p.nb = nb; p.key_only = ko; p.part_out = part_out;
+  return fr::decode_launch(p, static_cast<cudaStream_t>(stream));
+}
+}  // namespace
+
+extern "C" {
+
+int fr_abi_version() { return 9; }
+
+int fr_v2_attn(int fmt, const void* q, long long q_bs, const uint8_t* pool, const int* block_table, int bt_stride,
+               const int* seq_lens, int B, int Hkv, int page, int nsplit, int chunk, float qscale,
+               const uint8_t* kmask, const uint8_t* vmask, int rb, int qrot, int vrot, int variant, int stages,
+               float* opart, float* mlpart, int* counter, void* out, long long o_bs, const void* tail,
+               const int* tail_len, const int* tail_idx, long long tail_bs, long long tail_ts, void* stream, int gqa,
+               int kv_start) {
+  (void)stages;
+  int nb, ko;
+  if (!fmt_info(fmt, nb, ko)) return -4;
+  if (variant & VAR_HD256) return -8;
+  const uint8_t* km = (!ko && qrot) ? kmask : nullptr;
+  const uint8_t* vm = (!ko && vrot) ? vmask : nullptr;
+  const uint8_t* vt = (!ko && (vrot || tail != nullptr)) ? vmask : nullptr;
+  if ((km || vm || vt) && rb != 32) return -3;
+  return attn_common(nb, ko, q, q_bs, pool, block_table, bt_stride, seq_lens, B, Hkv, gqa > 0 ? gqa : 4, page, nsplit,
+                     chunk, qscale, km, vm, vt, opart, mlpart, counter, out, o_bs, tail, tail_len, tail_idx, tail_bs,
+                     tail_ts, stream, kv_start, nullptr);
+}
+
+int fr_v2_write(int fmt, const void* kv, long long kv_ts, const long long* slots, int T, int Hkv, int page,
+                const uint8_t* mask, int rb, uint8_t* pool, void* stream, int hd, const float* kmu) {
+  if (T <= 0) return 0;
+  if (hd != 0 && hd != 128) return -8;
+  if (fmt != FMT_INT4A && fmt != FMT_INT2A) return -4;
+  if (page != 16 && page != 32) return -5;
+  if (mask != nullptr && rb != 32) return -3;
+  return fr::rows_launch(fmt == FMT_INT4A ? 4 : 2, kv, kv_ts, slots, 0, T, Hkv, page, mask, nullptr, kmu, pool, 0, 2 * Hkv, 0,
+                         static_cast<cudaStream_t>(stream));
+}
+
+int fr_v2_occupancy(int fmt, int variant, int stages, int page) {
+  (void)variant; (void)stages; (void)page;
+  int nb, ko;
+  if (!fmt_info(fmt, nb, ko)) return 0;
+  return fr::decode_occupancy(nb, ko);
+}
+int fr_v2_chunk_bytes(int fmt, int page) { return page * ((fmt == FMT_INT2A || fmt == FMT_KONLYA2) ? 80 : 144); }
+
+int fr_cb_nsg() { return 15; }
+
+int fr_cb_write(const void* kv, long long kv_ts, const long long* slots, int slot_ph, int T, int Hkv, int page, int tg,
+                const float* CT, const float* co, const unsigned* sg, int kind, uint8_t* pool, void* stream, int hd,
+                const float* kmu) {
+  (void)tg; (void)co; (void)sg;
+  if (T <= 0) return 0;
+  if (hd != 0 && hd != 128) return -8;
+  int nb;
+  if (!kind_info(kind, nb)) return -4;
+  if (page != 16 && page != 32) return -5;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int rc = fr::dyn_keys_launch(nb, kv, kv_ts, slots, slot_ph, T, Hkv, page, CT, kmu, pool, st);
+  if (rc) return rc;
+  return fr::rows_launch(nb, kv, kv_ts, slots, slot_ph, T, Hkv, page, nullptr, nullptr, nullptr, pool, Hkv, Hkv, 1, st);
+}
+
+int fr_cb_write3(const void* kv, long long kv_ts, const long long* slots, int slot_ph, int T, int Hkv, int page,
+                 const float* CT, const float* co, const void* C1, const float* beta, const unsigned* sg, int kind,
+                 uint8_t* pool, int nchunk, int nchunk_v, void* stream, const float* kmu) {
+  (void)co; (void)C1; (void)beta; (void)sg;   // C1 / beta are the reference's ranking tables: the bytes do not depend on them
+  if (T <= 0) return 0;
+  int nb;
+  if (!kind_info(kind, nb)) return -4;
+  if (page != 16 && page != 32) return -5;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (nchunk >= 0) {
+    const int rc = fr::dyn_keys_launch(nb, kv, kv_ts, slots, slot_ph, T, Hkv, page, CT, kmu, pool, st);
+    if (rc) return rc;
+  }
+  if (nchunk_v >= 0)
+    return fr::rows_launch(nb, kv, kv_ts, slots, slot_ph, T, Hkv, page, nullptr, nullptr, nullptr, pool, Hkv, Hkv, 1, st);
+  return 0;
+}
+
+int fr_w3_static_write(const void* kv, long long kv_ts, const long long* slots, int T, int Hkv, int page,
+                       const uint8_t* mask, const uint8_t* hfull, int asym, uint8_t* pool, int path, void* stream,
+                       const float* kmu) {
+  (void)path;
+  if (T <= 0) return 0;
+  if (asym != 1 && asym != 2) return -4;
+  if (page != 16 && page != 32) return -5;
+  return fr::rows_launch(asym == 1 ? 4 : 2, kv, kv_ts, slots, 0, T, Hkv, page, mask, hfull, kmu, pool, 0, 2 * Hkv, 0,
+                         static_cast<cudaStream_t>(stream));
+}
+
+int fr_cb_attn(const void* q, long long q_bs, const uint8_t* pool, const int* block_table, int bt_stride,
+               const int* seq_lens, int B, int Hkv, int page, int nsplit, int chunk, float qscale, const unsigned* sg,
+               int kind, int variant, int stages, float* opart, float* mlpart, int* counter, void* out, long long o_bs,
+               const void* tail, const int* tail_len, const int* tail_idx, long long tail_bs, long long tail_ts,
+               void* stream, int kv_start) {
+  (void)sg; (void)variant; (void)stages;
+  int nb;
+  if (!kind_info(kind, nb)) return -4;
+  return attn_common(nb, 1, q, q_bs, pool, block_table, bt_stride, seq_lens, B, Hkv, 4, page, nsplit, chunk, qscale,
+                     nullptr, nullptr, nullptr, opart, mlpart, counter, out, o_bs, tail, tail_len, tail_idx, tail_bs,
+                     tail_ts, stream, kv_start, nullptr);
+}
+
+int fr_cb_occupancy(int kind, int variant, int stages, int page) {
+  (void)variant; (void)stages; (void)page;
+  int nb;
+  if (!kind_info(kind, nb)) return 0;
+  return fr::decode_occupancy(nb, 1);
+}
+int fr_cb_chunk_bytes(int kind, int page) { return page * (kind == KIND_KONLYA2 ? 80 : 144); }
+int fr_cb_write_smem(int kind, int tg, int hd) {
+  (void)kind; (void)hd;
+  const int t = tg < 1 ? 1 : (tg > 4 ? 4 : tg);
+  return t * (128 * 4 + 2 * 128 * 4 * 2 + 2 * 128 + 2 * 4 * 2 + 2 * 4);   // static shared memory of the key writer
+}
+
+const char* fr_last_error() { return cudaGetErrorString(cudaGetLastError()); }
+
+int fr_head_fwht(const void* x, long long x_ts, void* out, long long o_ts, int T, int H, const uint8_t* flags,
+                 float scale, void* stream, int D) {
+  if (T <= 0) return 0;
+  if (D != 128) return -8;
+  return fr::head_fwht_launch(x, x_ts, out, o_ts, T, H, flags, scale, static_cast<cudaStream_t>(stream));
+}
+
+// ---- extensions (no counterpart in the reference ABI)
+int fr_attn_partial(int fmt, const void* q, long long q_bs, const uint8_t* pool, const int* block_table, int bt_stride,
+                    const int* seq_lens, int B, int Hkv, int page, int nsplit, int chunk, float qscale,
+                    const uint8_t* kmask, const uint8_t* vmask, float* opart, float* mlpart, int* counter, float* part,
+                    const void* tail, const int* tail_len, const int* tail_idx, long long tail_bs, long long tail_ts,
+                    void* stream, int gqa, int kv_start) {
+  int nb, ko;
+  if (!fmt_info(fmt, nb, ko)) return -4;
+  return attn_common(nb, ko, q, q_bs, pool, block_table, bt_stride, seq_lens, B, Hkv, gqa > 0 ? gqa : 4, page, nsplit, chunk,
+                     qscale, ko ? nullptr : kmask, ko ? nullptr : vmask, ko ? nullptr : vmask, opart, mlpart, counter,
+                     nullptr, 0, tail, tail_len, tail_idx, tail_bs, tail_ts, stream, kv_start, part);
+}
+
+int fr_device_status() { return fr::decode_status(); }
+
+}  // extern "C"

@@ -1,0 +1,746 @@
+// Paged split-KV GQA decode attention over INT4 / INT2 FlagRot pages for sm_100a.
+//
+// Replaces the reference kernels k_attn2 / k_attn2g (kernels/csrc/attn_decode_v2.cu:687, attn_decode_v2g.cuh:276), k_cbk
+// (kernels/csrc/attn_codebook_attn.cuh:2126), the BF16 window kernels k_tail_* (attn_tail.cuh) and the in-kernel split
+// merge (attn_merge.cuh) for the formats int4a / int2a (static block flags) and konlya / konlya2 (per-token flags in the
+// scale sign bits).  Same pages, same workspace contract, one launch.
+//
+// Design (B200): the path is HBM-bound, but 2.5 - 4.5-bit cells carry more multiply-accumulates per byte than the FP32
+// lanes of an SM can retire at HBM speed, so the dot products run on the integer tensor path (mma.sync m16n8k32
+// u8 x s8 -> s32) directly on the packed codes; everything that touches a scale, a flag or the softmax stays on the
+// CUDA cores.
+//   * grid (Hkv * ceil(G / 4), nsplit [+ 1 window CTA], B), 128 threads; a CTA serves 4 q heads of one kv head;
+//   * each warp owns every 4th 32-token block (two pages) of the split and a private ring of bulk-copy stages:
+//     lane 0 issues one cp.async.bulk per page (one contiguous 2304 / 1280-byte chunk) completing on the stage's
+//     mbarrier; waits are bounded and report through a status word instead of spinning forever;
+//   * QK: A = the code bytes as stored (the K row layout is the m16n8k32 A fragment: one 128-bit shared load per
+//     token gives all four groups), B = q in 15-bit fixed point split hi / lo, for key-only pages in three bases
+//     (identity, per-group H32, whole-head H128); per (token, group) the flags select the variant, the zero point is
+//     removed with the matching sum of q, the group scale is applied in fp32;
+//   * PV: P' = p * V-scale is quantised to 14 bits per (token, group) with a running normaliser, transposed through
+//     1 KB of shared memory per warp and multiplied with the V^T code bytes (again the stored bytes are the A
+//     fragment); integer accumulators are folded into fp32 whenever the running maximum or the normaliser moves;
+//   * the 4 warps merge in shared memory; splits merge through the caller's workspace, last arriving CTA wins.
+#include <cmath>
+
+#include "fr_common.cuh"
+#include "fr_kernels.h"
+
+namespace fr {
+
+namespace {
+
+constexpr int NWARP = 4;
+constexpr int BLK = 32;            // tokens per warp step
+constexpr int ST = 3;              // bulk-copy stages per warp
+constexpr int MAXPG = 512;         // pages per split (chunk <= 8192 tokens of 16)
+#define NEG_INF (-INFINITY)
+constexpr int WAIT_LIMIT = 1 << 22;
+
+__device__ int g_status;           // != 0: a bounded wait gave up (value = line of the wait)
+
+FR_DEVI uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+FR_DEVI void mbar_init(uint32_t a, int n) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(a), "r"(n)); }
+FR_DEVI void mbar_expect(uint32_t a, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(a), "r"(bytes) : "memory");
+}
+FR_DEVI void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t mbar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(dst),
+               "l"(src), "r"(bytes), "r"(mbar)
+               : "memory");
+}
+FR_DEVI bool mbar_wait(uint32_t a, uint32_t parity) {  // bounded: false after WAIT_LIMIT probes
+  for (int it = 0; it < WAIT_LIMIT; ++it) {
+    uint32_t ok;
+    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+                 : "=r"(ok)
+                 : "r"(a), "r"(parity)
+                 : "memory");
+    if (ok) return true;
+  }
+  return false;
+}
+FR_DEVI void mma_u8s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+FR_DEVI float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+  return y;
+}
+FR_DEVI uint32_t prmt(uint32_t a, uint32_t b, uint32_t s) {
+  uint32_t r;
+  asm("prmt.b32 %0, %1, %2, %3;\n" : "=r"(r) : "r"(a), "r"(b), "r"(s));
+  return r;
+}
+FR_DEVI float h2f(uint32_t bits16) { return __half2float(__ushort_as_half(static_cast<unsigned short>(bits16))); }
+FR_DEVI float2 h2x2f(uint32_t v) {   // two packed fp16 -> two fp32
+  __half2 h;
+  *reinterpret_cast<uint32_t*>(&h) = v;
+  return __half22float2(h);
+}
+
+template <int NB> struct DLay {
+  static constexpr int P = 16;
+  static constexpr int CHUNK = Lay<NB>::CELL * P;             // 2304 | 1280
+  static constexpr int PG1 = CHUNK + 64;                      // second page of a stage (64-byte skew: bank spread)
+  static constexpr int STAGE = ((PG1 + CHUNK + 127) / 128) * 128;
+  static constexpr int V_OFF = Lay<NB>::CBY * P, KS_OFF = 2 * Lay<NB>::CBY * P, VS_OFF = KS_OFF + 8 * P;
+  static constexpr uint32_t ZM = NB == 4 ? 0xFu : 0x3u;
+};
+constexpr int PBUF_WORDS = 4 * 72;  // P' exchange per warp: [head] stride 72 words (18 x 16 B), [c][hl][e][j]
+
+// shared memory map (dynamic): ring | pbuf | q table | sums | page ids | merge scratch (aliases the ring)
+template <int NB, int NV> struct SMap {
+  static constexpr int RING = 0;
+  static constexpr int RING_BYTES = NWARP * ST * DLay<NB>::STAGE;
+  static constexpr int PBUF = RING + RING_BYTES;
+  static constexpr int QT = PBUF + NWARP * PBUF_WORDS * 4;             // int16 [NV][4][128]
+  static constexpr int SQ = QT + NV * 4 * 128 * 2;                      // int [NV][4][4]
+  static constexpr int SF = SQ + NV * 16 * 4;                           // float [4]
+  static constexpr int PIDX = SF + 16;                                  // int [MAXPG]
+  static constexpr int MBAR = PIDX + MAXPG * 4;                         // u64 [NWARP][ST]
+  static constexpr int TOTAL = MBAR + NWARP * ST * 8;
+  static_assert(RING_BYTES >= NWARP * (4 * 128 + 8) * 4, "merge scratch aliases the ring");
+};
+
+// ------------------------------------------------------------------------------------------------ split merge
+// parts of (row b, kv head, q tile): slots base .. base + n - 1, each [4][128] floats of opart and [4][2] of mlpart.
+// Warp w merges head w: (m, l) of the parts over the lanes, then the float4 rows.
+FR_DEVI void merge_parts(const float* opart, const float* mlpart, int base, int n, int head, int lane, float (&x)[4],
+                         float& Mo, float& Lo) {
+  const float2* ml = reinterpret_cast<const float2*>(mlpart);
+  float M = NEG_INF;
+  for (int s = lane; s < n; s += 32) M = fmaxf(M, __ldcg(&ml[(base + s) * 4 + head]).x);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(FULLMASK, M, o));
+  float l = 0.f;
+  for (int s = lane; s < n; s += 32) {
+    const float2 v = __ldcg(&ml[(base + s) * 4 + head]);
+    l += v.x == NEG_INF ? 0.f : ex2(v.x - M) * v.y;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) l += __shfl_xor_sync(FULLMASK, l, o);
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  const float4* op = reinterpret_cast<const float4*>(opart) + head * 32 + lane;
+  int s = 0;
+  for (; s + 4 <= n; s += 4) {
+    float4 v[4];
+    float wgt[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      v[k] = __ldcg(op + static_cast<size_t>(base + s + k) * 128);
+      const float m = __ldcg(&ml[(base + s + k) * 4 + head]).x;
+      wgt[k] = m == NEG_INF ? 0.f : ex2(m - M);
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      acc.x = fmaf(wgt[k], v[k].x, acc.x); acc.y = fmaf(wgt[k], v[k].y, acc.y);
+      acc.z = fmaf(wgt[k], v[k].z, acc.z); acc.w = fmaf(wgt[k], v[k].w, acc.w);
+    }
+  }
+  for (; s < n; ++s) {
+    const float4 v = __ldcg(op + static_cast<size_t>(base + s) * 128);
+    const float m = __ldcg(&ml[(base + s) * 4 + head]).x;
+    const float wgt = m == NEG_INF ? 0.f : ex2(m - M);
+    acc.x = fmaf(wgt, v.x, acc.x); acc.y = fmaf(wgt, v.y, acc.y); acc.z = fmaf(wgt, v.z, acc.z); acc.w = fmaf(wgt, v.w, acc.w);
+  }
+  x[0] = acc.x; x[1] = acc.y; x[2] = acc.z; x[3] = acc.w;
+  Mo = M; Lo = l;
+}
+
+// orthonormal H32 of the flagged 32-blocks of a row held 4 elements per lane (mask: 4 bytes of this kv head)
+FR_DEVI void rot_blocks(float (&x)[4], const uint8_t* mask, int lane) {
+  if (mask == nullptr) return;
+  const bool rot = mask[lane >> 3] != 0;
+  if (!__any_sync(FULLMASK, rot)) return;
+  float y[4] = {x[0], x[1], x[2], x[3]};
+  fwht_row_stages(y, lane, 32);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) if (rot) x[i] = y[i] * C32;
+}
+
+// final store of head `head` of the CTA's q tile: x = unnormalised row (4 dims per lane), l its denominator
+FR_DEVI void store_row(const DecodeParams& p, int b, int kvh, int qt, int head, int lane, float (&x)[4], float M, float l) {
+  const int g = qt * 4 + head;
+  if (g >= p.G) return;
+  const float rl = l > 0.f ? 1.f / l : 0.f;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) x[i] *= rl;
+  rot_blocks(x, p.vmask ? p.vmask + kvh * 4 : nullptr, lane);      // static formats: back to the original V basis
+  const int hq = kvh * p.G + g;
+  if (p.part_out != nullptr) {   // extension: fp32 row + (m, l) for a merge across devices
+    float* po = p.part_out + (static_cast<size_t>(b) * p.Hkv * p.G + hq) * 130;
+    *reinterpret_cast<float2*>(po + 4 * lane) = make_float2(x[0], x[1]);
+    *reinterpret_cast<float2*>(po + 4 * lane + 2) = make_float2(x[2], x[3]);
+    if (lane == 0) { po[128] = M; po[129] = l; }
+    return;
+  }
+  const __nv_bfloat162 o01 = __floats2bfloat162_rn(x[0], x[1]), o23 = __floats2bfloat162_rn(x[2], x[3]);
+  uint2 ov;
+  ov.x = *reinterpret_cast<const uint32_t*>(&o01);
+  ov.y = *reinterpret_cast<const uint32_t*>(&o23);
+  *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(p.out) + b * p.o_bs + hq * HD + 4 * lane) = ov;
+}
+
+// CTA epilogue.  scr: per warp [4][128] floats o (unnormalised, relative to the warp's m) then [4] m, [4] l.
+// Combines the warps, then either stores the row (single part) or publishes the partial and, as last arriver of the
+// (row, kv head), merges every part of every q tile.
+FR_DEVI void cta_finish(const DecodeParams& p, float* scr, int b, int kvh, int qt, int NT, int part, int nparts, int nsp,
+                        int* last_flag) {
+  const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+  constexpr int WS = 4 * 128 + 8;
+  __syncthreads();
+  // warp w combines head w over the 4 warps
+  float M = NEG_INF;
+#pragma unroll
+  for (int k = 0; k < NWARP; ++k) M = fmaxf(M, scr[k * WS + 512 + w]);
+  float x[4] = {0.f, 0.f, 0.f, 0.f}, l = 0.f;
+#pragma unroll
+  for (int k = 0; k < NWARP; ++k) {
+    const float mk = scr[k * WS + 512 + w];
+    const float wk = mk == NEG_INF ? 0.f : ex2(mk - M);
+    const float4 v = *reinterpret_cast<const float4*>(scr + k * WS + w * 128 + 4 * lane);
+    x[0] = fmaf(wk, v.x, x[0]); x[1] = fmaf(wk, v.y, x[1]); x[2] = fmaf(wk, v.z, x[2]); x[3] = fmaf(wk, v.w, x[3]);
+    l = fmaf(wk, scr[k * WS + 516 + w], l);
+  }
+  if (nparts * NT == 1) {
+    store_row(p, b, kvh, qt, w, lane, x, M, l);
+    return;
+  }
+  const int slot = ((b * p.Hkv + kvh) * NT + qt) * nsp + part;
+  *reinterpret_cast<float4*>(p.opart + static_cast<size_t>(slot) * 512 + w * 128 + 4 * lane) = make_float4(x[0], x[1], x[2], x[3]);
+  if (lane == 0) *reinterpret_cast<float2*>(p.mlpart + slot * 8 + 2 * w) = make_float2(M, l);
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    const int old = atomicAdd(p.counter + b * p.Hkv + kvh, 1);
+    *last_flag = old == nparts * NT - 1;
+  }
+  __syncthreads();
+  if (!*last_flag) return;
+  __threadfence();
+  for (int t = 0; t < NT; ++t) {
+    float y[4], Mo, Lo;
+    merge_parts(p.opart, p.mlpart, ((b * p.Hkv + kvh) * NT + t) * nsp, nparts, w, lane, y, Mo, Lo);
+    store_row(p, b, kvh, t, w, lane, y, Mo, Lo);
+  }
+  if (tid == 0) p.counter[b * p.Hkv + kvh] = 0;
+}
+
+// ------------------------------------------------------------------------------------------------ BF16 window CTA
+// one CTA per (row, kv head, q tile): fp32 softmax over the <= 256 BF16 rows of the row's ring entry; warp w takes
+// tokens w, w + 4, ...; lane = 4 dims.
+FR_DEVI void tail_cta(const DecodeParams& p, float* scr, int b, int kvh, int qt, int tl) {
+  const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+  constexpr int WS = 4 * 128 + 8;
+  const __nv_bfloat16* qb = static_cast<const __nv_bfloat16*>(p.q) + b * p.q_bs + (kvh * p.G + qt * 4) * HD;
+  float q[4][4];
+#pragma unroll
+  for (int g = 0; g < 4; ++g) {
+    uint2 raw = make_uint2(0, 0);
+    if (qt * 4 + g < p.G) raw = *reinterpret_cast<const uint2*>(qb + g * HD + 4 * lane);
+    q[g][0] = bf16_lo(raw.x) * p.qscale; q[g][1] = bf16_hi(raw.x) * p.qscale;
+    q[g][2] = bf16_lo(raw.y) * p.qscale; q[g][3] = bf16_hi(raw.y) * p.qscale;
+  }
+  const __nv_bfloat16* tb = static_cast<const __nv_bfloat16*>(p.tail) + (p.tail_idx ? p.tail_idx[b] : b) * p.tail_bs;
+  const __nv_bfloat16* kr = tb + kvh * HD + 4 * lane;
+  const __nv_bfloat16* vr = tb + (p.Hkv + kvh) * HD + 4 * lane;
+  float m[4], l[4], o[4][4];
+#pragma unroll
+  for (int g = 0; g < 4; ++g) {
+    m[g] = NEG_INF; l[g] = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) o[g][i] = 0.f;
+  }
+  constexpr int U = 4;
+  for (int t0 = w; t0 < tl; t0 += NWARP * U) {
+    uint2 kk[U], vv[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int t = t0 + NWARP * u;
+      kk[u] = t < tl ? __ldg(reinterpret_cast<const uint2*>(kr + t * p.tail_ts)) : make_uint2(0, 0);
+      vv[u] = t < tl ? __ldg(reinterpret_cast<const uint2*>(vr + t * p.tail_ts)) : make_uint2(0, 0);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (t0 + NWARP * u >= tl) break;
+      const float k4[4] = {bf16_lo(kk[u].x), bf16_hi(kk[u].x), bf16_lo(kk[u].y), bf16_hi(kk[u].y)};
+      const float v4[4] = {bf16_lo(vv[u].x), bf16_hi(vv[u].x), bf16_lo(vv[u].y), bf16_hi(vv[u].y)};
+      float s[4];
+#pragma unroll
+      for (int g = 0; g < 4; ++g) s[g] = fmaf(q[g][0], k4[0], fmaf(q[g][1], k4[1], fmaf(q[g][2], k4[2], q[g][3] * k4[3])));
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1)
+#pragma unroll
+        for (int g = 0; g < 4; ++g) s[g] += __shfl_xor_sync(FULLMASK, s[g], off);
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        const float mn = fmaxf(m[g], s[g]);
+        const float a = m[g] == NEG_INF ? 0.f : ex2(m[g] - mn), pr = ex2(s[g] - mn);
+        l[g] = l[g] * a + pr;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) o[g][i] = fmaf(pr, v4[i], o[g][i] * a);
+        m[g] = mn;
+      }
+    }
+  }
+  // static formats with V flags: move the partial into the stored V basis (the final back-rotation serves all parts)
+#pragma unroll
+  for (int g = 0; g < 4; ++g) {
+    rot_blocks(o[g], p.vmask_tail ? p.vmask_tail + kvh * 4 : nullptr, lane);
+    *reinterpret_cast<float4*>(scr + w * WS + g * 128 + 4 * lane) = make_float4(o[g][0], o[g][1], o[g][2], o[g][3]);
+    if (lane == 0) { scr[w * WS + 512 + g] = m[g]; scr[w * WS + 516 + g] = l[g]; }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ q prologue
+// warp g prepares q head g of the tile (row mapping): the NV variants in fixed point, their per-group sums, the scale.
+template <int NV>
+FR_DEVI void q_prologue(const DecodeParams& p, int b, int kvh, int qt, int16_t* qtab, int* sq, float* sf) {
+  const int lane = threadIdx.x & 31, g = threadIdx.x >> 5;
+  const __nv_bfloat16* qb = static_cast<const __nv_bfloat16*>(p.q) + b * p.q_bs + (kvh * p.G + qt * 4 + g) * HD;
+  uint2 raw = make_uint2(0, 0);
+  if (qt * 4 + g < p.G) raw = *reinterpret_cast<const uint2*>(qb + 4 * lane);
+  float v[NV][4];
+  v[0][0] = bf16_lo(raw.x); v[0][1] = bf16_hi(raw.x); v[0][2] = bf16_lo(raw.y); v[0][3] = bf16_hi(raw.y);
+  if constexpr (NV == 3) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { v[1][i] = v[0][i]; v[2][i] = v[0][i]; }
+    fwht_row_stages(v[1], lane, 32);
+    fwht_row_stages(v[2], lane, 128);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { v[1][i] *= C32; v[2][i] *= C128; }
+  } else {
+    rot_blocks(v[0], p.kmask ? p.kmask + kvh * 4 : nullptr, lane);   // static: q into the stored K basis
+  }
+  float am = 0.f;
+#pragma unroll
+  for (int c = 0; c < NV; ++c)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) am = fmaxf(am, fabsf(v[c][i]));
+  am = warp_max(am);
+  const float step = am > 0.f ? am * (1.0f / 16256.0f) : 1.0f;
+  const float inv = 1.0f / step;
+#pragma unroll
+  for (int c = 0; c < NV; ++c) {
+    int s = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int qi = max(-16256, min(16256, __float2int_rn(v[c][i] * inv)));
+      qtab[(c * 4 + g) * 128 + 4 * lane + i] = static_cast<int16_t>(qi);
+      s += qi;
+    }
+    s += __shfl_xor_sync(FULLMASK, s, 1);
+    s += __shfl_xor_sync(FULLMASK, s, 2);
+    s += __shfl_xor_sync(FULLMASK, s, 4);
+    if ((lane & 7) == 0) sq[(c * 4 + g) * 4 + (lane >> 3)] = s;
+  }
+  if (lane == 0) sf[g] = p.qscale * step;
+}
+
+// ------------------------------------------------------------------------------------------------ the kernel
+template <int NB, bool KO>
+__global__ void __launch_bounds__(128, 3) k_decode(const DecodeParams p) {
+  constexpr int NV = KO ? 3 : 1;
+  using L = DLay<NB>;
+  using S = SMap<NB, NV>;
+  extern __shared__ __align__(128) uint8_t smem[];
+  __shared__ int last_flag;
+  const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5, gid = lane >> 2, tig = lane & 3;
+  const int NT = (p.G + 3) >> 2;
+  const int kvh = blockIdx.x / NT, qt = blockIdx.x % NT, split = blockIdx.y, b = blockIdx.z;
+  const int has_tail = p.tail != nullptr;
+  const int nsp = p.nsplit + has_tail;
+  const int len = p.seq_lens[b];
+  const int ns_b = len > 0 ? min(p.nsplit, max(1, (len + p.chunk - 1) / p.chunk)) : 0;
+  const int nparts = ns_b + has_tail;
+  float* scr = reinterpret_cast<float*>(smem + S::RING);
+  constexpr int WS = 4 * 128 + 8;
+
+  if (split >= p.nsplit) {   // the BF16 window CTA
+    const int tl = min(p.tail_len[b], 256);
+    if (len <= 0 && tl <= 0 && nparts * NT > 1) {
+      // nothing to attend: still publish an empty part so that the tickets add up
+    }
+    tail_cta(p, scr, b, kvh, qt, tl);
+    cta_finish(p, scr, b, kvh, qt, NT, ns_b, nparts, nsp, &last_flag);
+    return;
+  }
+  if (split >= ns_b) return;
+
+  const int c0 = split * p.chunk, c1 = min(len, c0 + p.chunk);
+  const int lo = max(c0, p.kv_start);                                 // first attended token
+  const int ntok = c1 - c0, nblk = (ntok + BLK - 1) / BLK;
+  int16_t* qtab = reinterpret_cast<int16_t*>(smem + S::QT);
+  int* sqs = reinterpret_cast<int*>(smem + S::SQ);
+  float* sfs = reinterpret_cast<float*>(smem + S::SF);
+  int* pidx = reinterpret_cast<int*>(smem + S::PIDX);
+  uint64_t* mbar = reinterpret_cast<uint64_t*>(smem + S::MBAR);
+
+  if (lane == 0) {
+#pragma unroll
+    for (int s = 0; s < ST; ++s) mbar_init(smem_u32(&mbar[w * ST + s]), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  {
+    const int* bt = p.block_table + static_cast<size_t>(b) * p.bt_stride + c0 / L::P;
+    const int npg = (ntok + L::P - 1) / L::P;
+    for (int i = tid; i < npg && i < MAXPG; i += 128) pidx[i] = __ldg(bt + i);
+  }
+  q_prologue<NV>(p, b, kvh, qt, qtab, sqs, sfs);
+  __syncthreads();
+
+  const uint8_t* poolh = p.pool + static_cast<size_t>(kvh) * L::CHUNK;
+  const size_t pstride = static_cast<size_t>(p.Hkv) * L::CHUNK;
+  const uint32_t ring = smem_u32(smem + S::RING) + w * ST * L::STAGE;
+  const uint32_t mb0 = smem_u32(&mbar[w * ST]);
+  // block n of this warp = CTA block w + 4 n
+  const int nmine = nblk > w ? (nblk - w + NWARP - 1) / NWARP : 0;
+  auto issue = [&](int n) {
+    const int blk = w + NWARP * n, s = n % ST;
+    const int t0 = blk * BLK;
+    const int npages = (ntok - t0) > L::P ? 2 : 1;
+    mbar_expect(mb0 + 8 * s, npages * L::CHUNK);
+    bulk_g2s(ring + s * L::STAGE, poolh + static_cast<size_t>(pidx[2 * blk]) * pstride, L::CHUNK, mb0 + 8 * s);
+    if (npages == 2)
+      bulk_g2s(ring + s * L::STAGE + L::PG1, poolh + static_cast<size_t>(pidx[2 * blk + 1]) * pstride, L::CHUNK, mb0 + 8 * s);
+  };
+  if (lane == 0)
+    for (int n = 0; n < ST - 1 && n < nmine; ++n) issue(n);
+
+  // ---- per-thread constants
+  // q B fragments: column gid = (head gid >> 1, part gid & 1: hi / lo); k = 4 tig .. (b0), 16 + 4 tig .. (b1)
+  uint32_t qf[NV][4][2];
+  int SQ[NV][4];
+  {
+    const int hd = gid >> 1, lo_part = gid & 1;
+#pragma unroll
+    for (int c = 0; c < NV; ++c)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+          uint32_t word = 0;
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const int qi = qtab[(c * 4 + hd) * 128 + 32 * j + 16 * r + 4 * tig + k];
+            const int hi = (qi + 64) >> 7, lw = qi - (hi << 7);
+            word |= static_cast<uint32_t>((lo_part ? lw : hi) & 0xFF) << (8 * k);
+          }
+          qf[c][j][r] = word;
+        }
+        SQ[c][j] = sqs[(c * 4 + tig) * 4 + j];
+      }
+  }
+  const float sfac = sfs[tig];
+  // tokens of this lane inside a block: tau_i = 8 c + 2 i + e, (c, e) = (gid >> 1, gid & 1)
+  const int tc = gid >> 1, te = gid & 1;
+  const int tpage = tc >> 1;                                           // page of the block holding the lane's tokens
+  const uint32_t tpoff = tpage * L::PG1;
+  const int tpos0 = 8 * (tc & 1) + te;                                 // position in the page of token i = 0 (+ 2 i)
+  // P' exchange buffer
+  uint32_t* pbuf = reinterpret_cast<uint32_t*>(smem + S::PBUF) + w * PBUF_WORDS;
+  uint32_t* pw_dst = pbuf + tig * 72 + tc * 16 + te * 4;               // + hl * 8, 4 words (j)
+  const uint32_t* pw_src = pbuf + (gid >> 1) * 72 + tig * 16 + (gid & 1) * 8;   // 8 words: [e][j]
+
+  // ---- running state (head tig)
+  float m_run = NEG_INF, l_run = 0.f;
+  float nmax = 0.f, nrm = 0.f, inrm = 0.f;      // normaliser of P': P~ = rint(p * sv * nrm), nrm = 2^14 / nmax
+  int Oi[2][4][4];                               // [m][w][frag] integer PV accumulators
+  float Of[2][4][2];                             // folded fp32 accumulators, rows gid / gid + 8 of tile (m, w), head tig
+  int Zi[4];
+  float Zf[4];
+#pragma unroll
+  for (int a = 0; a < 2; ++a)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+#pragma unroll
+      for (int k = 0; k < 4; ++k) Oi[a][c][k] = 0;
+      Of[a][c][0] = Of[a][c][1] = 0.f;
+    }
+#pragma unroll
+  for (int j = 0; j < 4; ++j) { Zi[j] = 0; Zf[j] = 0.f; }
+
+  auto fold = [&](float alpha) {   // integer accumulators -> fp32 (scaled by inrm), then everything times alpha
+#pragma unroll
+    for (int a = 0; a < 2; ++a)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        Of[a][c][0] = (Of[a][c][0] + static_cast<float>(Oi[a][c][0] * 256 + Oi[a][c][1]) * inrm) * alpha;
+        Of[a][c][1] = (Of[a][c][1] + static_cast<float>(Oi[a][c][2] * 256 + Oi[a][c][3]) * inrm) * alpha;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) Oi[a][c][k] = 0;
+      }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      Zf[j] = (Zf[j] + static_cast<float>(Zi[j]) * inrm) * alpha;
+      Zi[j] = 0;
+    }
+    l_run *= alpha;
+  };
+
+  bool wait_ok = true;
+  for (int n = 0; n < nmine; ++n) {
+    const int blk = w + NWARP * n, s = n % ST;
+    __syncwarp();
+    if (lane == 0 && n + ST - 1 < nmine) issue(n + ST - 1);
+    if (!mbar_wait(mb0 + 8 * s, (n / ST) & 1)) { wait_ok = false; }
+    const uint8_t* st = smem + S::RING + (w * ST + s) * L::STAGE;
+    const int tok0 = c0 + blk * BLK;                                   // absolute position of the block's token 0
+    const bool partial = tok0 < lo || tok0 + BLK > c1;
+
+    // ---- scale words of the lane's 4 tokens: K (4 groups per token), V (4 tokens per group)
+    uint32_t ksw[4][2], vsw[4][2];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint2 t = *reinterpret_cast<const uint2*>(st + tpoff + L::KS_OFF + 8 * (tpos0 + 2 * i));
+      ksw[i][0] = t.x; ksw[i][1] = t.y;
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const uint2 t = *reinterpret_cast<const uint2*>(st + tpoff + L::VS_OFF + 2 * (j * L::P + 8 * (tc & 1) + 4 * te));
+      vsw[j][0] = t.x; vsw[j][1] = t.y;                                // tokens i = 0, 1 | 2, 3
+    }
+    bool valid[4] = {true, true, true, true};
+    if (partial) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int pos = tok0 + 8 * tc + 2 * i + te;
+        valid[i] = pos >= lo && pos < c1;
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {   // garbage beyond the sequence must not reach the normaliser / P'
+        if (!valid[0]) vsw[j][0] &= 0xFFFF0000u;
+        if (!valid[1]) vsw[j][0] &= 0x0000FFFFu;
+        if (!valid[2]) vsw[j][1] &= 0xFFFF0000u;
+        if (!valid[3]) vsw[j][1] &= 0x0000FFFFu;
+      }
+    }
+    // ---- QK
+    float sc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      uint32_t ka[2][4];   // code words of rows i = 2 u, 2 u + 1: INT4 4 words (group j), INT2 2 words (groups 2 jp, 2 jp + 1)
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        const int pos = tpos0 + 2 * (2 * u + r);
+        if (NB == 4) {
+          const uint4 t = *reinterpret_cast<const uint4*>(st + tpoff + 64 * pos + 16 * tig);
+          ka[r][0] = t.x; ka[r][1] = t.y; ka[r][2] = t.z; ka[r][3] = t.w;
+        } else {
+          const uint2 t = *reinterpret_cast<const uint2*>(st + tpoff + 32 * (pos ^ ((pos >> 1) & 2)) + 8 * tig);
+          ka[r][0] = t.x; ka[r][1] = t.y; ka[r][2] = 0; ka[r][3] = 0;
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        uint32_t a0, a1, a2, a3;
+        if (NB == 4) {
+          a0 = ka[0][j] & 0x0F0F0F0Fu; a2 = (ka[0][j] >> 4) & 0x0F0F0F0Fu;
+          a1 = ka[1][j] & 0x0F0F0F0Fu; a3 = (ka[1][j] >> 4) & 0x0F0F0F0Fu;
+        } else {
+          const int sh = 4 * (j & 1);
+          a0 = (ka[0][j >> 1] >> sh) & 0x03030303u; a2 = (ka[0][j >> 1] >> (sh + 2)) & 0x03030303u;
+          a1 = (ka[1][j >> 1] >> sh) & 0x03030303u; a3 = (ka[1][j >> 1] >> (sh + 2)) & 0x03030303u;
+        }
+        int acc[NV][4];
+#pragma unroll
+        for (int c = 0; c < NV; ++c) {
+          acc[c][0] = acc[c][1] = acc[c][2] = acc[c][3] = 0;
+          mma_u8s8(acc[c], a0, a1, a2, a3, qf[c][j][0], qf[c][j][1]);
+        }
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+          const int i = 2 * u + r;
+          const uint32_t kw = (ksw[i][j >> 1] >> (16 * (j & 1))) & 0xFFFFu;
+          int hi = acc[0][2 * r], lw = acc[0][2 * r + 1], sq = SQ[0][j];
+          if constexpr (KO) {
+            const bool hfl = (kw & 0x8000u) != 0;
+            const bool ffl = ((vsw[0][i >> 1] >> (16 * (i & 1))) & 0x8000u) != 0;
+            hi = ffl ? acc[NV - 1][2 * r] : (hfl ? acc[NV > 1 ? 1 : 0][2 * r] : hi);
+            lw = ffl ? acc[NV - 1][2 * r + 1] : (hfl ? acc[NV > 1 ? 1 : 0][2 * r + 1] : lw);
+            sq = ffl ? SQ[NV - 1][j] : (hfl ? SQ[NV > 1 ? 1 : 0][j] : sq);
+          }
+          const int val = hi * 128 + lw - static_cast<int>(kw & L::ZM) * sq;
+          sc[i] = fmaf(h2f(kw & 0x7FFFu), static_cast<float>(val), sc[i]);
+        }
+      }
+    }
+    // ---- softmax step (head tig; the 8 lanes of a column hold the block's 32 tokens)
+    float bm = NEG_INF;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      sc[i] = valid[i] ? sc[i] * sfac : NEG_INF;
+      bm = fmaxf(bm, sc[i]);
+    }
+    bm = fmaxf(bm, __shfl_xor_sync(FULLMASK, bm, 4));
+    bm = fmaxf(bm, __shfl_xor_sync(FULLMASK, bm, 8));
+    bm = fmaxf(bm, __shfl_xor_sync(FULLMASK, bm, 16));
+    // largest V scale of the lane's tokens (fp16 order = integer order of the 15-bit patterns)
+    uint32_t vm = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const uint32_t a = vsw[j][0] & 0x7FFF7FFFu, c = vsw[j][1] & 0x7FFF7FFFu;
+      vm = max(vm, max(max(a & 0xFFFFu, a >> 16), max(c & 0xFFFFu, c >> 16)));
+    }
+    const float vmax = h2f(vm);
+    if (__any_sync(FULLMASK, bm > m_run || vmax > nmax)) {
+      float wmax = vmax;
+      wmax = fmaxf(wmax, __shfl_xor_sync(FULLMASK, wmax, 4));
+      wmax = fmaxf(wmax, __shfl_xor_sync(FULLMASK, wmax, 8));
+      wmax = fmaxf(wmax, __shfl_xor_sync(FULLMASK, wmax, 16));
+      const float mn = fmaxf(m_run, bm);
+      const float alpha = (m_run == NEG_INF || mn == m_run) ? (m_run == NEG_INF ? 0.f : 1.f) : ex2(m_run - mn);
+      fold(alpha);
+      m_run = mn;
+      if (wmax > nmax) {
+        nmax = 2.f * wmax;
+        nrm = 16384.f / nmax;
+        inrm = nmax * (1.0f / 16384.f);
+      }
+    }
+    const float msafe = m_run == NEG_INF ? 0.f : m_run;
+    float pn[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float pr = ex2(sc[i] - msafe);
+      l_run += pr;
+      pn[i] = pr * nrm;
+    }
+    // ---- P~ per (token, group): 14-bit fixed point, transposed through shared memory into the PV B fragments
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      uint32_t x01, x23;
+      {
+        const float2 s01 = h2x2f(vsw[j][0] & 0x7FFF7FFFu), s23 = h2x2f(vsw[j][1] & 0x7FFF7FFFu);
+        const uint32_t t0 = __float_as_uint(fmaf(pn[0], s01.x, 8388608.f)), t1 = __float_as_uint(fmaf(pn[1], s01.y, 8388608.f));
+        const uint32_t t2 = __float_as_uint(fmaf(pn[2], s23.x, 8388608.f)), t3 = __float_as_uint(fmaf(pn[3], s23.y, 8388608.f));
+        x01 = prmt(t0, t1, 0x5410u);
+        x23 = prmt(t2, t3, 0x5410u);
+      }
+      // zero-point sums with the same integers the tensor path sees
+      const uint32_t z01 = vsw[j][0] & (L::ZM | (L::ZM << 16)), z23 = vsw[j][1] & (L::ZM | (L::ZM << 16));
+      Zi[j] += static_cast<int>((x01 & 0xFFFFu) * (z01 & 0xFFFFu) + (x01 >> 16) * (z01 >> 16) +
+                                (x23 & 0xFFFFu) * (z23 & 0xFFFFu) + (x23 >> 16) * (z23 >> 16));
+      const uint32_t y01 = x01 + 0x00800080u, y23 = x23 + 0x00800080u;   // P~ = 256 hi + lo, lo in [-128, 127]
+      const uint32_t hiw = prmt(y01, y23, 0x7531u);
+      const uint32_t low = prmt(y01, y23, 0x6420u) ^ 0x80808080u;
+      pw_dst[j] = hiw;
+      pw_dst[8 + j] = low;
+    }
+    __syncwarp();
+    uint32_t pb[2][4];   // [e][j] of this lane's column (head gid >> 1, part gid & 1), tokens of chunk tig
+    {
+      const uint4 t0 = *reinterpret_cast<const uint4*>(pw_src), t1 = *reinterpret_cast<const uint4*>(pw_src + 4);
+      pb[0][0] = t0.x; pb[0][1] = t0.y; pb[0][2] = t0.z; pb[0][3] = t0.w;
+      pb[1][0] = t1.x; pb[1][1] = t1.y; pb[1][2] = t1.z; pb[1][3] = t1.w;
+    }
+    // ---- PV: A = V^T code bytes of chunk tig (page tig >> 1, c8 = tig & 1), 16 d rows per tile
+    {
+      const uint8_t* vb = st + (tig >> 1) * L::PG1 + L::V_OFF;
+#pragma unroll
+      for (int ww = 0; ww < 4; ++ww) {
+        const int e = (ww * 8 + gid) * (L::P / 8) + (tig & 1);
+        uint32_t vw[4];
+        if (NB == 4) {
+          const uint4 t = *reinterpret_cast<const uint4*>(vb + 16 * e);
+          vw[0] = t.x; vw[1] = t.y; vw[2] = t.z; vw[3] = t.w;
+        } else {
+          const uint2 t = *reinterpret_cast<const uint2*>(vb + 8 * e);
+          vw[0] = t.x; vw[1] = t.y; vw[2] = 0; vw[3] = 0;
+        }
+#pragma unroll
+        for (int mm = 0; mm < 2; ++mm) {
+          uint32_t a0, a1, a2, a3;
+          if (NB == 4) {
+            a0 = vw[2 * mm] & 0x0F0F0F0Fu; a2 = (vw[2 * mm] >> 4) & 0x0F0F0F0Fu;
+            a1 = vw[2 * mm + 1] & 0x0F0F0F0Fu; a3 = (vw[2 * mm + 1] >> 4) & 0x0F0F0F0Fu;
+          } else {
+            a0 = vw[mm] & 0x03030303u; a2 = (vw[mm] >> 2) & 0x03030303u;
+            a1 = (vw[mm] >> 4) & 0x03030303u; a3 = (vw[mm] >> 6) & 0x03030303u;
+          }
+          const int j = 2 * mm + (ww >> 1);
+          mma_u8s8(Oi[mm][ww], a0, a1, a2, a3, pb[0][j], pb[1][j]);
+        }
+      }
+    }
+  }
+  if (!wait_ok && lane == 0) atomicExch(&g_status, __LINE__);
+
+  // ---- warp epilogue: fold, reduce over the column's lanes, remove the zero points, park in shared memory
+  fold(1.f);
+  l_run += __shfl_xor_sync(FULLMASK, l_run, 4);
+  l_run += __shfl_xor_sync(FULLMASK, l_run, 8);
+  l_run += __shfl_xor_sync(FULLMASK, l_run, 16);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    Zf[j] += __shfl_xor_sync(FULLMASK, Zf[j], 4);
+    Zf[j] += __shfl_xor_sync(FULLMASK, Zf[j], 8);
+    Zf[j] += __shfl_xor_sync(FULLMASK, Zf[j], 16);
+  }
+  __syncthreads();   // every warp is done with its ring: the scratch aliases it
+#pragma unroll
+  for (int mm = 0; mm < 2; ++mm)
+#pragma unroll
+    for (int ww = 0; ww < 4; ++ww) {
+      const int j = 2 * mm + (ww >> 1), d = 64 * mm + 16 * ww + gid;
+      scr[w * WS + tig * 128 + d] = Of[mm][ww][0] - Zf[j];
+      scr[w * WS + tig * 128 + d + 8] = Of[mm][ww][1] - Zf[j];
+    }
+  if (gid == 0) { scr[w * WS + 512 + tig] = m_run; scr[w * WS + 516 + tig] = l_run; }
+  cta_finish(p, scr, b, kvh, qt, NT, split, nparts, nsp, &last_flag);
+}
+
+template <int NB, bool KO> int launch_k(const DecodeParams& p, cudaStream_t st) {
+  constexpr int NV = KO ? 3 : 1;
+  constexpr int smem = SMap<NB, NV>::TOTAL;
+  static bool set = false;
+  if (!set) {
+    if (cudaFuncSetAttribute(k_decode<NB, KO>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -2;
+    set = true;
+  }
+  const int NT = (p.G + 3) / 4;
+  const dim3 grid(p.Hkv * NT, p.nsplit + (p.tail != nullptr ? 1 : 0), p.B);
+  k_decode<NB, KO><<<grid, 128, smem, st>>>(p);
+  return cudaPeekAtLastError() == cudaSuccess ? 0 : -1;
+}
+
+}  // namespace
+
+int decode_launch(const DecodeParams& p, cudaStream_t st) {
+  if (p.B <= 0) return 0;
+  if (p.page != 16) return -5;
+  if (p.chunk <= 0 || p.chunk % 64 != 0 || p.chunk > MAXPG * 16 || p.nsplit < 1) return -3;
+  if (p.nb == 4) return p.key_only ? launch_k<4, true>(p, st) : launch_k<4, false>(p, st);
+  return p.key_only ? launch_k<2, true>(p, st) : launch_k<2, false>(p, st);
+}
+
+int decode_occupancy(int nb, int key_only) {
+  int n = 0;
+  cudaError_t e;
+  if (nb == 4 && key_only) {
+    cudaFuncSetAttribute(k_decode<4, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMap<4, 3>::TOTAL);
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, k_decode<4, true>, 128, SMap<4, 3>::TOTAL);
+  } else if (nb == 4) {
+    cudaFuncSetAttribute(k_decode<4, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMap<4, 1>::TOTAL);
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, k_decode<4, false>, 128, SMap<4, 1>::TOTAL);
+  } else if (key_only) {
+    cudaFuncSetAttribute(k_decode<2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMap<2, 3>::TOTAL);
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, k_decode<2, true>, 128, SMap<2, 3>::TOTAL);
+  } else {
+    cudaFuncSetAttribute(k_decode<2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMap<2, 1>::TOTAL);
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, k_decode<2, false>, 128, SMap<2, 1>::TOTAL);
+  }
+  return e == cudaSuccess ? n : 0;
+}
+
+int decode_status() {
+  int v = 0;
+  cudaMemcpyFromSymbol(&v, g_status, sizeof(int));
+  return v;
+}
+
+}  // namespace fr

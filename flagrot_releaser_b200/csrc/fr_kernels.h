@@ -1,0 +1,39 @@
+// Internal launcher declarations shared by the translation units of libflagrot_kernels.so (not part of the C ABI).
+#pragma once
+#include <cstdint>
+#include <cuda_runtime.h>
+
+namespace fr {
+
+int head_fwht_launch(const void* x, long long x_ts, void* out, long long o_ts, int T, int H, const uint8_t* flags,
+                     float scale, cudaStream_t st);
+// rows [row0, row0 + nrow) of every token through the static row writer (nb = 4 | 2 code bits)
+int rows_launch(int nb, const void* kv, long long kv_ts, const long long* slots, int slot_ph, int T, int Hkv, int page,
+                const uint8_t* mask, const uint8_t* hfull, const float* kmu, uint8_t* pool, int row0, int nrow,
+                int shared15, cudaStream_t st);
+int dyn_keys_launch(int nb, const void* kv, long long kv_ts, const long long* slots, int slot_ph, int T, int Hkv, int page,
+                    const float* CT, const float* kmu, uint8_t* pool, cudaStream_t st);
+
+// paged decode attention (fr_decode.cu)
+struct DecodeParams {
+  const void* q; long long q_bs;             // bf16 [B, G * Hkv, 128], row stride in elements
+  const uint8_t* pool;                       // [num_pages, Hkv, chunk]
+  const int* block_table; int bt_stride;     // int32 [B, bt_stride] (stride 0: every row reads row 0)
+  const int* seq_lens;                       // int32 [B]
+  int B, Hkv, G, page, nsplit, chunk;        // nsplit body splits of `chunk` tokens
+  float qscale;                              // softmax scale * log2(e)
+  const uint8_t* kmask; const uint8_t* vmask;  // static formats: [Hkv, 4] block flags or null (q rotation / output back-rotation)
+  const uint8_t* vmask_tail;                 // V flags applied to the BF16 window partial (stored V basis) or null
+  float* opart; float* mlpart; int* counter;
+  void* out; long long o_bs;                 // bf16 [B, G * Hkv * 128]
+  const void* tail; const int* tail_len; const int* tail_idx; long long tail_bs, tail_ts;
+  int kv_start;
+  int nb;                                    // code bits 4 | 2
+  int key_only;                              // 1: per-token flags in the scale sign bits (konlya / konlya2)
+  float* part_out;                           // optional: unmerged (m, l, o) of the whole row (extension entry)
+};
+int decode_launch(const DecodeParams& p, cudaStream_t st);
+int decode_occupancy(int nb, int key_only);
+int decode_status();   // 0, or the source line of a bounded wait that gave up (sticky)
+
+}  // namespace fr

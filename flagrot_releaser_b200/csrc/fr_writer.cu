@@ -1,0 +1,325 @@
+// Paged cache writers for sm_100a: whole-head Hadamard, static writer (block flags, whole-head flags, key centring) and
+// the dynamic key-only 2x2 writer (per 32-vector {I, H32} x per head {base, H128} chosen by the calibrated
+// attention-weighted error; flags in the sign bits of the scale words).
+//
+// Replaces, byte for byte, the reference kernels k_paged_write (kernels/csrc/attn_decode_v2.cu:1717-1881), k_head_fwht
+// (integrations/vllm_flagrot/csrc/flagrot_capi.cu:167-197), k_cb_write (kernels/csrc/attn_codebook.cu:46-361) and the
+// fused v3 writers (kernels/csrc/attn_cb_write3.cuh) for the kinds konlya / konlya2 and the formats int4a / int2a.
+//
+// Structure: two kernels.
+//   k_rows      one warp per (token, K or V row): load 4 bf16 per lane, optional whole-head H128 (+ bf16 rounding),
+//               key centring, per-block H32, group quantizer, scatter into the page.  Used for the static formats
+//               (all rows) and for the value rows of the dynamic kinds.
+//   k_dyn_keys  one CTA of 128 threads per (kv head, TG tokens).  Thread i owns dimension i, so the 32 x 32 and
+//               128 x 128 weighted-error products read C_q^T rows fully coalesced (L1 / L2 resident, 64 KB per head) and
+//               accumulate in the reference's sequential fp32 order; the whole-head candidate is evaluated by one warp
+//               per token in the row mapping.  No tensor cores: the criterion is defined by its fp32 operation order.
+// V^T code words are shared by 8 tokens; a token only ever flips the bits of its own field (fr::put_field), so tokens
+// of one word may be written by different warps, kernels or streams in any order.
+#include "fr_common.cuh"
+#include "fr_kernels.h"
+
+namespace fr {
+
+// ------------------------------------------------------------------------------------------------ whole-head Hadamard
+__global__ void __launch_bounds__(256) k_head_fwht(const __nv_bfloat16* __restrict__ x, long long x_ts,
+                                                   __nv_bfloat16* out, long long o_ts, int T, int H,
+                                                   const uint8_t* __restrict__ flags, float scale) {
+  const long long warp = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (warp >= static_cast<long long>(T) * H) return;
+  const int t = static_cast<int>(warp / H), h = static_cast<int>(warp % H);
+  const uint2 raw = *reinterpret_cast<const uint2*>(x + t * x_ts + h * HD + 4 * lane);
+  uint2 res = raw;
+  if (flags[h]) {
+    float v[4] = {bf16_lo(raw.x), bf16_hi(raw.x), bf16_lo(raw.y), bf16_hi(raw.y)};
+    fwht_row_stages(v, lane, 128);
+    const __nv_bfloat162 r0 = __floats2bfloat162_rn(__fmul_rn(v[0], scale), __fmul_rn(v[1], scale));
+    const __nv_bfloat162 r1 = __floats2bfloat162_rn(__fmul_rn(v[2], scale), __fmul_rn(v[3], scale));
+    res.x = *reinterpret_cast<const uint32_t*>(&r0);
+    res.y = *reinterpret_cast<const uint32_t*>(&r1);
+  }
+  *reinterpret_cast<uint2*>(out + t * o_ts + h * HD + 4 * lane) = res;
+}
+
+// ------------------------------------------------------------------------------------------------ page stores
+// K row of one token from the 128 codes of the row (row mapping: lane l holds d = 4 l .. 4 l + 3)
+template <int NB>
+FR_DEVI void store_k_row(uint8_t* chunk, int P, int pos, int lane, const unsigned (&code)[4], unsigned word) {
+  unsigned cb[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) cb[i] = __shfl_down_sync(FULLMASK, code[i], 4);   // the B elements (d + 16)
+  const int tg = lane & 7, j = lane >> 3;
+  if (NB == 4) {
+    unsigned wd = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) wd |= (code[i] << (8 * i)) | (cb[i] << (8 * i + 4));
+    if (tg < 4) *reinterpret_cast<uint32_t*>(chunk + Lay<4>::krow(pos) + 16 * tg + 4 * j) = wd;
+  } else {
+    unsigned hw = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) hw |= (code[i] << (8 * i)) | (cb[i] << (8 * i + 2));
+    const unsigned hw1 = __shfl_down_sync(FULLMASK, hw, 8);                     // group j + 1
+    if (tg < 4 && !(j & 1)) *reinterpret_cast<uint32_t*>(chunk + Lay<2>::krow(pos) + 8 * tg + 4 * (j >> 1)) = hw | (hw1 << 4);
+  }
+  if (tg == 0) *reinterpret_cast<uint16_t*>(chunk + Lay<NB>::ks_off(P) + 8 * pos + 2 * j) = static_cast<uint16_t>(word);
+}
+
+// V^T codes + V scale of one token (row mapping).  shared15: bit 15 of the group-0 word belongs to the key writer.
+template <int NB>
+FR_DEVI void store_v_row(uint8_t* chunk, int P, int pos, int lane, const unsigned (&code)[4], unsigned word, bool shared15) {
+  const int c8 = pos >> 3, ii = (pos & 7) >> 1, b = pos & 1;
+  const int w = (lane & 15) >> 2, r8 = (lane & 3) >> 1, m = lane >> 4;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int gid = 4 * (lane & 1) + i;
+    const int e = (w * 8 + gid) * (P >> 3) + c8;
+    if (NB == 4) put_field(chunk, Lay<4>::v_off(P) + 16 * e + 4 * (2 * m + r8) + ii, 4 * b, 0xFu, code[i]);
+    else put_field(chunk, Lay<2>::v_off(P) + 8 * e + 4 * m + ii, 4 * r8 + 2 * b, 0x3u, code[i]);
+  }
+  if ((lane & 7) == 0) {
+    const int j = lane >> 3;
+    const int off = Lay<NB>::vs_off(P) + 2 * (j * P + 8 * c8 + vslot8(pos));
+    if (shared15 && j == 0) put_word_low15(chunk, off, word);
+    else *reinterpret_cast<uint16_t*>(chunk + off) = static_cast<uint16_t>(word);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ row writer
+struct RowParams {
+  const __nv_bfloat16* kv; long long kv_ts;
+  const long long* slots; int slot_ph;
+  int T, Hkv, page;
+  const uint8_t* mask;      // [2 Hkv, 4] H32 block flags (K rows first) or null
+  const uint8_t* hfull;     // [2 Hkv] whole-head flags or null
+  const float* kmu;         // [Hkv, 128] or null
+  uint8_t* pool;
+  int row0, nrow;           // rows [row0, row0 + nrow) of the 2 Hkv rows of a token
+  int shared15;
+};
+
+template <int NB>
+__global__ void __launch_bounds__(128) k_rows(const RowParams p) {
+  const int lane = threadIdx.x & 31;
+  const long long item = static_cast<long long>(blockIdx.x) * 4 + (threadIdx.x >> 5);
+  if (item >= static_cast<long long>(p.T) * p.nrow) return;
+  const int t = static_cast<int>(item / p.nrow), hr = p.row0 + static_cast<int>(item % p.nrow);
+  const bool isv = hr >= p.Hkv;
+  const int head = isv ? hr - p.Hkv : hr;
+  const long long slot = p.slot_ph ? p.slots[static_cast<long long>(t) * p.Hkv + head] : p.slots[t];
+  if (slot < 0) return;
+  const int P = p.page;
+  const long long page = slot / P;
+  const int pos = static_cast<int>(slot % P);
+  uint8_t* chunk = p.pool + (page * p.Hkv + head) * static_cast<long long>(Lay<NB>::chunk(P));
+
+  const uint2 raw = *reinterpret_cast<const uint2*>(p.kv + t * p.kv_ts + hr * HD + 4 * lane);
+  float v[4] = {bf16_lo(raw.x), bf16_hi(raw.x), bf16_lo(raw.y), bf16_hi(raw.y)};
+  if (p.hfull != nullptr && p.hfull[hr]) {   // whole-head H128 x / 16, rounded to bf16 once
+    fwht_row_stages(v, lane, 128);
+    const __nv_bfloat162 r0 = __floats2bfloat162_rn(__fmul_rn(v[0], 0.0625f), __fmul_rn(v[1], 0.0625f));
+    const __nv_bfloat162 r1 = __floats2bfloat162_rn(__fmul_rn(v[2], 0.0625f), __fmul_rn(v[3], 0.0625f));
+    const uint32_t a = *reinterpret_cast<const uint32_t*>(&r0), b = *reinterpret_cast<const uint32_t*>(&r1);
+    v[0] = bf16_lo(a); v[1] = bf16_hi(a); v[2] = bf16_lo(b); v[3] = bf16_hi(b);
+  }
+  if (p.kmu != nullptr && !isv) {
+    const float4 m = *reinterpret_cast<const float4*>(p.kmu + hr * HD + 4 * lane);
+    v[0] = __fsub_rn(v[0], m.x); v[1] = __fsub_rn(v[1], m.y); v[2] = __fsub_rn(v[2], m.z); v[3] = __fsub_rn(v[3], m.w);
+  }
+  const bool rot = p.mask != nullptr && p.mask[hr * 4 + (lane >> 3)];
+  {  // H32 of the flagged 32-blocks (the shuffles run on every lane; unflagged groups keep their values)
+    float y[4] = {v[0], v[1], v[2], v[3]};
+    if (p.mask != nullptr && __any_sync(FULLMASK, rot)) {
+      fwht_row_stages(y, lane, 32);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) if (rot) v[i] = __fmul_rn(y[i], C32);
+    }
+  }
+  const float mn = group_min8(fminf(fminf(v[0], v[1]), fminf(v[2], v[3])));
+  const float mx = group_max8(fmaxf(fmaxf(v[0], v[1]), fmaxf(v[2], v[3])));
+  unsigned code[4], word = 0;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) quant_store<NB>(v[i], mn, mx, code[i], word);
+  if (!isv) store_k_row<NB>(chunk, P, pos, lane, code, word);
+  else store_v_row<NB>(chunk, P, pos, lane, code, word, p.shared15 != 0);
+}
+
+// ------------------------------------------------------------------------------------------------ dynamic key writer
+struct DynParams {
+  const __nv_bfloat16* kv; long long kv_ts;
+  const long long* slots; int slot_ph;
+  int T, Hkv, page;
+  const float* CT;          // [Hkv, 128 (k), 128 (i)] = C_q[h][i][k]
+  const float* kmu;
+  uint8_t* pool;
+};
+
+template <int NB, int TG>
+__global__ void __launch_bounds__(128) k_dyn_keys(const DynParams p) {
+  __shared__ float xs[TG][HD];              // centred key rows
+  __shared__ float es[TG][2][HD];           // reconstruction errors of the head candidates (base, F)
+  __shared__ float ps[TG][2][HD];           // e_i * u_i
+  __shared__ uint8_t cs[TG][2][HD];         // stored codes of the head candidates
+  __shared__ uint16_t ws[TG][2][4];         // stored scale words (base: with the H32 flag)
+  __shared__ float herr[TG][2];
+  const int i = threadIdx.x, lane = i & 31, j = i >> 5;
+  const int h = blockIdx.x, t0 = blockIdx.y * TG;
+  const int ntok = min(TG, p.T - t0);
+  const float* __restrict__ CT = p.CT + static_cast<size_t>(h) * HD * HD;
+
+  // ---- A1: local candidates I / H32 of 32-vector j (dim mapping), block-diagonal weighted error, first argmin
+#pragma unroll
+  for (int t = 0; t < TG; ++t) {
+    if (t >= ntok) break;
+    float z = __bfloat162float(p.kv[(t0 + t) * p.kv_ts + h * HD + i]);
+    if (p.kmu != nullptr) z = __fsub_rn(z, __ldg(p.kmu + h * HD + i));
+    xs[t][i] = z;
+    const float y1 = fwht32_lane(z, lane);
+    const float mn0 = warp_min(z), mx0 = warp_max(z), mn1 = warp_min(y1), mx1 = warp_max(y1);
+    const float e0 = __fsub_rn(quant_err_deq<NB>(z, mn0, mx0), z);
+    const float e1 = __fsub_rn(fwht32_lane(quant_err_deq<NB>(y1, mn1, mx1), lane), z);
+    float u0 = 0.f, u1 = 0.f;
+#pragma unroll 8
+    for (int k = 0; k < 32; ++k) {
+      const float cv = __ldg(CT + (32 * j + k) * HD + i);                  // C[i][32 j + k]
+      const float p0 = __fmul_rn(cv, __shfl_sync(FULLMASK, e0, k));
+      const float p1 = __fmul_rn(cv, __shfl_sync(FULLMASK, e1, k));
+      u0 = k == 0 ? p0 : __fadd_rn(u0, p0);
+      u1 = k == 0 ? p1 : __fadd_rn(u1, p1);
+    }
+    const float err0 = tree32(__fmul_rn(e0, u0)), err1 = tree32(__fmul_rn(e1, u1));
+    const bool ch = err1 < err0;
+    unsigned code, word;
+    quant_store<NB>(ch ? y1 : z, ch ? mn1 : mn0, ch ? mx1 : mx0, code, word);
+    es[t][0][i] = ch ? e1 : e0;
+    cs[t][0][i] = static_cast<uint8_t>(code);
+    if (lane == 0) ws[t][0][j] = static_cast<uint16_t>(word | (ch ? 0x8000u : 0u));
+  }
+  __syncthreads();
+  // ---- A2: whole-head candidate F = H128 (row mapping, warp j = token j)
+  if (j < ntok) {
+    const int t = j;
+    float x[4], y[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) { x[k] = xs[t][4 * lane + k]; y[k] = x[k]; }
+    fwht_row_stages(y, lane, 128);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) y[k] = __fmul_rn(y[k], C128);
+    const float mn = group_min8(fminf(fminf(y[0], y[1]), fminf(y[2], y[3])));
+    const float mx = group_max8(fmaxf(fmaxf(y[0], y[1]), fmaxf(y[2], y[3])));
+    float d[4];
+    unsigned word = 0;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      unsigned code;
+      d[k] = quant_err_deq<NB>(y[k], mn, mx);
+      quant_store<NB>(y[k], mn, mx, code, word);
+      cs[t][1][4 * lane + k] = static_cast<uint8_t>(code);
+    }
+    fwht_row_stages(d, lane, 128);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) es[t][1][4 * lane + k] = __fsub_rn(__fmul_rn(d[k], C128), x[k]);
+    if ((lane & 7) == 0) ws[t][1][lane >> 3] = static_cast<uint16_t>(word);
+  }
+  __syncthreads();
+  // ---- B: u_i = ((U0 + U1) + U2) + U3, U_b = seq_{k in block b} C[i][k] e_k, for every (token, head candidate)
+  {
+    float u[TG][2];
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+      float U[TG][2];
+#pragma unroll 4
+      for (int k = 0; k < 32; ++k) {
+        const float cv = __ldg(CT + (32 * b + k) * HD + i);
+#pragma unroll
+        for (int t = 0; t < TG; ++t)
+#pragma unroll
+          for (int c = 0; c < 2; ++c) {
+            const float pr = __fmul_rn(cv, es[t][c][32 * b + k]);
+            U[t][c] = k == 0 ? pr : __fadd_rn(U[t][c], pr);
+          }
+      }
+#pragma unroll
+      for (int t = 0; t < TG; ++t)
+#pragma unroll
+        for (int c = 0; c < 2; ++c) u[t][c] = b == 0 ? U[t][c] : __fadd_rn(u[t][c], U[t][c]);
+    }
+#pragma unroll
+    for (int t = 0; t < TG; ++t)
+#pragma unroll
+      for (int c = 0; c < 2; ++c) ps[t][c][i] = __fmul_rn(es[t][c][i], u[t][c]);
+  }
+  __syncthreads();
+  // ---- C: halving tree of e * u over the 128 dims (warp per (token, candidate))
+  for (int it = j; it < 2 * ntok; it += 4) {
+    const int t = it >> 1, c = it & 1;
+    const float a = __fadd_rn(ps[t][c][lane], ps[t][c][lane + 64]);
+    const float b = __fadd_rn(ps[t][c][lane + 32], ps[t][c][lane + 96]);
+    const float e = tree32(__fadd_rn(a, b));
+    if (lane == 0) herr[t][c] = e;
+  }
+  __syncthreads();
+  // ---- D: head choice and page write (warp j = token j)
+  if (j < ntok) {
+    const int t = j;
+    const long long slot = p.slot_ph ? p.slots[static_cast<long long>(t0 + t) * p.Hkv + h] : p.slots[t0 + t];
+    if (slot < 0) return;
+    const bool F = herr[t][1] < herr[t][0];
+    const int c = F ? 1 : 0;
+    const int P = p.page;
+    const long long page = slot / P;
+    const int pos = static_cast<int>(slot % P);
+    uint8_t* chunk = p.pool + (page * p.Hkv + h) * static_cast<long long>(Lay<NB>::chunk(P));
+    unsigned code[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) code[k] = cs[t][c][4 * lane + k];
+    store_k_row<NB>(chunk, P, pos, lane, code, ws[t][c][lane >> 3]);
+    if (lane == 0)   // the key's whole-head flag rides in bit 15 of the token's V group-0 scale word
+      put_word_bit15(chunk, Lay<NB>::vs_off(P) + 2 * (8 * (pos >> 3) + vslot8(pos)), F);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ launchers
+static int check_launch() { return cudaPeekAtLastError() == cudaSuccess ? 0 : -1; }
+
+int head_fwht_launch(const void* x, long long x_ts, void* out, long long o_ts, int T, int H, const uint8_t* flags,
+                     float scale, cudaStream_t st) {
+  const long long warps = static_cast<long long>(T) * H;
+  const unsigned blocks = static_cast<unsigned>((warps * 32 + 255) / 256);
+  k_head_fwht<<<blocks, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), x_ts, static_cast<__nv_bfloat16*>(out), o_ts,
+                                      T, H, flags, scale);
+  return check_launch();
+}
+
+int rows_launch(int nb, const void* kv, long long kv_ts, const long long* slots, int slot_ph, int T, int Hkv, int page,
+                const uint8_t* mask, const uint8_t* hfull, const float* kmu, uint8_t* pool, int row0, int nrow,
+                int shared15, cudaStream_t st) {
+  if (T <= 0 || nrow <= 0) return 0;
+  RowParams p{static_cast<const __nv_bfloat16*>(kv), kv_ts, slots, slot_ph, T, Hkv, page, mask, hfull, kmu, pool, row0,
+              nrow, shared15};
+  const long long items = static_cast<long long>(T) * nrow;
+  const unsigned blocks = static_cast<unsigned>((items + 3) / 4);
+  if (nb == 4) k_rows<4><<<blocks, 128, 0, st>>>(p);
+  else k_rows<2><<<blocks, 128, 0, st>>>(p);
+  return check_launch();
+}
+
+template <int NB>
+static int dyn_keys_nb(const DynParams& p, cudaStream_t st) {
+  const long long items = static_cast<long long>(p.T) * p.Hkv;
+  const int tg = items <= 1024 ? 1 : items <= 4096 ? 2 : 4;
+  const dim3 grid(p.Hkv, (p.T + tg - 1) / tg);
+  if (tg == 1) k_dyn_keys<NB, 1><<<grid, 128, 0, st>>>(p);
+  else if (tg == 2) k_dyn_keys<NB, 2><<<grid, 128, 0, st>>>(p);
+  else k_dyn_keys<NB, 4><<<grid, 128, 0, st>>>(p);
+  return check_launch();
+}
+
+int dyn_keys_launch(int nb, const void* kv, long long kv_ts, const long long* slots, int slot_ph, int T, int Hkv, int page,
+                    const float* CT, const float* kmu, uint8_t* pool, cudaStream_t st) {
+  if (T <= 0) return 0;
+  DynParams p{static_cast<const __nv_bfloat16*>(kv), kv_ts, slots, slot_ph, T, Hkv, page, CT, kmu, pool};
+  return nb == 4 ? dyn_keys_nb<4>(p, st) : dyn_keys_nb<2>(p, st);
+}
+
+}  // namespace fr
