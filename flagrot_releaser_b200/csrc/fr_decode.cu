@@ -22,6 +22,7 @@
 //     fragment); integer accumulators are folded into fp32 whenever the running maximum or the normaliser moves;
 //   * the 4 warps merge in shared memory; splits merge through the caller's workspace, last arriving CTA wins.
 #include <cmath>
+#include <type_traits>
 
 #include "fr_common.cuh"
 #include "fr_kernels.h"
@@ -32,7 +33,13 @@ namespace {
 
 constexpr int NWARP = 4;
 constexpr int BLK = 32;            // tokens per warp step
-constexpr int ST = 3;              // bulk-copy stages per warp
+#ifndef FR_DEC_ST
+#define FR_DEC_ST 3
+#endif
+#ifndef FR_DEC_MINB
+#define FR_DEC_MINB 3
+#endif
+constexpr int ST = FR_DEC_ST;      // bulk-copy stages per warp
 constexpr int MAXPG = 512;         // pages per split (chunk <= 8192 tokens of 16)
 #define NEG_INF (-INFINITY)
 constexpr int WAIT_LIMIT = 1 << 22;
@@ -60,8 +67,14 @@ FR_DEVI bool mbar_wait(uint32_t a, uint32_t parity) {  // bounded: false after W
   }
   return false;
 }
-FR_DEVI void mma_u8s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
-  asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+// D = A * B with a zero accumulator (no register initialisation)
+FR_DEVI void mma_u8s8_z(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};\n"
+               : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
+FR_DEVI void mma_u8u8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.u8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
                : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
@@ -74,6 +87,19 @@ FR_DEVI uint32_t prmt(uint32_t a, uint32_t b, uint32_t s) {
   uint32_t r;
   asm("prmt.b32 %0, %1, %2, %3;\n" : "=r"(r) : "r"(a), "r"(b), "r"(s));
   return r;
+}
+FR_DEVI uint4 lds128(uint32_t a) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+  return v;
+}
+FR_DEVI uint2 lds64(uint32_t a) {
+  uint2 v;
+  asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];\n" : "=r"(v.x), "=r"(v.y) : "r"(a));
+  return v;
+}
+FR_DEVI void sts128(uint32_t a, uint32_t x, uint32_t y, uint32_t z, uint32_t w) {
+  asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};\n" ::"r"(a), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
 }
 FR_DEVI float h2f(uint32_t bits16) { return __half2float(__ushort_as_half(static_cast<unsigned short>(bits16))); }
 FR_DEVI float2 h2x2f(uint32_t v) {   // two packed fp16 -> two fp32
@@ -89,6 +115,11 @@ template <int NB> struct DLay {
   static constexpr int STAGE = ((PG1 + CHUNK + 127) / 128) * 128;
   static constexpr int V_OFF = Lay<NB>::CBY * P, KS_OFF = 2 * Lay<NB>::CBY * P, VS_OFF = KS_OFF + 8 * P;
   static constexpr uint32_t ZM = NB == 4 ? 0xFu : 0x3u;
+  // the tensor path reads the code fields in place, i.e. scaled by a power of two:
+  // K fields of group j by KF(j) (INT4 16; INT2 4 for even, 64 for odd groups), V^T rows gid / gid + 8 by 1 / VF0, 1 / VF1
+  __host__ __device__ static constexpr int kf(int j) { return NB == 4 ? 16 : ((j & 1) ? 64 : 4); }
+  __host__ __device__ static constexpr float kfinv(int j) { return 1.0f / static_cast<float>(kf(j)); }
+  static constexpr float VF0 = NB == 4 ? 1.0f / 16.0f : 1.0f / 4.0f, VF1 = NB == 4 ? 1.0f / 16.0f : 1.0f / 64.0f;
 };
 constexpr int PBUF_WORDS = 4 * 72;  // P' exchange per warp: [head] stride 72 words (18 x 16 B), [c][hl][e][j]
 
@@ -322,14 +353,14 @@ FR_DEVI void q_prologue(const DecodeParams& p, int b, int kvh, int qt, int16_t* 
 #pragma unroll
     for (int i = 0; i < 4; ++i) am = fmaxf(am, fabsf(v[c][i]));
   am = warp_max(am);
-  const float step = am > 0.f ? am * (1.0f / 16256.0f) : 1.0f;
+  const float step = am > 0.f ? am * (1.0f / 8128.0f) : 1.0f;
   const float inv = 1.0f / step;
 #pragma unroll
   for (int c = 0; c < NV; ++c) {
     int s = 0;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      const int qi = max(-16256, min(16256, __float2int_rn(v[c][i] * inv)));
+      const int qi = max(-8128, min(8128, __float2int_rn(v[c][i] * inv)));
       qtab[(c * 4 + g) * 128 + 4 * lane + i] = static_cast<int16_t>(qi);
       s += qi;
     }
@@ -343,7 +374,7 @@ FR_DEVI void q_prologue(const DecodeParams& p, int b, int kvh, int qt, int16_t* 
 
 // ------------------------------------------------------------------------------------------------ the kernel
 template <int NB, bool KO>
-__global__ void __launch_bounds__(128, 3) k_decode(const DecodeParams p) {
+__global__ void __launch_bounds__(128, FR_DEC_MINB) k_decode(const DecodeParams p) {
   constexpr int NV = KO ? 3 : 1;
   using L = DLay<NB>;
   using S = SMap<NB, NV>;
@@ -414,7 +445,7 @@ __global__ void __launch_bounds__(128, 3) k_decode(const DecodeParams p) {
   // ---- per-thread constants
   // q B fragments: column gid = (head gid >> 1, part gid & 1: hi / lo); k = 4 tig .. (b0), 16 + 4 tig .. (b1)
   uint32_t qf[NV][4][2];
-  int SQ[NV][4];
+  int SQ[NV][4];   // per-group sums of the fixed-point q, pre-multiplied by the code scaling of the group (KF)
   {
     const int hd = gid >> 1, lo_part = gid & 1;
 #pragma unroll
@@ -432,23 +463,33 @@ __global__ void __launch_bounds__(128, 3) k_decode(const DecodeParams p) {
           }
           qf[c][j][r] = word;
         }
-        SQ[c][j] = sqs[(c * 4 + tig) * 4 + j];
+        SQ[c][j] = sqs[(c * 4 + tig) * 4 + j] * L::kf(j);
       }
   }
-  const float sfac = sfs[tig];
+  const float sfac = NB == 4 ? sfs[tig] * L::kfinv(0) : sfs[tig];
   // tokens of this lane inside a block: tau_i = 8 c + 2 i + e, (c, e) = (gid >> 1, gid & 1)
   const int tc = gid >> 1, te = gid & 1;
-  const int tpage = tc >> 1;                                           // page of the block holding the lane's tokens
-  const uint32_t tpoff = tpage * L::PG1;
+  const uint32_t tpoff = (tc >> 1) * L::PG1;                           // page of the block holding the lane's tokens
   const int tpos0 = 8 * (tc & 1) + te;                                 // position in the page of token i = 0 (+ 2 i)
-  // P' exchange buffer
-  uint32_t* pbuf = reinterpret_cast<uint32_t*>(smem + S::PBUF) + w * PBUF_WORDS;
-  uint32_t* pw_dst = pbuf + tig * 72 + tc * 16 + te * 4;               // + hl * 8, 4 words (j)
-  const uint32_t* pw_src = pbuf + (gid >> 1) * 72 + tig * 16 + (gid & 1) * 8;   // 8 words: [e][j]
+  // P' exchange buffer: [head] 72 words, [part hi / lo] 36 words, [chunk c] 8 words, [e] 4 words, [j]
+  const uint32_t pbuf = smem_u32(smem + S::PBUF) + w * PBUF_WORDS * 4;
+  const uint32_t pw_dst = pbuf + 4 * (tig * 72 + tc * 8 + te * 4);               // + 144 bytes for the lo part
+  const uint32_t pw_src = pbuf + 4 * ((gid >> 1) * 72 + (gid & 1) * 36 + tig * 8);   // 8 words: [e][j]
+  // byte offsets of this lane's shared-memory reads inside a stage
+  const uint32_t ks_off = tpoff + L::KS_OFF + 8 * tpos0;               // + 16 i
+  const uint32_t vs_off = tpoff + L::VS_OFF + 2 * (8 * (tc & 1) + 4 * te);   // + 2 P j
+  uint32_t kc_off[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int pos = tpos0 + 2 * i;
+    kc_off[i] = tpoff + (NB == 4 ? 64 * pos + 16 * tig : 32 * (pos ^ ((pos >> 1) & 2)) + 8 * tig);
+  }
+  const uint32_t vc_off = (tig >> 1) * L::PG1 + L::V_OFF + (NB == 4 ? 16 : 8) * (gid * (L::P / 8) + (tig & 1));
 
   // ---- running state (head tig)
   float m_run = NEG_INF, l_run = 0.f;
-  float nmax = 0.f, nrm = 0.f, inrm = 0.f;      // normaliser of P': P~ = rint(p * sv * nrm), nrm = 2^14 / nmax
+  uint32_t nmax16 = 0;                           // fp16 bits of the largest V scale admitted by the normaliser
+  float nrm = 0.f, inrm = 0.f;                   // P~ = rint(p * sv * nrm), nrm = 2^14 / (2 max sv)
   int Oi[2][4][4];                               // [m][w][frag] integer PV accumulators
   float Of[2][4][2];                             // folded fp32 accumulators, rows gid / gid + 8 of tile (m, w), head tig
   int Zi[4];
@@ -469,8 +510,8 @@ __global__ void __launch_bounds__(128, 3) k_decode(const DecodeParams p) {
     for (int a = 0; a < 2; ++a)
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
-        Of[a][c][0] = (Of[a][c][0] + static_cast<float>(Oi[a][c][0] * 256 + Oi[a][c][1]) * inrm) * alpha;
-        Of[a][c][1] = (Of[a][c][1] + static_cast<float>(Oi[a][c][2] * 256 + Oi[a][c][3]) * inrm) * alpha;
+        Of[a][c][0] = (Of[a][c][0] + static_cast<float>(Oi[a][c][0] * 256 + Oi[a][c][1]) * (inrm * L::VF0)) * alpha;
+        Of[a][c][1] = (Of[a][c][1] + static_cast<float>(Oi[a][c][2] * 256 + Oi[a][c][3]) * (inrm * L::VF1)) * alpha;
 #pragma unroll
         for (int k = 0; k < 4; ++k) Oi[a][c][k] = 0;
       }
@@ -482,30 +523,29 @@ __global__ void __launch_bounds__(128, 3) k_decode(const DecodeParams p) {
     l_run *= alpha;
   };
 
-  bool wait_ok = true;
-  for (int n = 0; n < nmine; ++n) {
-    const int blk = w + NWARP * n, s = n % ST;
-    __syncwarp();
-    if (lane == 0 && n + ST - 1 < nmine) issue(n + ST - 1);
-    if (!mbar_wait(mb0 + 8 * s, (n / ST) & 1)) { wait_ok = false; }
-    const uint8_t* st = smem + S::RING + (w * ST + s) * L::STAGE;
-    const int tok0 = c0 + blk * BLK;                                   // absolute position of the block's token 0
-    const bool partial = tok0 < lo || tok0 + BLK > c1;
-
-    // ---- scale words of the lane's 4 tokens: K (4 groups per token), V (4 tokens per group)
+  // one 32-token block of this warp from stage memory `st`; PARTIAL: some tokens lie outside [lo, c1)
+  auto process = [&](const uint32_t st, int tok0, auto partial_tag) {
+    constexpr bool PARTIAL = decltype(partial_tag)::value;
+    // ---- scale words of the lane's 4 tokens: K (token i: groups 0 1 | 2 3), V (group j: tokens 0 1 | 2 3)
     uint32_t ksw[4][2], vsw[4][2];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      const uint2 t = *reinterpret_cast<const uint2*>(st + tpoff + L::KS_OFF + 8 * (tpos0 + 2 * i));
+      const uint2 t = lds64(st + ks_off + 16 * i);
       ksw[i][0] = t.x; ksw[i][1] = t.y;
     }
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      const uint2 t = *reinterpret_cast<const uint2*>(st + tpoff + L::VS_OFF + 2 * (j * L::P + 8 * (tc & 1) + 4 * te));
-      vsw[j][0] = t.x; vsw[j][1] = t.y;                                // tokens i = 0, 1 | 2, 3
+      const uint2 t = lds64(st + vs_off + 2 * L::P * j);
+      vsw[j][0] = t.x; vsw[j][1] = t.y;
     }
     bool valid[4] = {true, true, true, true};
-    if (partial) {
+    [[maybe_unused]] bool ffl[4] = {false, false, false, false};
+    if constexpr (KO) {   // whole-head flag of the key of token i: bit 15 of its V group-0 word
+      ffl[0] = (vsw[0][0] & 0x8000u) != 0; ffl[1] = static_cast<int>(vsw[0][0]) < 0;
+      ffl[2] = (vsw[0][1] & 0x8000u) != 0; ffl[3] = static_cast<int>(vsw[0][1]) < 0;
+      vsw[0][0] &= 0x7FFF7FFFu; vsw[0][1] &= 0x7FFF7FFFu;
+    }
+    if constexpr (PARTIAL) {
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const int pos = tok0 + 8 * tc + 2 * i + te;
@@ -526,46 +566,55 @@ __global__ void __launch_bounds__(128, 3) k_decode(const DecodeParams p) {
       uint32_t ka[2][4];   // code words of rows i = 2 u, 2 u + 1: INT4 4 words (group j), INT2 2 words (groups 2 jp, 2 jp + 1)
 #pragma unroll
       for (int r = 0; r < 2; ++r) {
-        const int pos = tpos0 + 2 * (2 * u + r);
         if (NB == 4) {
-          const uint4 t = *reinterpret_cast<const uint4*>(st + tpoff + 64 * pos + 16 * tig);
+          const uint4 t = lds128(st + kc_off[2 * u + r]);
           ka[r][0] = t.x; ka[r][1] = t.y; ka[r][2] = t.z; ka[r][3] = t.w;
         } else {
-          const uint2 t = *reinterpret_cast<const uint2*>(st + tpoff + 32 * (pos ^ ((pos >> 1) & 2)) + 8 * tig);
+          const uint2 t = lds64(st + kc_off[2 * u + r]);
           ka[r][0] = t.x; ka[r][1] = t.y; ka[r][2] = 0; ka[r][3] = 0;
+        }
+      }
+      float skf[2][4];     // group scales of the two rows
+      int nz[2][4];        // minus the zero points
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        const int i = 2 * u + r;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const uint32_t wv = ksw[i][h];
+          const float2 f = h2x2f(KO ? (wv & 0x7FFF7FFFu) : wv);
+          skf[r][2 * h] = f.x; skf[r][2 * h + 1] = f.y;
+          const uint32_t zz = wv & (L::ZM | (L::ZM << 16));
+          nz[r][2 * h] = -static_cast<int>(zz & 0xFFFFu);
+          nz[r][2 * h + 1] = -static_cast<int>(zz >> 16);
         }
       }
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
+        // A fragments: the code fields in place, scaled by KF(j) = 16 (INT4) | 4, 64 (INT2): no right shifts
         uint32_t a0, a1, a2, a3;
         if (NB == 4) {
-          a0 = ka[0][j] & 0x0F0F0F0Fu; a2 = (ka[0][j] >> 4) & 0x0F0F0F0Fu;
-          a1 = ka[1][j] & 0x0F0F0F0Fu; a3 = (ka[1][j] >> 4) & 0x0F0F0F0Fu;
+          a0 = (ka[0][j] * 16u) & 0xF0F0F0F0u; a2 = ka[0][j] & 0xF0F0F0F0u;
+          a1 = (ka[1][j] * 16u) & 0xF0F0F0F0u; a3 = ka[1][j] & 0xF0F0F0F0u;
         } else {
-          const int sh = 4 * (j & 1);
-          a0 = (ka[0][j >> 1] >> sh) & 0x03030303u; a2 = (ka[0][j >> 1] >> (sh + 2)) & 0x03030303u;
-          a1 = (ka[1][j >> 1] >> sh) & 0x03030303u; a3 = (ka[1][j >> 1] >> (sh + 2)) & 0x03030303u;
+          const uint32_t msk = (j & 1) ? 0xC0C0C0C0u : 0x0C0C0C0Cu;
+          a0 = (ka[0][j >> 1] * 4u) & msk; a2 = ka[0][j >> 1] & msk;
+          a1 = (ka[1][j >> 1] * 4u) & msk; a3 = ka[1][j >> 1] & msk;
         }
         int acc[NV][4];
 #pragma unroll
-        for (int c = 0; c < NV; ++c) {
-          acc[c][0] = acc[c][1] = acc[c][2] = acc[c][3] = 0;
-          mma_u8s8(acc[c], a0, a1, a2, a3, qf[c][j][0], qf[c][j][1]);
-        }
+        for (int c = 0; c < NV; ++c) mma_u8s8_z(acc[c], a0, a1, a2, a3, qf[c][j][0], qf[c][j][1]);
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
           const int i = 2 * u + r;
-          const uint32_t kw = (ksw[i][j >> 1] >> (16 * (j & 1))) & 0xFFFFu;
-          int hi = acc[0][2 * r], lw = acc[0][2 * r + 1], sq = SQ[0][j];
+          int val = acc[0][2 * r] * 128 + acc[0][2 * r + 1] + nz[r][j] * SQ[0][j];
           if constexpr (KO) {
-            const bool hfl = (kw & 0x8000u) != 0;
-            const bool ffl = ((vsw[0][i >> 1] >> (16 * (i & 1))) & 0x8000u) != 0;
-            hi = ffl ? acc[NV - 1][2 * r] : (hfl ? acc[NV > 1 ? 1 : 0][2 * r] : hi);
-            lw = ffl ? acc[NV - 1][2 * r + 1] : (hfl ? acc[NV > 1 ? 1 : 0][2 * r + 1] : lw);
-            sq = ffl ? SQ[NV - 1][j] : (hfl ? SQ[NV > 1 ? 1 : 0][j] : sq);
+            const int vh = acc[1][2 * r] * 128 + acc[1][2 * r + 1] + nz[r][j] * SQ[1][j];
+            const int vf = acc[2][2 * r] * 128 + acc[2][2 * r + 1] + nz[r][j] * SQ[2][j];
+            const bool hfl = (j & 1) ? static_cast<int>(ksw[i][j >> 1]) < 0 : (ksw[i][j >> 1] & 0x8000u) != 0;
+            val = ffl[i] ? vf : (hfl ? vh : val);
           }
-          const int val = hi * 128 + lw - static_cast<int>(kw & L::ZM) * sq;
-          sc[i] = fmaf(h2f(kw & 0x7FFFu), static_cast<float>(val), sc[i]);
+          sc[i] = fmaf(NB == 4 ? skf[r][j] : skf[r][j] * L::kfinv(j), static_cast<float>(val), sc[i]);
         }
       }
     }
@@ -573,33 +622,30 @@ __global__ void __launch_bounds__(128, 3) k_decode(const DecodeParams p) {
     float bm = NEG_INF;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      sc[i] = valid[i] ? sc[i] * sfac : NEG_INF;
+      sc[i] = (!PARTIAL || valid[i]) ? sc[i] * sfac : NEG_INF;
       bm = fmaxf(bm, sc[i]);
     }
     bm = fmaxf(bm, __shfl_xor_sync(FULLMASK, bm, 4));
     bm = fmaxf(bm, __shfl_xor_sync(FULLMASK, bm, 8));
     bm = fmaxf(bm, __shfl_xor_sync(FULLMASK, bm, 16));
     // largest V scale of the lane's tokens (fp16 order = integer order of the 15-bit patterns)
-    uint32_t vm = 0;
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const uint32_t a = vsw[j][0] & 0x7FFF7FFFu, c = vsw[j][1] & 0x7FFF7FFFu;
-      vm = max(vm, max(max(a & 0xFFFFu, a >> 16), max(c & 0xFFFFu, c >> 16)));
-    }
-    const float vmax = h2f(vm);
-    if (__any_sync(FULLMASK, bm > m_run || vmax > nmax)) {
-      float wmax = vmax;
-      wmax = fmaxf(wmax, __shfl_xor_sync(FULLMASK, wmax, 4));
-      wmax = fmaxf(wmax, __shfl_xor_sync(FULLMASK, wmax, 8));
-      wmax = fmaxf(wmax, __shfl_xor_sync(FULLMASK, wmax, 16));
+    uint32_t vm = __vmaxu2(__vmaxu2(__vmaxu2(vsw[0][0], vsw[0][1]), __vmaxu2(vsw[1][0], vsw[1][1])),
+                           __vmaxu2(__vmaxu2(vsw[2][0], vsw[2][1]), __vmaxu2(vsw[3][0], vsw[3][1])));
+    vm = max(vm & 0xFFFFu, vm >> 16);
+    if (__any_sync(FULLMASK, bm > m_run || vm > nmax16)) {
+      uint32_t wm = vm;
+      wm = max(wm, __shfl_xor_sync(FULLMASK, wm, 4));
+      wm = max(wm, __shfl_xor_sync(FULLMASK, wm, 8));
+      wm = max(wm, __shfl_xor_sync(FULLMASK, wm, 16));
       const float mn = fmaxf(m_run, bm);
-      const float alpha = (m_run == NEG_INF || mn == m_run) ? (m_run == NEG_INF ? 0.f : 1.f) : ex2(m_run - mn);
+      const float alpha = m_run == NEG_INF ? 0.f : (mn == m_run ? 1.f : ex2(m_run - mn));
       fold(alpha);
       m_run = mn;
-      if (wmax > nmax) {
-        nmax = 2.f * wmax;
-        nrm = 16384.f / nmax;
-        inrm = nmax * (1.0f / 16384.f);
+      if (wm > nmax16) {     // twice the largest scale seen (one exponent step in fp16), capped below infinity
+        nmax16 = min(wm + 0x0400u, 0x7BFFu);
+        const float nf = h2f(nmax16);
+        nrm = 16384.f / nf;
+        inrm = nf * (1.0f / 16384.f);
       }
     }
     const float msafe = m_run == NEG_INF ? 0.f : m_run;
@@ -610,63 +656,66 @@ __global__ void __launch_bounds__(128, 3) k_decode(const DecodeParams p) {
       l_run += pr;
       pn[i] = pr * nrm;
     }
-    // ---- P~ per (token, group): 14-bit fixed point, transposed through shared memory into the PV B fragments
+    // ---- P~ per (token, group): 14-bit fixed point (u8 hi, u8 lo), transposed through shared memory into the PV B fragments
+    uint32_t hiw[4], low[4];
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      uint32_t x01, x23;
-      {
-        const float2 s01 = h2x2f(vsw[j][0] & 0x7FFF7FFFu), s23 = h2x2f(vsw[j][1] & 0x7FFF7FFFu);
-        const uint32_t t0 = __float_as_uint(fmaf(pn[0], s01.x, 8388608.f)), t1 = __float_as_uint(fmaf(pn[1], s01.y, 8388608.f));
-        const uint32_t t2 = __float_as_uint(fmaf(pn[2], s23.x, 8388608.f)), t3 = __float_as_uint(fmaf(pn[3], s23.y, 8388608.f));
-        x01 = prmt(t0, t1, 0x5410u);
-        x23 = prmt(t2, t3, 0x5410u);
-      }
-      // zero-point sums with the same integers the tensor path sees
-      const uint32_t z01 = vsw[j][0] & (L::ZM | (L::ZM << 16)), z23 = vsw[j][1] & (L::ZM | (L::ZM << 16));
-      Zi[j] += static_cast<int>((x01 & 0xFFFFu) * (z01 & 0xFFFFu) + (x01 >> 16) * (z01 >> 16) +
-                                (x23 & 0xFFFFu) * (z23 & 0xFFFFu) + (x23 >> 16) * (z23 >> 16));
-      const uint32_t y01 = x01 + 0x00800080u, y23 = x23 + 0x00800080u;   // P~ = 256 hi + lo, lo in [-128, 127]
-      const uint32_t hiw = prmt(y01, y23, 0x7531u);
-      const uint32_t low = prmt(y01, y23, 0x6420u) ^ 0x80808080u;
-      pw_dst[j] = hiw;
-      pw_dst[8 + j] = low;
+      const float2 s01 = h2x2f(vsw[j][0]), s23 = h2x2f(vsw[j][1]);
+      const uint32_t t0 = __float_as_uint(fmaf(pn[0], s01.x, 8388608.f)), t1 = __float_as_uint(fmaf(pn[1], s01.y, 8388608.f));
+      const uint32_t t2 = __float_as_uint(fmaf(pn[2], s23.x, 8388608.f)), t3 = __float_as_uint(fmaf(pn[3], s23.y, 8388608.f));
+      const uint32_t x01 = prmt(t0, t1, 0x5410u), x23 = prmt(t2, t3, 0x5410u);
+      hiw[j] = prmt(x01, x23, 0x7531u);
+      low[j] = prmt(x01, x23, 0x6420u);
+      // zero-point sums with the same integers the tensor path sees: bytes (z0, z1, z2, z3)
+      const uint32_t zb = prmt(vsw[j][0] & (L::ZM | (L::ZM << 16)), vsw[j][1] & (L::ZM | (L::ZM << 16)), 0x6420u);
+      Zi[j] = __dp2a_hi(x23, zb, __dp2a_lo(x01, zb, static_cast<unsigned>(Zi[j])));
     }
+    sts128(pw_dst, hiw[0], hiw[1], hiw[2], hiw[3]);
+    sts128(pw_dst + 144, low[0], low[1], low[2], low[3]);
     __syncwarp();
     uint32_t pb[2][4];   // [e][j] of this lane's column (head gid >> 1, part gid & 1), tokens of chunk tig
     {
-      const uint4 t0 = *reinterpret_cast<const uint4*>(pw_src), t1 = *reinterpret_cast<const uint4*>(pw_src + 4);
+      const uint4 t0 = lds128(pw_src), t1 = lds128(pw_src + 16);
       pb[0][0] = t0.x; pb[0][1] = t0.y; pb[0][2] = t0.z; pb[0][3] = t0.w;
       pb[1][0] = t1.x; pb[1][1] = t1.y; pb[1][2] = t1.z; pb[1][3] = t1.w;
     }
-    // ---- PV: A = V^T code bytes of chunk tig (page tig >> 1, c8 = tig & 1), 16 d rows per tile
-    {
-      const uint8_t* vb = st + (tig >> 1) * L::PG1 + L::V_OFF;
+    // ---- PV: A = V^T code fields of chunk tig (page tig >> 1, c8 = tig & 1) in place, 16 d rows per tile
 #pragma unroll
-      for (int ww = 0; ww < 4; ++ww) {
-        const int e = (ww * 8 + gid) * (L::P / 8) + (tig & 1);
-        uint32_t vw[4];
-        if (NB == 4) {
-          const uint4 t = *reinterpret_cast<const uint4*>(vb + 16 * e);
-          vw[0] = t.x; vw[1] = t.y; vw[2] = t.z; vw[3] = t.w;
-        } else {
-          const uint2 t = *reinterpret_cast<const uint2*>(vb + 8 * e);
-          vw[0] = t.x; vw[1] = t.y; vw[2] = 0; vw[3] = 0;
-        }
+    for (int ww = 0; ww < 4; ++ww) {
+      uint32_t vw[4];
+      if (NB == 4) {
+        const uint4 t = lds128(st + vc_off + 16 * (ww * 8 * (L::P / 8)));
+        vw[0] = t.x; vw[1] = t.y; vw[2] = t.z; vw[3] = t.w;
+      } else {
+        const uint2 t = lds64(st + vc_off + 8 * (ww * 8 * (L::P / 8)));
+        vw[0] = t.x; vw[1] = t.y; vw[2] = 0; vw[3] = 0;
+      }
 #pragma unroll
-        for (int mm = 0; mm < 2; ++mm) {
-          uint32_t a0, a1, a2, a3;
-          if (NB == 4) {
-            a0 = vw[2 * mm] & 0x0F0F0F0Fu; a2 = (vw[2 * mm] >> 4) & 0x0F0F0F0Fu;
-            a1 = vw[2 * mm + 1] & 0x0F0F0F0Fu; a3 = (vw[2 * mm + 1] >> 4) & 0x0F0F0F0Fu;
-          } else {
-            a0 = vw[mm] & 0x03030303u; a2 = (vw[mm] >> 2) & 0x03030303u;
-            a1 = (vw[mm] >> 4) & 0x03030303u; a3 = (vw[mm] >> 6) & 0x03030303u;
-          }
-          const int j = 2 * mm + (ww >> 1);
-          mma_u8s8(Oi[mm][ww], a0, a1, a2, a3, pb[0][j], pb[1][j]);
+      for (int mm = 0; mm < 2; ++mm) {
+        uint32_t a0, a1, a2, a3;
+        if (NB == 4) {   // rows gid (word 2 mm) and gid + 8 (word 2 mm + 1), both scaled by 16
+          a0 = (vw[2 * mm] * 16u) & 0xF0F0F0F0u; a2 = vw[2 * mm] & 0xF0F0F0F0u;
+          a1 = (vw[2 * mm + 1] * 16u) & 0xF0F0F0F0u; a3 = vw[2 * mm + 1] & 0xF0F0F0F0u;
+        } else {         // row gid scaled by 4, row gid + 8 by 64
+          a0 = (vw[mm] * 4u) & 0x0C0C0C0Cu; a2 = vw[mm] & 0x0C0C0C0Cu;
+          a1 = (vw[mm] * 4u) & 0xC0C0C0C0u; a3 = vw[mm] & 0xC0C0C0C0u;
         }
+        const int j = 2 * mm + (ww >> 1);
+        mma_u8u8(Oi[mm][ww], a0, a1, a2, a3, pb[0][j], pb[1][j]);
       }
     }
+  };
+
+  bool wait_ok = true;
+  for (int n = 0; n < nmine; ++n) {
+    const int blk = w + NWARP * n, s = n % ST;
+    __syncwarp();
+    if (lane == 0 && n + ST - 1 < nmine) issue(n + ST - 1);
+    if (!mbar_wait(mb0 + 8 * s, (n / ST) & 1)) wait_ok = false;
+    const uint32_t st = ring + s * L::STAGE;
+    const int tok0 = c0 + blk * BLK;                                   // absolute position of the block's token 0
+    if (tok0 < lo || tok0 + BLK > c1) process(st, tok0, std::true_type{});
+    else process(st, tok0, std::false_type{});
   }
   if (!wait_ok && lane == 0) atomicExch(&g_status, __LINE__);
 
