@@ -179,8 +179,8 @@ __global__ void __launch_bounds__(128) k_dyn_keys(const DynParams p) {
     const float e0 = __fsub_rn(quant_err_deq<NB>(z, mn0, mx0), z);
     const float e1 = __fsub_rn(fwht32_lane(quant_err_deq<NB>(y1, mn1, mx1), lane), z);
     float u0 = 0.f, u1 = 0.f;
-#pragma unroll 8
-    for (int k = 0; k < 32; ++k) {
+#pragma unroll
+    for (int k = 0; k < 32; ++k) {   // fully unrolled: the 32 loads do not depend on the sum chain and go out together
       const float cv = __ldg(CT + (32 * j + k) * HD + i);                  // C[i][32 j + k]
       const float p0 = __fmul_rn(cv, __shfl_sync(FULLMASK, e0, k));
       const float p1 = __fmul_rn(cv, __shfl_sync(FULLMASK, e1, k));
@@ -228,7 +228,7 @@ __global__ void __launch_bounds__(128) k_dyn_keys(const DynParams p) {
 #pragma unroll
     for (int b = 0; b < 4; ++b) {
       float U[TG][2];
-#pragma unroll 4
+#pragma unroll 16
       for (int k = 0; k < 32; ++k) {
         const float cv = __ldg(CT + (32 * b + k) * HD + i);
 #pragma unroll
