@@ -7,6 +7,7 @@
 // -4 unknown format / kind, -5 page size, -8 head dim.  Formats built here: int4a (5), int2a (8), konlya (7 / kind 10),
 // konlya2 (9 / kind 11); the symmetric INT4 formats and the ablation codebooks answer -4.
 #include <cstdint>
+#include <cstdio>
 #include <cuda_runtime.h>
 
 #include "fr_kernels.h"
@@ -184,5 +185,54 @@ int fr_attn_partial(int fmt, const void* q, long long q_bs, const uint8_t* pool,
 }
 
 int fr_device_status() { return fr::decode_status(); }
+
+// ---- decode attention for callers that may not allocate device memory
+// Some hosts of this library cannot hand over a workspace: a serving worker whose memory pool was sized and frozen at
+// start-up (every later cudaMalloc would fail or fragment it), or a C / C++ host that owns no allocator at all and only
+// forwards pointers it was given.  For them the split partials and the merge tickets live in one array compiled into
+// the library.  Every GPU that loads the library carries these 16 MiB until the process exits.
+// The host sees `g_noalloc_scratch` only as a handle of the symbol; the device address is looked up per device.
+namespace {
+constexpr size_t NOALLOC_SCRATCH_BYTES = 16u << 20;
+static __device__ __align__(256) unsigned char g_noalloc_scratch[NOALLOC_SCRATCH_BYTES];
+constexpr int NOALLOC_MAX_DEVICES = 64;
+unsigned char* g_noalloc_ptr[NOALLOC_MAX_DEVICES];   // device address of the array on each device (0: not looked up yet)
+}  // namespace
+
+int fr_cb_attn_noalloc(const void* q, long long q_bs, const uint8_t* pool, const int* block_table, int bt_stride,
+                       const int* seq_lens, int B, int Hkv, int page, int nsplit, int chunk, float qscale, int kind,
+                       void* out, long long o_bs, const void* tail, const int* tail_len, const int* tail_idx,
+                       long long tail_bs, long long tail_ts, void* stream, int kv_start) {
+  int nb;
+  if (!kind_info(kind, nb)) return -4;
+  if (B <= 0) return 0;
+  if (Hkv <= 0 || nsplit < 1) return -3;
+  // layout: tickets int32 [B * Hkv] (rounded up to 256 bytes) | (max, sum) pairs | partial rows
+  const size_t parts = static_cast<size_t>(B) * Hkv * (static_cast<size_t>(nsplit) + 1);
+  const size_t cnt_bytes = (static_cast<size_t>(B) * Hkv * sizeof(int) + 255) & ~static_cast<size_t>(255);
+  const size_t ml_bytes = (parts * 8 * sizeof(float) + 255) & ~static_cast<size_t>(255);
+  const size_t need = cnt_bytes + ml_bytes + parts * 512 * sizeof(float);
+  if (need > NOALLOC_SCRATCH_BYTES) {
+    std::fprintf(stderr, "fr_cb_attn_noalloc: batch %d x %d kv heads x %d splits needs %zu bytes of scratch, the built-in "
+                         "array holds %zu; use fr_cb_attn with a caller workspace or fewer splits\n",
+                 B, Hkv, nsplit, need, static_cast<size_t>(NOALLOC_SCRATCH_BYTES));
+    return -9;
+  }
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= NOALLOC_MAX_DEVICES) return -1;
+  if (g_noalloc_ptr[dev] == nullptr) {   // first call on this device (do it before any stream capture)
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_noalloc_scratch) != cudaSuccess || p == nullptr) return -1;
+    g_noalloc_ptr[dev] = static_cast<unsigned char*>(p);
+  }
+  unsigned char* base = g_noalloc_ptr[dev];
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // the array keeps whatever the previous call (or an aborted one) left: the tickets must start at zero
+  if (cudaMemsetAsync(base, 0, cnt_bytes, st) != cudaSuccess) return -1;
+  return attn_common(nb, 1, q, q_bs, pool, block_table, bt_stride, seq_lens, B, Hkv, 4, page, nsplit, chunk, qscale, nullptr,
+                     nullptr, nullptr, reinterpret_cast<float*>(base + cnt_bytes + ml_bytes),
+                     reinterpret_cast<float*>(base + cnt_bytes), reinterpret_cast<int*>(base), out, o_bs, tail, tail_len,
+                     tail_idx, tail_bs, tail_ts, stream, kv_start, nullptr);
+}
 
 }  // extern "C"

@@ -70,10 +70,11 @@ def lib():
     L.fr_head_fwht.argtypes = [P, LL, P, LL, I, I, P, F, P, I]
     L.fr_cb_write3.argtypes = [P, LL, P, I, I, I, I, P, P, P, P, P, I, P, I, I, P, P]
     L.fr_w3_static_write.argtypes = [P, LL, P, I, I, I, P, P, I, P, I, P, P]
+    L.fr_cb_attn_noalloc.argtypes = [P, LL, P, P, I, P, I, I, I, I, I, F, I, P, LL, P, P, P, LL, LL, P, I]
     L.fr_attn_partial.argtypes = [I, P, LL, P, P, I, P, I, I, I, I, I, F, P, P, P, P, P, P, P, P, P, LL, LL, P, I, I]
     for n in ("fr_v2_attn", "fr_v2_write", "fr_v2_occupancy", "fr_v2_chunk_bytes", "fr_cb_write", "fr_cb_attn",
               "fr_cb_occupancy", "fr_cb_chunk_bytes", "fr_cb_nsg", "fr_head_fwht", "fr_cb_write3",
-              "fr_w3_static_write", "fr_cb_write_smem", "fr_attn_partial", "fr_device_status"):
+              "fr_w3_static_write", "fr_cb_write_smem", "fr_attn_partial", "fr_device_status", "fr_cb_attn_noalloc"):
         getattr(L, n).restype = I
     _LIB = L
     return L
@@ -346,6 +347,25 @@ def cb_attn(q, pool, block_table, seq_lens, out, nsplit, chunk, ws, qscale, kind
                             ws.mlpart.data_ptr(), ws.counter.data_ptr(), out.data_ptr(), out.stride(0), _ptr(tail),
                             _ptr(tail_len), _ptr(tail_idx), 0 if tail is None else tail_bs,
                             0 if tail is None else tail_ts, _stream(), int(kv_start)), "fr_cb_attn")
+
+
+def cb_attn_noalloc(q, pool, block_table, seq_lens, out, nsplit, chunk, qscale, kind, tail=None, tail_len=None,
+                    tail_idx=None, tail_bs=None, tail_ts=None, page=16, kv_start=0):
+    """cb_attn for a caller that cannot allocate a Workspace: the partials live in a 16 MiB array inside the library.
+    Returns the entry point's code (0 ok, -9: the request does not fit the built-in array) instead of raising on -9.
+    Calls that overlap on the GPU share the array and must be serialised; make the first call on a device outside any
+    stream capture."""
+    B, Hq, Dh = q.shape
+    Hkv = Hq // 4
+    assert Hq == 4 * pool.shape[1] and Dh == D and q.stride(2) == 1 and q.stride(1) == D and out.stride(1) == 1
+    bt, bts = _bt_args(block_table)
+    rc = lib().fr_cb_attn_noalloc(q.data_ptr(), q.stride(0), pool.data_ptr(), bt, bts, seq_lens.data_ptr(), B, Hkv, page,
+                                  nsplit, chunk, qscale, CB_KINDS[kind], out.data_ptr(), out.stride(0), _ptr(tail),
+                                  _ptr(tail_len), _ptr(tail_idx), 0 if tail is None else tail_bs,
+                                  0 if tail is None else tail_ts, _stream(), int(kv_start))
+    if rc not in (0, -9):
+        _check(rc, "fr_cb_attn_noalloc")
+    return rc
 
 
 def attn_partial(q, pool, block_table, seq_lens, part, nsplit, chunk, ws, qscale, fmt, kmask=None, vmask=None, tail=None,

@@ -107,6 +107,20 @@ int fr_attn_partial(int fmt, const void* q, long long q_bs, const uint8_t* pool,
 /* 0, or the source line of a bounded device-side wait that gave up (sticky; synchronises the device). */
 int fr_device_status(void);
 
+/* No counterpart in the reference.  fr_cb_attn (GQA 4, kinds 10 / 11) for a caller that cannot supply a workspace
+ * because it cannot allocate device memory: a serving worker whose memory pool is frozen after start-up, or a plain C
+ * host that only forwards the pointers it was handed.  The split partials and merge tickets live in a 16 MiB array
+ * built into the library (held by every GPU that loads it, until exit); inputs and outputs are still the caller's.
+ * Needs 256-rounded 4 * B * Hkv + 32 * parts bytes plus 2048 * parts bytes, parts = B * Hkv * (nsplit + 1); a larger
+ * request returns -9 and prints the sizes to stderr.  The call allocates nothing.  The first call on a device looks up
+ * the array's device address: make that call before any stream capture.  All calls share the array, so two calls that
+ * overlap on the GPU (two streams, or two host threads) corrupt each other: serialise them.  Each call clears its
+ * tickets first; nothing else in the array is assumed. */
+int fr_cb_attn_noalloc(const void* q, long long q_bs, const uint8_t* pool, const int* block_table, int bt_stride,
+                       const int* seq_lens, int B, int Hkv, int page, int nsplit, int chunk, float qscale, int kind,
+                       void* out, long long o_bs, const void* tail, const int* tail_len, const int* tail_idx,
+                       long long tail_bs, long long tail_ts, void* stream, int kv_start);
+
 #ifdef __cplusplus
 }
 #endif
