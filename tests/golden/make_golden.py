@@ -288,11 +288,64 @@ def gen_pages():
     np.savez_compressed(HERE / "pages.npz", **pages)
 
 
+def gen_kivi():
+    """FlagRot-KIVI (kivi2:32): plain KIVI reconstructions (blockflag.formats.fake via qattention._fake_tok_ for keys along the
+    token axis, formats.fake for values) and the simulator's dynamic choices (the functions of
+    integrations/vllm_flagrot/tests/test_kivi.py:72-88: qattention._weights / _vec_err / _head_err / _pool_tokens) and
+    reconstructions (qattention.dyn_quant), each 32-token group on its own, group 0 without its 4 sink tokens."""
+    from blockflag import qattention as QA
+    from blockflag.hadamard import fwht
+    g = torch.Generator().manual_seed(404)
+    H, ng, S, NQ = 2, 6, 4, 192
+    T = ng * 32
+    mu = torch.randn(H, 128, generator=g) * 2.0
+    mu[:, torch.randint(0, 128, (6,), generator=g)] *= 6
+    k = (mu[None] + torch.randn(T, H, 128, generator=g) * (0.5 + torch.rand(H, 128, generator=g))).bfloat16()
+    v = (torch.randn(T, H, 128, generator=g) * 0.3 + mu[None] * 0.05).bfloat16()
+    qs = torch.randn(H, NQ, 128, generator=g) * 0.3
+    lz = torch.full((H, NQ), 5.0)
+    co = torch.rand(H, 128, generator=g) + 0.1
+    qscale = 1 / math.sqrt(128)
+    out = dict(k=bits_of(k), v=bits_of(v), qs=qs.numpy(), lz=lz.numpy(), co=co.numpy(), qscale=np.float64(qscale), S=np.int32(S))
+    SPEC = "kivi2:32"
+    QA.KV.update(dyn=dict(rule="att", local=["H"], head=["F"], group=1, only=None), sink=0, qs={0: qs}, lz={0: lz},
+                 qscale=qscale, co={0: co}, xf=None, dynstat={})
+    xf = k.float().permute(1, 0, 2)[None]                                    # [1, H, T, 128]
+    vf = v.float().permute(1, 0, 2)[None]
+    rec_id = torch.empty_like(xf)
+    rec_dyn = torch.empty_like(xf)
+    lbs, fbs = [], []
+    for a, b_ in [(S, 32)] + [(32 * i, 32 * i + 32) for i in range(1, ng)]:
+        seg = xf[:, :, a:b_]
+        rec_id[:, :, a:b_] = QA._fake_tok_(seg, SPEC)
+        rec_dyn[:, :, a:b_] = QA.dyn_quant(seg, SPEC, 32, "k", 0, "token")
+        W = QA._weights("k", 0, seg)
+        Q = lambda y: QA._fake_tok(y, SPEC)  # noqa: E731
+        recs = [Q(seg), fwht(Q(fwht(seg, 32)), 32)]
+        errs = QA._pool_tokens(torch.stack([QA._vec_err(r - seg, W, 32) for r in recs]), 32, 3)
+        ch = errs.argmin(0)
+        sel = ch[..., None].expand(*ch.shape, 32).reshape(seg.shape)
+        r = torch.where(sel == 1, recs[1], recs[0])
+        F = fwht(Q(fwht(seg, 128)), 128)
+        he = QA._pool_tokens(torch.stack([QA._head_err(h - seg, W) for h in (r, F)]), 32, 3)
+        hs = he.argmin(0)
+        lbs.append(ch[0][:, 0].numpy())                                      # [H, 4]
+        fbs.append(hs[0][:, 0].numpy())                                      # [H]
+    rec_id[:, :, :S] = xf[:, :, :S]
+    rec_dyn[:, :, :S] = xf[:, :, :S]
+    out.update(k_rec_ident=rec_id[0].permute(1, 0, 2).numpy(), k_rec_dyn=rec_dyn[0].permute(1, 0, 2).numpy(),
+               k_local=np.stack(lbs).astype(np.int8), k_head=np.stack(fbs).astype(np.int8))
+    out["v_rec_ident"] = FM.fake(vf, SPEC)[0].permute(1, 0, 2).numpy()
+    out["v_rec_dyn"] = QA.dyn_quant(vf, SPEC, 32, "v", 0)[0].permute(1, 0, 2).numpy()
+    np.savez_compressed(HERE / "kivi.npz", **out)
+
+
 if __name__ == "__main__":
     torch.manual_seed(0)
     gen_dynamic()
     gen_static()
     gen_pages_and_decode()
     gen_pages()
+    gen_kivi()
     for f in sorted(HERE.glob("*.npz")):
         print(f.name, f.stat().st_size)

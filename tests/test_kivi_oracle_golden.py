@@ -1,0 +1,104 @@
+"""Pins oracle/kivi_oracle.py against the reference simulator's outputs (tests/golden/kivi.npz): plain-KIVI reconstructions
+bit for bit (CPU arithmetic, recip=False), dynamic choices within the reference's own mismatch allowance, and the page
+packer against the parser on random fields."""
+import numpy as np
+import pytest
+
+from oracle import flagrot_oracle as O
+from oracle import kivi_oracle as KO
+
+
+@pytest.fixture(scope="module")
+def g(golden_dir):
+    return np.load(golden_dir / "kivi.npz")
+
+
+def _groups(g):
+    S = int(g["S"])
+    k = O.bf16_bits_to_f32(g["k"])
+    for gi in range(k.shape[0] // 32):
+        valid = np.arange(32) + 32 * gi >= S
+        yield gi, k[32 * gi:32 * gi + 32], valid
+
+
+def test_plain_kivi_reconstruction_bit_exact(g):
+    for gi, x, valid in _groups(g):
+        e = KO.encode_key_group(x, valid, g["qs"], g["lz"], float(g["qscale"]), ident=True, recip=False)
+        rec = e["codes"].astype(np.float32) * e["s"][None] + e["mn"][None]
+        assert np.array_equal(rec[valid], g["k_rec_ident"][32 * gi:32 * gi + 32][valid]), gi
+    v = O.bf16_bits_to_f32(g["v"])
+    e = KO.encode_values(v, g["co"], ident=True, recip=False)
+    rec = e["codes"].astype(np.float32) * np.repeat(e["s"], 32, -1) + np.repeat(e["mn"], 32, -1)
+    assert np.array_equal(rec, g["v_rec_ident"])
+
+
+def test_dynamic_key_choices_match_simulator(g):
+    mism = n = 0
+    num = den = 0.0
+    for gi, x, valid in _groups(g):
+        e = KO.encode_key_group(x, valid, g["qs"], g["lz"], float(g["qscale"]), recip=False)
+        for h in range(x.shape[1]):
+            n += 1
+            sf, of = bool(g["k_head"][gi, h]), bool(e["choice"][h, 4])
+            if sf != of or (not sf and list(g["k_local"][gi, h]) != list(e["choice"][h, :4])):
+                mism += 1
+        # reconstruction (fp32 meta, original basis) against the simulator's
+        s, mn = e["s"], e["mn"]
+        r = e["codes"].astype(np.float32) * s[None] + mn[None]
+        rh = O.fwht(r, 32)
+        rF = O.fwht(r, 128)
+        ch = e["choice"]
+        rec = np.where(np.repeat(ch[:, :4], 32, -1)[None] == 1, rh, r)
+        rec = np.where((ch[:, 4] == 1)[None, :, None], rF, rec)
+        ref = g["k_rec_dyn"][32 * gi:32 * gi + 32]
+        num += float(((rec - ref)[valid] ** 2).sum())
+        den += float(((ref - x)[valid] ** 2).sum())
+    assert mism <= max(1, n // 50), (mism, n)
+    assert g["k_local"].any() and g["k_head"].any() and not g["k_head"].all()
+    assert num / den < 0.05 * max(1, mism)      # identical when the choices agree (up to fp32 summation order)
+
+
+def test_dynamic_value_choices_match_simulator(g):
+    v = O.bf16_bits_to_f32(g["v"])
+    e = KO.encode_values(v, g["co"], recip=False)
+    r = e["codes"].astype(np.float32) * np.repeat(e["s"], 32, -1) + np.repeat(e["mn"], 32, -1)
+    rec = np.where(np.repeat(e["cand"], 32, -1) == 1, O.fwht(r, 32), r)
+    rec = np.where((e["cand"][..., :1] == 2), O.fwht(r, 128), rec)
+    ref = g["v_rec_dyn"]
+    rel = np.sqrt(((rec - ref) ** 2).sum(-1)) / np.maximum(np.sqrt(((ref - v) ** 2).sum(-1)), 1e-12)
+    assert (rel > 0.2).sum() <= max(1, rel.size // 200), int((rel > 0.2).sum())
+    assert (e["cand"] == 1).any() and (e["cand"] == 2).any() and (e["cand"] == 0).any()
+
+
+def test_pack_parse_round_trip(g):
+    rs = np.random.RandomState(3)
+    H, ng = 2, 3
+    T = 32 * ng
+    pool = rs.randint(0, 256, (2 * ng + 2, H, KO.CB), dtype=np.uint8)
+    perm = rs.permutation(2 * ng + 2)[:2 * ng]
+    pos = np.arange(T)
+    slots = perm[pos // 16] * 16 + pos % 16
+    k = O.bf16_bits_to_f32(g["k"][:T])
+    v = O.bf16_bits_to_f32(g["v"][:T])
+    ev = KO.encode_values(v, g["co"], recip=True)
+    KO.write_values(pool, slots, ev["codes"], ev["meta"], ev["vf"])
+    recs = []
+    for gi in range(ng):
+        valid = np.ones(32, bool)
+        e = KO.encode_key_group(k[32 * gi:32 * gi + 32], valid, g["qs"], g["lz"], float(g["qscale"]), recip=True)
+        KO.write_key_group(pool, slots[32 * gi:32 * gi + 32], valid, e["codes"], e["meta"])
+        recs.append(e)
+    K, V = KO.dequant_groups(pool[perm])
+    # values: dequantised from the stored fp16 meta and inverse-transformed per token
+    s16 = np.abs(ev["meta"][..., 0].astype(np.float64))
+    r = ev["codes"].astype(np.float64) * np.repeat(s16, 32, -1) + np.repeat(ev["meta"][..., 1].astype(np.float64), 32, -1)
+    rec = np.where(np.repeat(ev["cand"], 32, -1) == 1, (r.reshape(T, H, 4, 32) @ O.hadamard(32)).reshape(T, H, 128), r)
+    rec = np.where(ev["cand"][..., :1] == 2, r @ O.hadamard(128), rec)
+    np.testing.assert_allclose(V, rec, rtol=0, atol=1e-9)
+    for gi, e in enumerate(recs):
+        s16 = np.abs(e["meta"][..., 0].astype(np.float64))
+        r = e["codes"].astype(np.float64) * s16[None] + e["meta"][..., 1].astype(np.float64)[None]
+        ch = e["choice"]
+        rec = np.where(np.repeat(ch[:, :4], 32, -1)[None] == 1, (r.reshape(32, H, 4, 32) @ O.hadamard(32)).reshape(32, H, 128), r)
+        rec = np.where((ch[:, 4] == 1)[None, :, None], r @ O.hadamard(128), rec)
+        np.testing.assert_allclose(K[32 * gi:32 * gi + 32], rec, rtol=0, atol=1e-9)
