@@ -1,0 +1,290 @@
+"""GPU parity of the FlagRot-KIVI library (kv_*) through the C ABI.
+
+Contract (the reference's encoder uses contracted FMAs, expf and mapping-dependent sums, and its own tests accept up to 2 %
+differing choices, integrations/vllm_flagrot/tests/test_kivi.py:140,175):
+  * identity-only and frozen-choice modes: pool bytes equal the oracle's (GPU arithmetic) and, where oracle/_ref holds the
+    reference's kivi.cu built for sm_100a, that library's, byte for byte;
+  * dynamic selection: flags agree with the oracle / the reference library on >= 98 % of (group, head) and (token, head)
+    items, and the bytes of the agreeing items are equal;
+  * decode attention: within 1e-2 of max|ref| of float64 attention over the parsed pages + BF16 ring rows (the
+    reference's own bound, test_kivi.py:249), for GQA 4 / 6 / 8, lengths 1 .. 2077, two split plans;
+  * dequantisation kernel == the oracle's parser; LSE merge == the formula evaluated in fp32.
+"""
+import ctypes
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import flagrot_oracle as O
+from oracle import kivi_oracle as KO
+from tests._util import bits, ref_lib
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+D, PAGE, GRP = 128, 16, 32
+
+
+@pytest.fixture(scope="module")
+def KV():
+    from flagrot_releaser_b200 import kivi
+    kivi.lib()
+    return kivi
+
+
+def keys(T, Hkv, g):
+    """post-RoPE-like keys: per-channel offsets (large on a few channels), per-token noise, a few outlier tokens."""
+    mu = torch.randn(Hkv, D, generator=g) * 2.0
+    mu[:, torch.randint(0, D, (6,), generator=g)] *= 6
+    x = mu[None] + torch.randn(T, Hkv, D, generator=g) * (0.5 + torch.rand(Hkv, D, generator=g))
+    x[torch.randint(0, T, (3,), generator=g)] *= 3
+    return x.bfloat16()
+
+
+def calib(Hkv, g, NQ=256):
+    return (torch.randn(Hkv, NQ, D, generator=g) * 0.3, torch.full((Hkv, NQ), 5.0), torch.rand(Hkv, D, generator=g) + 0.1,
+            1 / math.sqrt(D))
+
+
+def setup(T, Hkv, g, S=4):
+    k = keys(T, Hkv, g)
+    v = (keys(T, Hkv, g).float() * 0.3).bfloat16()
+    kv = torch.cat([k, v], 1).contiguous()
+    npg = T // PAGE + 5
+    perm = torch.randperm(npg, generator=g)[:T // PAGE]
+    pos = torch.arange(T)
+    slots = perm[pos // PAGE].long() * PAGE + pos % PAGE
+    ng = T // GRP
+    gp = pos.view(ng, GRP)
+    sidx = torch.where(gp < S, torch.full_like(gp, -1), gp).contiguous()
+    dslot = slots.view(ng, GRP).contiguous()
+    pool0 = torch.randint(0, 256, (npg, Hkv, KO.CB), dtype=torch.uint8, generator=g)
+    return kv, slots, sidx, dslot, pool0, perm
+
+
+def oracle_pool(pool0, kv, slots, sidx, dslot, qs, lz, qsc, co, ident=False, fix=None):
+    exp = pool0.numpy().copy()
+    x = O.bf16_bits_to_f32(bits(kv))
+    Hkv = x.shape[1] // 2
+    ev = KO.encode_values(x[:, Hkv:], co.numpy(), ident=ident, vfix=None if fix is None else fix.numpy(), recip=True)
+    KO.write_values(exp, slots.numpy(), ev["codes"], ev["meta"], ev["vf"])
+    ch = []
+    for n in range(sidx.shape[0]):
+        valid = sidx[n].numpy() != -1
+        e = KO.encode_key_group(x[32 * n:32 * n + 32, :Hkv], valid, qs.numpy(), lz.numpy(), qsc, ident=ident,
+                                kfix=None if fix is None else fix.numpy(), recip=True)
+        KO.write_key_group(exp, dslot[n].numpy(), valid, e["codes"], e["meta"])
+        ch.append(e["choice"])
+    return exp, ev["cand"], np.stack(ch)
+
+
+def run_writers(KV, pool0, kv, slots, sidx, dslot, qs, lz, qsc, co, Hkv, ident=False, fix=None):
+    pool = pool0.clone().to(DEV)
+    kvd = kv.to(DEV)
+    fx = None if fix is None else fix.to(DEV)
+    KV.v_write(kvd, slots.to(DEV), co.to(DEV), None, pool, Hkv, D, ident=ident, fix=fx)
+    KV.k_encode(kvd, sidx.to(DEV), dslot.to(DEV), qs.to(DEV), lz.to(DEV), qsc, pool, Hkv, D, ident=ident, fix=fx)
+    torch.cuda.synchronize()
+    return pool
+
+
+@pytest.mark.parametrize("mode", ["ident", "fixed"])
+def test_writers_exact_modes_vs_oracle(KV, mode):
+    g = torch.Generator().manual_seed(61)
+    Hkv, T = 4, 192
+    qs, lz, co, qsc = calib(Hkv, g)
+    kv, slots, sidx, dslot, pool0, _ = setup(T, Hkv, g)
+    fix = None
+    if mode == "fixed":
+        fix = torch.tensor([0b0101, 0b1 << 16, 0b1111, 0], dtype=torch.int32)
+    exp, _, _ = oracle_pool(pool0, kv, slots, sidx, dslot, qs, lz, qsc, co, ident=mode == "ident", fix=fix)
+    pool = run_writers(KV, pool0, kv, slots, sidx, dslot, qs, lz, qsc, co, Hkv, ident=mode == "ident", fix=fix)
+    got = pool.cpu().numpy()
+    assert np.array_equal(got, exp), int((got != exp).sum())
+
+
+def _flags(pool_np, perm, Hkv):
+    """key flags per (group, head) [ng, H, 5] and value candidates per (token, head) [T, H, 4] read back from the pages."""
+    ch = pool_np[perm.numpy()]
+    npg = ch.shape[0]
+    ng = npg // 2
+    km = np.ascontiguousarray(ch[..., KO.OFF_KM:KO.OFF_VC]).view(np.float16).reshape(npg, Hkv, PAGE, 4, 2)
+    kmg = km.reshape(ng, 2, Hkv, PAGE, 4, 2).transpose(0, 2, 1, 3, 4, 5).reshape(ng, Hkv, D, 2)
+    kf = np.signbit(kmg[..., :5, 0]).astype(int)
+    vm = np.ascontiguousarray(ch[..., KO.OFF_VM:KO.OFF_VF]).view(np.float16).reshape(npg, Hkv, PAGE, 4, 2)
+    vl = np.signbit(vm[..., 0]).astype(int)
+    vF = (ch[..., KO.OFF_VF:KO.OFF_VF + PAGE] != 0)
+    cand = np.where(vF[..., None], 2, vl).transpose(0, 2, 1, 3).reshape(npg * PAGE, Hkv, 4)
+    return kf, cand
+
+
+def test_writers_dynamic_vs_oracle(KV):
+    g = torch.Generator().manual_seed(62)
+    Hkv, T = 8, 512
+    qs, lz, co, qsc = calib(Hkv, g)
+    kv, slots, sidx, dslot, pool0, perm = setup(T, Hkv, g)
+    exp, vcand, kch = oracle_pool(pool0, kv, slots, sidx, dslot, qs, lz, qsc, co)
+    pool = run_writers(KV, pool0, kv, slots, sidx, dslot, qs, lz, qsc, co, Hkv)
+    got = pool.cpu().numpy()
+    kf, cand = _flags(got, perm, Hkv)
+    kexp = kch.copy()
+    kexp[..., :4] = np.where(kch[..., 4:5] == 1, 0, kch[..., :4])          # H32 flags are stored only when the head choice is base
+    k_ok = (kf == kexp).all(-1)
+    v_ok = (cand == vcand).all(-1)
+    assert k_ok.mean() >= 0.98 and v_ok.mean() >= 0.98, (k_ok.mean(), v_ok.mean())
+    assert kch[..., :4].any() and kch[..., 4].any() and (vcand == 1).any() and (vcand == 2).any()
+    # the bytes of the items whose choices agree are equal
+    gch, ech = got[perm.numpy()], exp[perm.numpy()]
+    tok_ok = v_ok.reshape(-1, PAGE, Hkv).transpose(0, 2, 1)                # [page, H, cell]
+    for name, lo, w in (("VC", KO.OFF_VC, 32), ("VM", KO.OFF_VM, 16), ("VF", KO.OFF_VF, 1)):
+        a = gch[..., lo:lo + PAGE * w].reshape(*gch.shape[:2], PAGE, w)
+        b = ech[..., lo:lo + PAGE * w].reshape(*gch.shape[:2], PAGE, w)
+        assert np.array_equal(a[tok_ok], b[tok_ok]), name
+    grp_ok = np.repeat(k_ok, 2, 0)                                         # [page, H]
+    assert np.array_equal(gch[..., :KO.OFF_VC][grp_ok], ech[..., :KO.OFF_VC][grp_ok])
+
+
+def _ref(KV):
+    L = ref_lib("libflagrot_kivi_ref.so")
+    if L is None:
+        pytest.skip("oracle/_ref/libflagrot_kivi_ref.so not built")
+    P, I, LL, F = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float
+    L.kv_v_write.argtypes = [P, LL, I, I, I, P, P, P, P, I, P, I, P]
+    L.kv_k_encode.argtypes = [P, LL, P, LL, P, P, I, I, I, P, P, I, F, P, I, P, I, P]
+    L.kv_attn.argtypes = [P, LL, P, P, LL, P, I, I, I, I, I, I, I, F, P, P, P, I, P, P, P, LL, I, P]
+    return L
+
+
+def ref_writers(L, pool0, kv, slots, sidx, dslot, qs, lz, qsc, co, Hkv, ident=False, fix=None):
+    pool = pool0.clone().to(DEV)
+    kvd, sl, si, ds = kv.to(DEV), slots.to(DEV), sidx.to(DEV), dslot.to(DEV)
+    q_, l_, c_ = qs.to(DEV), lz.to(DEV), co.to(DEV)
+    fx = None if fix is None else fix.to(DEV)
+    st = torch.cuda.current_stream().cuda_stream
+    assert L.kv_v_write(kvd.data_ptr(), kvd.stride(0), kvd.shape[0], Hkv, D, sl.data_ptr(), c_.data_ptr(), None, pool.data_ptr(),
+                        int(ident), None if fx is None else fx.data_ptr(), 0, st) == 0
+    assert L.kv_k_encode(kvd.data_ptr(), kvd.stride(0), None, 0, si.data_ptr(), ds.data_ptr(), si.shape[0], Hkv, D, q_.data_ptr(),
+                         l_.data_ptr(), q_.shape[1], qsc, pool.data_ptr(), int(ident), None if fx is None else fx.data_ptr(), 0,
+                         st) == 0
+    torch.cuda.synchronize()
+    return pool
+
+
+def test_writers_vs_reference_library(KV):
+    L = _ref(KV)
+    g = torch.Generator().manual_seed(63)
+    Hkv, T = 8, 1024
+    qs, lz, co, qsc = calib(Hkv, g)
+    kv, slots, sidx, dslot, pool0, perm = setup(T, Hkv, g)
+    fix = torch.tensor([0b0101, 1 << 16, 0b1111, 0, 0b0011, 1 << 16, 0b1000, 0b0110], dtype=torch.int32)
+    for ident, fx in ((True, None), (False, fix)):
+        a = ref_writers(L, pool0, kv, slots, sidx, dslot, qs, lz, qsc, co, Hkv, ident=ident, fix=fx)
+        b = run_writers(KV, pool0, kv, slots, sidx, dslot, qs, lz, qsc, co, Hkv, ident=ident, fix=fx)
+        assert torch.equal(a, b), (ident, int((a != b).sum()))
+    a = ref_writers(L, pool0, kv, slots, sidx, dslot, qs, lz, qsc, co, Hkv).cpu().numpy()
+    b = run_writers(KV, pool0, kv, slots, sidx, dslot, qs, lz, qsc, co, Hkv).cpu().numpy()
+    kfa, ca = _flags(a, perm, Hkv)
+    kfb, cb = _flags(b, perm, Hkv)
+    k_ok, v_ok = (kfa == kfb).all(-1), (ca == cb).all(-1)
+    assert k_ok.mean() >= 0.99 and v_ok.mean() >= 0.99, (k_ok.mean(), v_ok.mean())
+    ga, gb = a[perm.numpy()], b[perm.numpy()]
+    grp_ok = np.repeat(k_ok, 2, 0)
+    assert np.array_equal(ga[..., :KO.OFF_VC][grp_ok], gb[..., :KO.OFF_VC][grp_ok])
+    tok_ok = v_ok.reshape(-1, PAGE, Hkv).transpose(0, 2, 1)
+    va = ga[..., KO.OFF_VC:KO.OFF_VM].reshape(*ga.shape[:2], PAGE, 32)
+    vb = gb[..., KO.OFF_VC:KO.OFF_VM].reshape(*ga.shape[:2], PAGE, 32)
+    assert np.array_equal(va[tok_ok], vb[tok_ok])
+
+
+@pytest.mark.parametrize("G", [4, 6, 8])
+def test_decode_attention(KV, G):
+    g = torch.Generator().manual_seed(70 + G)
+    Hkv, S, W = 4, 4, 128
+    Ls = (1, 5, 100, 132, 133, 161, 300, 1000, 2077)
+    qs, lz, co, qsc = calib(Hkv, g)
+    B, Lmax, T = len(Ls), max(Ls), S + W
+    npgr = ((Lmax + GRP - 1) // GRP) * 2
+    nb = B * npgr + 5
+    pool = torch.randint(0, 256, (nb, Hkv, KO.CB), dtype=torch.uint8, generator=g).to(DEV)
+    perm = torch.randperm(nb, generator=g)[:B * npgr].view(B, npgr).int()
+    ring = torch.zeros(B + 1, T, 2 * Hkv, D, dtype=torch.bfloat16)
+    q = (torch.randn(B, Hkv * G, D, generator=g) * 0.5).bfloat16()
+    for b, L in enumerate(Ls):
+        k = keys(L, Hkv, g)
+        v = (keys(L, Hkv, g).float() * 0.3).bfloat16()
+        kv = torch.cat([k, v], 1).contiguous()
+        pos = torch.arange(L)
+        slots = perm[b].long()[pos // PAGE] * PAGE + pos % PAGE
+        KV.v_write(kv.to(DEV), slots.to(DEV), co.to(DEV), None, pool, Hkv, D)
+        ngc = L // GRP
+        if ngc:
+            gp = torch.arange(ngc * GRP).view(ngc, GRP)
+            sidx = torch.where(gp < S, torch.full_like(gp, -1), gp).contiguous()
+            dslot = (perm[b].long()[gp // PAGE] * PAGE + gp % PAGE).contiguous()
+            KV.k_encode(kv.to(DEV), sidx.to(DEV), dslot.to(DEV), qs.to(DEV), lz.to(DEV), qsc, pool, Hkv, D)
+        for p in range(L):
+            if p < S:
+                ring[b, p] = kv[p]
+            elif p >= L - W:
+                ring[b, S + (p - S) % W] = kv[p]
+    torch.cuda.synchronize()
+    cached = torch.tensor([L - W if L - W > S else 0 for L in Ls], dtype=torch.int32)
+    tl = torch.tensor([min(L, T) for L in Ls], dtype=torch.int32)
+    ti = torch.arange(B, dtype=torch.int32)
+    scale = 1 / math.sqrt(D)
+    ref = KO.decode_reference(bits(q), pool.cpu().numpy(), perm.numpy(), cached.numpy(), scale, S, G, ring=bits(ring),
+                              tail_len=tl.numpy(), tail_idx=ti.numpy())
+    ns, chunk = KV.plan(B, Lmax, Hkv)
+    for ns_, ch_ in ((ns, chunk), (max(1, (Lmax + 255) // 256), 256)):
+        ws = KV.Workspace(B * Hkv * (ns_ + 1), G, D, DEV)
+        out = torch.zeros(B, Hkv * G * D, dtype=torch.bfloat16, device=DEV)
+        rd = ring.to(DEV)
+        KV.attn(q.to(DEV), pool, perm.to(DEV), cached.to(DEV), out, ns_, ch_, ws, scale * 1.4426950408889634, S, G,
+                ring=rd.view(-1, 2 * Hkv, D), tail_len=tl.to(DEV), tail_idx=ti.to(DEV), T=T)
+        torch.cuda.synchronize()
+        got = out.view(B, Hkv * G, D).double().cpu().numpy()
+        for b in range(B):
+            e = np.abs(got[b] - ref[b]).max() / max(np.abs(ref[b]).max(), 1e-9)
+            assert e <= 1e-2, (G, ns_, ch_, Ls[b], e)
+
+
+def test_dequant_and_lse_merge(KV):
+    g = torch.Generator().manual_seed(81)
+    Hkv, T = 4, 640
+    qs, lz, co, qsc = calib(Hkv, g)
+    kv, slots, sidx, dslot, pool0, perm = setup(T, Hkv, g)
+    pool = run_writers(KV, pool0, kv, slots, sidx, dslot, qs, lz, qsc, co, Hkv)
+    K0, V0 = KO.dequant_groups(pool.cpu().numpy()[perm.numpy()])
+    bt = perm.int().to(DEV)
+    for a, n in ((0, T), (4, 300), (96, 97), (37, T)):
+        k1, v1 = KV.dequant_cuda(pool, bt, a, n, Hkv, D, torch.float32)
+        assert np.abs(k1.cpu().numpy() - K0[a:n]).max() <= 1e-4 * np.abs(K0).max()
+        assert np.abs(v1.cpu().numpy() - V0[a:n]).max() <= 1e-4 * np.abs(V0).max()
+        k2, _ = KV.dequant_cuda(pool, bt, a, n, Hkv, D, torch.bfloat16)
+        assert np.abs(k2.float().cpu().numpy() - K0[a:n]).max() <= 2 ** -7 * np.abs(K0).max()
+    n, H = 77, 6
+    oa = torch.randn(n, H, D, generator=g).bfloat16().to(DEV)
+    ob = torch.randn(n, H, D, generator=g).bfloat16().to(DEV)
+    la = torch.randn(H, n, generator=g).to(DEV)
+    lb = torch.randn(H, n, generator=g).to(DEV)
+    lb[0, :5] = float("-inf")
+    out = torch.empty(n, H, D, dtype=torch.bfloat16, device=DEV)
+    KV.lse_merge(oa, la, ob, lb, out)
+    m = torch.maximum(la, lb)
+    wa, wb = torch.exp(la - m).t()[..., None], torch.exp(lb - m).t()[..., None]
+    exp = ((oa.float() * wa + ob.float() * wb) / (wa + wb)).bfloat16()
+    torch.cuda.synchronize()
+    assert torch.equal(out, exp)
+
+
+def test_error_codes(KV):
+    L = KV.lib()
+    z = torch.zeros(64, dtype=torch.uint8, device=DEV)
+    p = z.data_ptr()
+    assert L.kv_v_write(p, 0, 1, 1, 256, p, p, None, p, 0, None, 0, None) == 2
+    assert b"head dim 128" in L.kv_last_error()
+    assert L.kv_v_write(p, 0, 1, 1, 128, p, p, None, p, 0, None, 1, None) == 2
+    assert L.kv_v_write(p, 0, 0, 1, 128, p, p, None, p, 0, None, 0, None) == 0
+    assert L.kv_attn(p, 0, p, p, 0, p, 0, 1, 1, 9, 128, 1, 256, 1.0, p, p, p, 0, p, p, p, 0, 0, None) == 2
+    assert L.kv_attn(p, 0, p, p, 0, p, 0, 1, 1, 4, 128, 1, 100, 1.0, p, p, p, 0, p, p, p, 0, 0, None) == 2
