@@ -1,0 +1,272 @@
+"""GPU parity of the prefix-cached multi-query prefill path (libflagrot_mq.so through the C ABI) against the float64 oracle
+on the exactly dequantised pages, and against the fixtures made by the reference's own Python.  Request mixes follow the
+reference's kernel-level check (integrations/vllm_flagrot/scripts/bench_mq_prefill.py:99-118, 148-232): pools written by
+the library's own writers (static without / with block + whole-head flags, key-only with per-token flags), shuffled block
+tables, garbage free pages, partial pages / blocks, shift and sink offsets, several requests per launch, G 1 / 4 / 5 / 8.
+Unused block-table entries point at in-range canary pages.
+
+Tolerances: max-abs <= 2e-2 and relative RMS <= 1e-2 (the baseline's statement for attention outputs), plus the tighter
+relative L2 <= 3e-3 and |LSE error| <= 5e-3 that FP16 operands with fp32 accumulation should meet."""
+from __future__ import annotations
+
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import flagrot_oracle as O
+from oracle import mq_oracle as MO
+from _mq_cases import ATTN_CASES, block_table, make_request_pool, rand_kv, rand_q
+from _util import bits, calib
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+SCALE = 1 / math.sqrt(128)
+KINDS = {"rtn": ("int4a", 4, False), "flags": ("int4a", 4, False), "konlya": ("konlya", 4, True),
+         "rtn2": ("int2a", 2, False), "konlya2": ("konlya2", 2, True)}
+
+
+@pytest.fixture(scope="module")
+def libs():
+    from flagrot_releaser_b200 import kernels, prefill_mq
+    kernels.lib()
+    prefill_mq.lib()
+    return kernels, prefill_mq
+
+
+def compare(o, lse, ro, rl, what):
+    fin = np.isfinite(rl)
+    assert np.isneginf(lse[~fin]).all(), (what, "rows without a visible key must report -inf")
+    assert not np.isnan(o).any(), what
+    rows = fin.T[:, :, None]
+    assert np.abs(np.where(~rows, o, 0.0)).max() == 0.0, (what, "rows without a visible key must be zero")
+    o, ro = np.where(rows, o, 0.0), np.where(rows, ro, 0.0)
+    if not fin.any():
+        return
+    err = np.abs(o - ro)
+    rms = math.sqrt((err ** 2).mean()) / max(math.sqrt((ro ** 2).mean()), 1e-30)
+    l2 = np.linalg.norm(o - ro) / max(np.linalg.norm(ro), 1e-30)
+    assert err.max() <= 2e-2, (what, "max-abs", err.max())
+    assert rms <= 1e-2, (what, "relative RMS", rms)
+    assert l2 <= 3e-3, (what, "relative L2", l2)
+    assert np.abs(lse[fin] - rl[fin]).max() <= 5e-3, (what, "lse", np.abs(lse[fin] - rl[fin]).max())
+
+
+def run_mq(MQ, qall, pool, bt, reqs, G, W, S, key_only, int2, kernel, kfull=None, kmask=None, ext=None, waves=None):
+    Hkv = pool.shape[1]
+    plan = MQ.build_plan(reqs, G, Hkv, W, DEV, sink=S, kernel=kernel, ext=ext, waves=waves)
+    q16 = MQ.prep_q(qall, SCALE * MQ.LOG2E, G, idx=plan.idx, kfull=kfull, kmask=kmask)
+    opart, ml = MQ.attn(q16, pool, bt, plan, G, W, konly=key_only, int2=int2)
+    o, lse = MQ.merge(plan, opart, ml, G, fp32=True, want_lse=True)
+    torch.cuda.synchronize()
+    return plan, opart, ml, o, lse
+
+
+@pytest.mark.parametrize("kernel", [1, 3])
+@pytest.mark.parametrize("ci", range(len(ATTN_CASES)))
+def test_reference_fixtures(libs, ci, kernel):
+    """the cases whose expected outputs were computed by the reference's own parsers + float64 attention"""
+    _, MQ = libs
+    case = ATTN_CASES[ci]
+    gold = np.load(__import__("pathlib").Path(__file__).resolve().parent / "golden" / "mq_attn.npz")
+    pool, bt, qb = make_request_pool(case)
+    L, nq, W, S, G = case["L"], case["nq"], case["W"], case["S"], case["G"]
+    q = torch.from_numpy(qb.view(np.int16)).view(torch.bfloat16).to(DEV)
+    _, _, _, o, lse = run_mq(MQ, q, torch.from_numpy(pool).to(DEV), torch.from_numpy(bt)[None].to(DEV), [(0, 0, nq, L, L - nq)], G, W,
+                             S, case["key_only"], case["bits"] == 2, kernel)
+    compare(o.double().cpu().numpy(), lse.double().cpu().numpy(), gold[f"c{ci}_o"].astype(np.float64), gold[f"c{ci}_lse"],
+            (case["kind"], kernel))
+
+
+CASES = [  # (requests [(L, nq)], shift W, sink S, G, Hkv)
+    ([(1000, 1000)], 0, 0, 4, 2),
+    ([(777, 300)], 0, 0, 4, 8),
+    ([(6145, 145)], 0, 0, 4, 2),
+    ([(3000, 1)], 0, 0, 4, 2),
+    ([(17, 17)], 0, 0, 4, 2),
+    ([(16, 5)], 0, 0, 4, 2),
+    ([(64, 64)], 0, 0, 4, 2),
+    ([(2900, 145), (4000, 300), (1503, 17), (700, 700), (5000, 64)], 0, 0, 4, 2),
+    ([(2048, 1024)], 128, 0, 4, 2),
+    ([(130, 70)], 64, 0, 4, 2),
+    ([(4191, 300), (1000, 1000)], 128, 4, 4, 2),
+    ([(140, 140)], 128, 4, 4, 2),
+    ([(3000, 200), (300, 300)], 0, 0, 5, 2),
+    ([(3000, 200), (300, 300)], 0, 0, 8, 2),
+    ([(3000, 200)], 0, 0, 1, 4),
+]
+
+
+def build_case(K, mode, reqs, W, G, Hkv, seed):
+    """pool written by the library's writers; returns device tensors + the oracle's float64 caches per request"""
+    kind, nb, key_only = KINDS[mode]
+    g = torch.Generator().manual_seed(seed)
+    lens = [max(L - W, 1) for L, _ in reqs]
+    bt, total = block_table(lens, g)
+    pool = torch.randint(0, 256, (total, Hkv, O.chunk_bytes(nb, 16)), dtype=torch.uint8, generator=g).to(DEV)
+    btd = bt.to(DEV)
+    mask = hfull = None
+    if mode == "flags":
+        mask = (torch.rand(2 * Hkv, 4, generator=g) < 0.5).to(torch.uint8)
+        hfull = (torch.rand(2 * Hkv, generator=g) < 0.4).to(torch.uint8)
+        hfull[0] = 1
+    Cq, co = calib(Hkv, g)
+    CT = Cq.transpose(1, 2).contiguous().to(DEV)
+    qs, mq, row = [], [], 0
+    for i, (L, nq) in enumerate(reqs):
+        n = lens[i]
+        kv = rand_kv(n, Hkv, g).bfloat16().to(DEV)
+        pos = torch.arange(n)
+        sl = (bt[i].long()[pos // 16] * 16 + pos % 16).to(DEV)
+        if key_only:
+            K.cb_write(kv, sl, CT, co.to(DEV), kind, pool, 16)
+        elif mode == "flags":
+            K.w3_static_write(kv, sl, mask.to(DEV), hfull.to(DEV), pool, 16, fmt=kind)
+        else:
+            K.v2_write(kv, sl, torch.zeros(2 * Hkv, 4, dtype=torch.uint8, device=DEV), 32, pool, 16, fmt=kind)
+        qs.append(rand_q(nq, Hkv * G, g))
+        mq.append((i, row, row + nq, L, L - nq))
+        row += nq
+    torch.cuda.synchronize()
+    return pool, bt, btd, torch.cat(qs), mq, mask, hfull
+
+
+def oracle_case(pool, bt, qall, mq, W, S, G, nb, key_only, mask, hfull, ext=None):
+    pool_np, Hkv = pool.cpu().numpy(), pool.shape[1]
+    outs, lses = [], []
+    for (r, q0, q1, L, s) in mq:
+        e = ext.get(r, MO.NO_EXT) if ext else MO.NO_EXT
+        nk = max(L - W, e + 1, 0)
+        q = O.bf16_bits_to_f32(bits(qall[q0:q1]))
+        with np.errstate(invalid="ignore", over="ignore"):
+            kk, vv = MO.request_cache(pool_np, bt[r].numpy(), max(nk, 1), nb, key_only)
+        kk, vv = kk[:nk], vv[:nk]
+        if mask is not None:      # stored basis: rotate q like the keys; the output stays in the values' stored basis
+            q = MO.prep_q(q, 1.0, G, hfull[:Hkv].numpy(), mask[:Hkv].numpy())
+        o, lse = MO.attention(q, kk, vv, np.arange(s, L), W, SCALE, kmin=S, ext=e)
+        outs.append(o)
+        lses.append(lse)
+    return np.concatenate(outs), np.concatenate(lses, 1)
+
+
+@pytest.mark.parametrize("mode", ["rtn", "flags", "konlya", "rtn2", "konlya2"])
+@pytest.mark.parametrize("kernel", [1, 3])
+def test_request_mixes(libs, mode, kernel):
+    K, MQ = libs
+    kind, nb, key_only = KINDS[mode]
+    todo = CASES if mode in ("rtn", "flags", "konlya") else CASES[1::3]
+    for ci, (reqs, W, S, G, Hkv) in enumerate(todo):
+        if kernel == 1 and ci % 2 and mode != "konlya":
+            continue
+        pool, bt, btd, qall, mq, mask, hfull = build_case(K, mode, reqs, W, G, Hkv, 50 * ci + len(mode))
+        kf = hfull[:Hkv].to(DEV) if hfull is not None else None
+        km = mask[:Hkv].to(DEV) if mask is not None else None
+        plan, opart, ml, o, lse = run_mq(MQ, qall.to(DEV), pool, btd, mq, G, W, S, key_only, nb == 2, kernel, kf, km)
+        ro, rl = oracle_case(pool, bt, qall, mq, W, S, G, nb, key_only, mask, hfull)
+        compare(o.double().cpu().numpy(), lse.double().cpu().numpy(), ro, rl, (mode, kernel, reqs, W, S, G))
+        if mode == "rtn" and W == 0 and S == 0:            # direct bf16 merge into a view of the layer output
+            n = qall.shape[0]
+            ob = torch.zeros(n + 3, Hkv * G * 128 + 64, dtype=torch.bfloat16, device=DEV)
+            MQ.merge(plan, opart, ml, G, out=ob[:, :Hkv * G * 128])
+            torch.cuda.synchronize()
+            got = ob[:n, :Hkv * G * 128].view(n, Hkv * G, 128)
+            assert torch.equal(got, o.to(torch.bfloat16)), "bf16 rows must be the rounded fp32 rows"
+            assert int(ob[n:].abs().sum()) == 0 and int(ob[:, Hkv * G * 128:].abs().sum()) == 0
+
+
+def test_ext_rows_and_many_items(libs):
+    """ext (rows also see page keys <= ext) and a plan forced into many small items"""
+    K, MQ = libs
+    reqs, W, S, G, Hkv = [(1500, 64), (900, 100)], 128, 4, 4, 2
+    pool, bt, btd, qall, mq, _, _ = build_case(K, "konlya", [(L + 0, nq) for L, nq in reqs], 0, G, Hkv, 7)
+    ext = {0: 1480, 1: 500}
+    plan, _, _, o, lse = run_mq(MQ, qall.to(DEV), pool, btd, mq, G, W, S, True, False, 3, ext=ext, waves=40.0)
+    assert plan.nitems > plan.ntiles
+    ro, rl = oracle_case(pool, bt, qall, mq, W, S, G, 4, True, None, None, ext=ext)
+    compare(o.double().cpu().numpy(), lse.double().cpu().numpy(), ro, rl, "ext")
+
+
+def test_rows_without_keys(libs):
+    """shift larger than the early positions: those rows have no visible key (zero output, -inf LSE)"""
+    K, MQ = libs
+    reqs, W, S, G, Hkv = [(100, 100)], 40, 0, 4, 2
+    pool, bt, btd, qall, mq, _, _ = build_case(K, "rtn", reqs, W, G, Hkv, 9)
+    _, _, _, o, lse = run_mq(MQ, qall.to(DEV), pool, btd, mq, G, W, S, False, False, 3)
+    ro, rl = oracle_case(pool, bt, qall, mq, W, S, G, 4, False, None, None)
+    assert np.isneginf(rl[:, :40]).all() and np.isfinite(rl[:, 40:]).all()
+    compare(o.double().cpu().numpy(), lse.double().cpu().numpy(), ro, rl, "empty rows")
+
+
+def test_prep_q_matches_oracle(libs):
+    _, MQ = libs
+    g = torch.Generator().manual_seed(3)
+    Hkv, G, n = 4, 3, 37
+    q = rand_q(n, Hkv * G, g)
+    idx = torch.randperm(n, generator=g)[:20].int()
+    kfull = torch.tensor([1, 0, 1, 0], dtype=torch.uint8)
+    kmask = (torch.rand(Hkv, 4, generator=g) < 0.5).to(torch.uint8)
+    for src in (q, q.float()):
+        base = torch.zeros(n, Hkv * G + 2, 128, dtype=src.dtype)
+        base[:, 1:-1] = src
+        view = base.to(DEV)[:, 1:-1]                        # row stride != Hq * 128
+        got = MQ.prep_q(view, 0.37, G, idx=idx.to(DEV), kfull=kfull.to(DEV), kmask=kmask.to(DEV))
+        ref = MO.prep_q(q.float().numpy()[idx.long().numpy()], 0.37, G, kfull.numpy(), kmask.numpy())
+        np.testing.assert_allclose(got.double().cpu().numpy(), ref, rtol=2e-3, atol=2e-3)
+    plain = MQ.prep_q(q.to(DEV), 1.0, G)
+    assert torch.equal(plain.cpu(), q.to(torch.float16))
+
+
+def test_win_gather_and_bf_merge(libs):
+    _, MQ = libs
+    g = torch.Generator().manual_seed(11)
+    Hkv, G, n, m, S, W = 2, 4, 50, 30, 4, 16
+    Hq = Hkv * G
+    sinkb = torch.randn(7, 2 * Hkv, 128, generator=g).bfloat16()
+    preb = torch.randn(9, 2 * Hkv, 128, generator=g).bfloat16()
+    kch = torch.randn(n, Hkv * 128 + 32, generator=g).bfloat16()
+    vch = torch.randn(n, Hkv * 128, generator=g).bfloat16()
+    kinds = torch.randint(0, 3, (40,), generator=g)
+    rows = torch.stack([torch.randint(0, (7, 9, n)[int(k)], (1,), generator=g)[0] for k in kinds])
+    map_ = (kinds.long() << 32) | rows.long()
+    kw, vw = MQ.win_gather(map_.to(DEV), 40, sinkb.to(DEV), preb.to(DEV), kch.to(DEV)[:, :Hkv * 128], vch.to(DEV), Hkv, 128)
+    rk, rv = MO.win_gather(map_.numpy(), bits(sinkb), bits(preb), bits(kch[:, :Hkv * 128].contiguous()).reshape(n, Hkv, 128),
+                           bits(vch).reshape(n, Hkv, 128), Hkv)
+    assert np.array_equal(bits(kw), rk) and np.array_equal(bits(vw), rv)
+
+    q = rand_q(n, Hq, g)
+    idx = torch.randperm(n, generator=g)[:m].long()
+    o_p = torch.randn(m, Hq, 128, generator=g)
+    lse_p = torch.randn(Hq, m, generator=g) * 2
+    lse_p[:, 3] = -math.inf
+    o_w = torch.randn(m, Hq, 128, generator=g).bfloat16()
+    lse_w = torch.randn(Hq, m, generator=g) * 2
+    lse_w[:, 5] = math.inf
+    sk = torch.randn(3, S, 2 * Hkv, 128, generator=g).bfloat16()
+    row_req = torch.randint(0, 3, (m,), generator=g).long()
+    row_pos = torch.randint(0, 40, (m,), generator=g).long()
+    sk_len = torch.tensor([4, 2, 0]).long()
+    for use_w, use_s in ((True, True), (False, True), (True, False)):
+        out = torch.zeros(n, Hq * 128, dtype=torch.bfloat16, device=DEV)
+        MQ.bf_merge(q.to(DEV), idx.to(DEV), o_p.to(DEV), lse_p.to(DEV), o_w.to(DEV) if use_w else None,
+                    lse_w.to(DEV) if use_w else None, sk.to(DEV) if use_s else None, row_req.to(DEV), row_pos.to(DEV),
+                    sk_len.to(DEV), S if use_s else 0, W, SCALE, out, Hkv)
+        torch.cuda.synchronize()
+        ref = MO.bf_merge(q.float().numpy()[idx.numpy()], o_p.numpy(), lse_p.numpy(), o_w.float().numpy() if use_w else None,
+                          lse_w.numpy() if use_w else None, sk.float().numpy() if use_s else None, row_req.numpy(), row_pos.numpy(),
+                          sk_len.numpy(), S if use_s else 0, W, SCALE, Hkv)
+        got = out.view(n, Hq, 128)[idx.to(DEV)].double().cpu().numpy()
+        np.testing.assert_allclose(got, ref, rtol=1e-2, atol=1e-2)
+        untouched = torch.ones(n, dtype=torch.bool)
+        untouched[idx] = False
+        assert int(out.cpu()[untouched].abs().sum()) == 0
+
+
+def test_refusals(libs):
+    _, MQ = libs
+    L = MQ.lib()
+    assert L.frmq_attn(None, None, 0, None, 0, None, None, 1, 2, 4, 0, 0, None, None, 3, 256, None, 0) == -4
+    assert L.frmq_attn(None, None, 0, None, 0, None, None, 1, 2, 4, 0, 0, None, None, 7, 128, None, 0) == -3
+    assert L.frmq_attn(None, None, 0, None, 0, None, None, 0, 2, 4, 0, 0, None, None, 3, 128, None, 0) == 0
+    assert L.frmq_prep_q(None, 0, 0, None, 1, 8, 4, None, None, 1.0, None, 64, None) == -4
+    assert L.frmq_smem_bytes() > 0
