@@ -24,8 +24,12 @@
 #include <cmath>
 #include <type_traits>
 
+#include <cstdlib>
+#include <cstring>
+
 #include "fr_common.cuh"
 #include "fr_kernels.h"
+#include "fr_tc5.cuh"
 
 namespace fr {
 
@@ -757,12 +761,21 @@ template <int NB, bool KO> int launch_k(const DecodeParams& p, cudaStream_t st) 
   return cudaPeekAtLastError() == cudaSuccess ? 0 : -1;
 }
 
+#include "fr_decode_tc.cuh"
+
+// FLAGROT_DECODE_PATH=tc routes INT4 pages to the tcgen05 kernel (read at every launch; default: the mma.sync kernel)
+bool use_tc() {
+  const char* e = std::getenv("FLAGROT_DECODE_PATH");
+  return e != nullptr && std::strcmp(e, "tc") == 0;
+}
+
 }  // namespace
 
 int decode_launch(const DecodeParams& p, cudaStream_t st) {
   if (p.B <= 0) return 0;
   if (p.page != 16) return -5;
   if (p.chunk <= 0 || p.chunk % 64 != 0 || p.chunk > MAXPG * 16 || p.nsplit < 1) return -3;
+  if (p.nb == 4 && use_tc()) return p.key_only ? launch_tc<4, true>(p, st) : launch_tc<4, false>(p, st);
   if (p.nb == 4) return p.key_only ? launch_k<4, true>(p, st) : launch_k<4, false>(p, st);
   return p.key_only ? launch_k<2, true>(p, st) : launch_k<2, false>(p, st);
 }
@@ -770,7 +783,15 @@ int decode_launch(const DecodeParams& p, cudaStream_t st) {
 int decode_occupancy(int nb, int key_only) {
   int n = 0;
   cudaError_t e;
-  if (nb == 4 && key_only) {
+  if (nb == 4 && use_tc()) {
+    if (key_only) {
+      cudaFuncSetAttribute(k_decode_tc<4, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, TMap<4, 3>::TOTAL);
+      e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, k_decode_tc<4, true>, TC_THREADS, TMap<4, 3>::TOTAL);
+    } else {
+      cudaFuncSetAttribute(k_decode_tc<4, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, TMap<4, 1>::TOTAL);
+      e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, k_decode_tc<4, false>, TC_THREADS, TMap<4, 1>::TOTAL);
+    }
+  } else if (nb == 4 && key_only) {
     cudaFuncSetAttribute(k_decode<4, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMap<4, 3>::TOTAL);
     e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, k_decode<4, true>, 128, SMap<4, 3>::TOTAL);
   } else if (nb == 4) {

@@ -72,7 +72,7 @@ FR_DEVI uint64_t desc_plain(uint32_t saddr, uint32_t lbo, uint32_t sbo) {
 }
 // instruction descriptor: D format (0 f16, 1 f32, 2 s32), A / B formats (kind::f16: 0 f16, 1 bf16; kind::i8: 0 u8, 1 s8),
 // both operands K-major, M x N tile
-constexpr uint32_t idesc(int dfmt, int afmt, int bfmt, int M, int N) {
+__host__ __device__ constexpr uint32_t idesc(int dfmt, int afmt, int bfmt, int M, int N) {
   return (static_cast<uint32_t>(dfmt) << 4) | (static_cast<uint32_t>(afmt) << 7) | (static_cast<uint32_t>(bfmt) << 10) |
          (static_cast<uint32_t>(N >> 3) << 17) | (static_cast<uint32_t>(M >> 4) << 24);
 }
