@@ -46,7 +46,6 @@ constexpr int BLK = 32;            // tokens per warp step
 constexpr int ST = FR_DEC_ST;      // bulk-copy stages per warp
 constexpr int MAXPG = 512;         // pages per split (chunk <= 8192 tokens of 16)
 #define NEG_INF (-INFINITY)
-constexpr int WAIT_LIMIT = 1 << 22;
 
 __device__ int g_status;           // != 0: a bounded wait gave up (value = line of the wait)
 
@@ -60,16 +59,8 @@ FR_DEVI void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t mb
                "l"(src), "r"(bytes), "r"(mbar)
                : "memory");
 }
-FR_DEVI bool mbar_wait(uint32_t a, uint32_t parity) {  // bounded: false after WAIT_LIMIT probes
-  for (int it = 0; it < WAIT_LIMIT; ++it) {
-    uint32_t ok;
-    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
-                 : "=r"(ok)
-                 : "r"(a), "r"(parity)
-                 : "memory");
-    if (ok) return true;
-  }
-  return false;
+FR_DEVI bool mbar_wait(uint32_t a, uint32_t parity) {  // bounded: false after about half a second of SM clock
+  return tc5::mbar_wait(a, parity);
 }
 // D = A * B with a zero accumulator (no register initialisation)
 FR_DEVI void mma_u8s8_z(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {

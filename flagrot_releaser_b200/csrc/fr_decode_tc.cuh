@@ -67,21 +67,15 @@ FR_DEVI float redux_maxf(float x) {   // warp maximum through the order-preservi
   i ^= (i >> 31) & 0x7FFFFFFF;
   return __int_as_float(i);
 }
-// bounded and abortable: false after the limit (sets *abort) or as soon as another thread set *abort
-FR_DEVI bool tc_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort) {
-  for (int i = 0; i < tc5::WAIT_LIMIT; ++i) {
-    uint32_t ok;
-    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
-                 : "=r"(ok)
-                 : "r"(bar), "r"(parity)
-                 : "memory");
-    if (ok) return true;
-    if ((i & 63) == 63 && *abort) return false;
-  }
-  *abort = 1;
-  atomicExch(&g_status, __LINE__);
-  return false;
+// bounded and abortable (tc5::mbar_wait_abortable); the first wait of the kernel that runs out names its line
+FR_DEVI bool tc_wait_at(uint32_t bar, uint32_t parity, volatile uint32_t* abort, int line) {
+  if (tc5::mbar_try(bar, parity)) return true;
+  const bool was = *abort != 0;
+  const bool ok = tc5::mbar_wait_abortable(bar, parity, abort);
+  if (!ok && !was) atomicCAS(&g_status, 0, line);
+  return ok;
 }
+#define tc_wait(bar, parity, abort) tc_wait_at(bar, parity, abort, __LINE__)
 
 template <int NB, bool KO>
 __global__ void __launch_bounds__(TC_THREADS, 2) k_decode_tc(const DecodeParams p) {

@@ -18,7 +18,7 @@
 namespace tc5 {
 
 // ---------------------------------------------------------------------------------------------- mbarrier (bounded)
-constexpr int WAIT_LIMIT = 1 << 22;   // probes of try_wait before a wait gives up (each probe can sleep in hardware)
+constexpr long long WAIT_CYCLES = 1ll << 30;   // SM clock cycles (about half a second) before a wait gives up
 
 FR_DEVI void mbar_init(uint32_t a, int n) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(a), "r"(n)); }
 FR_DEVI void mbar_init_fence() { asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory"); }
@@ -26,16 +26,31 @@ FR_DEVI void mbar_arrive(uint32_t a) { asm volatile("mbarrier.arrive.shared::cta
 FR_DEVI void mbar_expect(uint32_t a, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(a), "r"(bytes) : "memory");
 }
-// false after WAIT_LIMIT probes: the caller records the failure and leaves without touching what it waited for
+FR_DEVI bool mbar_try(uint32_t a, uint32_t parity) {
+  uint32_t ok;
+  asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+               : "=r"(ok)
+               : "r"(a), "r"(parity)
+               : "memory");
+  return ok != 0;
+}
+// false after WAIT_CYCLES: the caller records the failure and leaves without touching what it waited for
 FR_DEVI bool mbar_wait(uint32_t a, uint32_t parity) {
-  for (int i = 0; i < WAIT_LIMIT; ++i) {
-    uint32_t ok;
-    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
-                 : "=r"(ok)
-                 : "r"(a), "r"(parity)
-                 : "memory");
-    if (ok) return true;
+  if (mbar_try(a, parity)) return true;
+  const long long t0 = clock64();
+  while (clock64() - t0 < WAIT_CYCLES)
+    if (mbar_try(a, parity)) return true;
+  return false;
+}
+// the same, ended early when another thread of the CTA has set *abort; a wait that runs out sets *abort itself
+FR_DEVI bool mbar_wait_abortable(uint32_t a, uint32_t parity, volatile uint32_t* abort) {
+  if (mbar_try(a, parity)) return true;
+  const long long t0 = clock64();
+  while (clock64() - t0 < WAIT_CYCLES) {
+    if (mbar_try(a, parity)) return true;
+    if (*abort) return false;
   }
+  *abort = 1;
   return false;
 }
 FR_DEVI void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t mbar) {

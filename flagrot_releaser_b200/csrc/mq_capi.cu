@@ -16,6 +16,7 @@
 #include <cuda_runtime.h>
 
 #include "fr_common.cuh"
+#include "fr_tc5.cuh"
 #include "../../include/flagrot_mq.h"
 
 namespace {
@@ -528,13 +529,21 @@ int launch_mq(const MqParams& p, int nitems, cudaStream_t st) {
   return cudaPeekAtLastError() == cudaSuccess ? 0 : -1;
 }
 
+#include "mq_tc.cuh"
+
 }  // namespace
 
 extern "C" {
 
 int frmq_abi_version() { return 7; }
 const char* frmq_last_error() { return cudaGetErrorString(cudaGetLastError()); }
-int frmq_smem_bytes() { return MSmem<128, 4>::TOTAL; }
+int frmq_smem_bytes() { return TQMap<4, 3>::TOTAL; }
+/* no counterpart in the reference: 0, or the source line of a bounded device-side wait that gave up (sticky) */
+int frmq_device_status() {
+  int v = 0;
+  cudaMemcpyFromSymbol(&v, g_mq_status, sizeof(int));
+  return v;
+}
 
 int frmq_prep_q(const void* q, int q_fp32, long long q_ts, const int* idx, int m, int Hq, int G, const uint8_t* kfull,
                 const uint8_t* kmask, float qscale, void* q16, int Dh, void* stream) {
@@ -559,6 +568,10 @@ int frmq_attn(const void* q16, const uint8_t* pool, long long page_stride, const
   if (kernel == 1) {          // 64 rows per tile
     if (b2) return ko ? launch_mq<64, 2, true>(p, nitems, st) : launch_mq<64, 2, false>(p, nitems, st);
     return ko ? launch_mq<64, 4, true>(p, nitems, st) : launch_mq<64, 4, false>(p, nitems, st);
+  }
+  if (kernel == 3) {          // tcgen05 / tensor memory
+    if (b2) return ko ? launch_mq_tc<2, true>(p, nitems, st) : launch_mq_tc<2, false>(p, nitems, st);
+    return ko ? launch_mq_tc<4, true>(p, nitems, st) : launch_mq_tc<4, false>(p, nitems, st);
   }
   if (b2) return ko ? launch_mq<128, 2, true>(p, nitems, st) : launch_mq<128, 2, false>(p, nitems, st);
   return ko ? launch_mq<128, 4, true>(p, nitems, st) : launch_mq<128, 4, false>(p, nitems, st);

@@ -28,7 +28,7 @@ LOG2E = 1.4426950408889634
 ABI = 7
 KERNEL = int(os.environ.get("FLAGROT_MQ_KERNEL", "3"))
 KROWS = {1: 64, 2: 128, 3: 128}       # query rows per tile
-KCTAS = {1: 3, 2: 2, 3: 2}            # resident CTAs per SM of this build's kernels (shared memory / registers)
+KCTAS = {1: 3, 2: 2, 3: 1}            # resident CTAs per SM of this build's kernels (shared / tensor memory, registers)
 WAVES = float(os.environ.get("FLAGROT_MQ_WAVES", "2"))
 MIN_BLOCKS = int(os.environ.get("FLAGROT_MQ_MIN_BLOCKS", "4"))
 NO_EXT = -(1 << 30)
@@ -54,6 +54,7 @@ def lib():
         raise RuntimeError(f"libflagrot_mq ABI {L.frmq_abi_version()} != {ABI}: rebuild ({path})")
     L.frmq_last_error.restype = ctypes.c_char_p
     L.frmq_smem_bytes.restype = I
+    L.frmq_device_status.restype = I
     L.frmq_prep_q.argtypes = [P, I, LL, P, I, I, I, P, P, F, P, I, P]
     L.frmq_attn.argtypes = [P, P, LL, P, LL, P, P, I, I, I, I, I, P, P, I, I, P, I]
     L.frmq_merge.argtypes = [P, I, P, P, I, I, I, P, LL, I, P, LL, I, P]
@@ -84,6 +85,11 @@ def _stream():
 def _check(rc, what):
     if rc != 0:
         raise RuntimeError(f"{what}: failed (code {rc}, {lib().frmq_last_error().decode()})")
+
+
+def device_status() -> int:
+    """0, or the source line of a bounded device-side wait that gave up (sticky; synchronises the device)."""
+    return int(lib().frmq_device_status())
 
 
 def num_sms(device) -> int:

@@ -4,7 +4,7 @@
  * Drop-in for the library the reference builds from integrations/vllm_flagrot/csrc/mq_prefill.cu and loads through ctypes
  * (integrations/vllm_flagrot/vllm_flagrot/prefill_mq.py:57-86).  Raw DEVICE pointers, the caller's cudaStream_t as void*;
  * asynchronous, allocation-free.  Return 0 ok, -1 launch error, -2 shared memory, -3 bad G / kernel, -4 head dim not 128.
- * kernel 1 = 64 query rows per tile, kernel 2 / 3 = 128 rows per tile (the partial buffers are [nitems, Hkv, rows, 128]).
+ * kernel 1 = 64 query rows per tile (mma.sync), kernel 2 = 128 rows (mma.sync), kernel 3 = 128 rows on tcgen05 / tensor memory (the partial buffers are [nitems, Hkv, rows, 128]).
  */
 #ifndef FLAGROT_MQ_H
 #define FLAGROT_MQ_H
@@ -18,6 +18,9 @@ extern "C" {
 int frmq_abi_version(void);
 const char* frmq_last_error(void);
 int frmq_smem_bytes(void);
+/* no counterpart in the reference: 0, or the source line of a bounded device-side wait that gave up (sticky;
+ * synchronises the device) */
+int frmq_device_status(void);
 
 /* q (bf16, or fp32 when q_fp32; row stride q_ts elements; rows idx[0..m) or 0..m) -> FP16 [m, Hq, 128] in the keys' stored
  * basis (kfull uint8 [Hkv]: whole-head H128 / 8; kmask uint8 [Hkv, 4]: H32 per group; either may be null) times qscale.

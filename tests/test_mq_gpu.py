@@ -67,10 +67,11 @@ def run_mq(MQ, qall, pool, bt, reqs, G, W, S, key_only, int2, kernel, kfull=None
     opart, ml = MQ.attn(q16, pool, bt, plan, G, W, konly=key_only, int2=int2)
     o, lse = MQ.merge(plan, opart, ml, G, fp32=True, want_lse=True)
     torch.cuda.synchronize()
+    assert MQ.device_status() == 0
     return plan, opart, ml, o, lse
 
 
-@pytest.mark.parametrize("kernel", [1, 3])
+@pytest.mark.parametrize("kernel", [1, 2, 3])
 @pytest.mark.parametrize("ci", range(len(ATTN_CASES)))
 def test_reference_fixtures(libs, ci, kernel):
     """the cases whose expected outputs were computed by the reference's own parsers + float64 attention"""
@@ -158,13 +159,13 @@ def oracle_case(pool, bt, qall, mq, W, S, G, nb, key_only, mask, hfull, ext=None
 
 
 @pytest.mark.parametrize("mode", ["rtn", "flags", "konlya", "rtn2", "konlya2"])
-@pytest.mark.parametrize("kernel", [1, 3])
+@pytest.mark.parametrize("kernel", [1, 2, 3])
 def test_request_mixes(libs, mode, kernel):
     K, MQ = libs
     kind, nb, key_only = KINDS[mode]
     todo = CASES if mode in ("rtn", "flags", "konlya") else CASES[1::3]
     for ci, (reqs, W, S, G, Hkv) in enumerate(todo):
-        if kernel == 1 and ci % 2 and mode != "konlya":
+        if kernel in (1, 2) and ci % 2 and mode != "konlya":
             continue
         pool, bt, btd, qall, mq, mask, hfull = build_case(K, mode, reqs, W, G, Hkv, 50 * ci + len(mode))
         kf = hfull[:Hkv].to(DEV) if hfull is not None else None
