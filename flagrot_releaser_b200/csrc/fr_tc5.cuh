@@ -34,12 +34,22 @@ FR_DEVI bool mbar_try(uint32_t a, uint32_t parity) {
                : "memory");
   return ok != 0;
 }
+// one probe that lets the hardware park the warp for up to `ns` nanoseconds (it wakes as soon as the phase completes):
+// a waiting warp then costs no issue slots, unlike a spin of plain probes
+FR_DEVI bool mbar_try_sleep(uint32_t a, uint32_t parity, uint32_t ns) {
+  uint32_t ok;
+  asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n selp.u32 %0, 1, 0, p;\n}\n"
+               : "=r"(ok)
+               : "r"(a), "r"(parity), "r"(ns)
+               : "memory");
+  return ok != 0;
+}
 // false after WAIT_CYCLES: the caller records the failure and leaves without touching what it waited for
 FR_DEVI bool mbar_wait(uint32_t a, uint32_t parity) {
   if (mbar_try(a, parity)) return true;
   const long long t0 = clock64();
   while (clock64() - t0 < WAIT_CYCLES)
-    if (mbar_try(a, parity)) return true;
+    if (mbar_try_sleep(a, parity, 20000u)) return true;
   return false;
 }
 // the same, ended early when another thread of the CTA has set *abort; a wait that runs out sets *abort itself
@@ -47,7 +57,7 @@ FR_DEVI bool mbar_wait_abortable(uint32_t a, uint32_t parity, volatile uint32_t*
   if (mbar_try(a, parity)) return true;
   const long long t0 = clock64();
   while (clock64() - t0 < WAIT_CYCLES) {
-    if (mbar_try(a, parity)) return true;
+    if (mbar_try_sleep(a, parity, 20000u)) return true;
     if (*abort) return false;
   }
   *abort = 1;
@@ -93,6 +103,13 @@ __host__ __device__ constexpr uint32_t idesc(int dfmt, int afmt, int bfmt, int M
 }
 
 // ---------------------------------------------------------------------------------------------- MMA issue (one thread)
+// true in exactly one lane of a converged warp.  Issuing under this predicate (instead of lane == 0) keeps the operands
+// of tcgen05.mma in the uniform datapath: descriptors built from warp-uniform values need no per-instruction transfer.
+FR_DEVI bool elect_one() {
+  uint32_t pred;
+  asm volatile("{\n .reg .pred P;\n elect.sync _|P, 0xffffffff;\n selp.u32 %0, 1, 0, P;\n}\n" : "=r"(pred));
+  return pred != 0;
+}
 // D[tmem] (+)= A[smem] * B[smem]^T; accumulate = 0 overwrites D
 FR_DEVI void mma_f16_ss(uint32_t d, uint64_t a, uint64_t b, uint32_t id, uint32_t accumulate) {
   asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(d), "l"(a),

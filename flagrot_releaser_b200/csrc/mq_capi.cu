@@ -269,6 +269,11 @@ FR_DEVI uint32_t lds16(uint32_t a) {
   asm volatile("ld.shared.u16 %0, [%1];\n" : "=h"(v) : "r"(a));
   return v;
 }
+FR_DEVI uint2 lds64(uint32_t a) {
+  uint2 v;
+  asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];\n" : "=r"(v.x), "=r"(v.y) : "r"(a));
+  return v;
+}
 FR_DEVI uint4 lds128(uint32_t a) {
   uint4 v;
   asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));

@@ -2,15 +2,15 @@
 // with the accumulators, the Q operand and the P operand in tensor memory.  Included by mq_capi.cu inside its anonymous
 // namespace (kernel 3 of frmq_attn); same work list, partial layout and numerics contract as the mma.sync kernel above.
 //
-// CTA = (item, kv head): 128 query rows x the item's 64-key blocks; 14 warps with fixed roles:
-//   warps 0-3   softmax: thread r owns query row r = tensor-memory lane r.  Per block: load the 64 scores, (mask,) running
-//               maximum with a lazy reference (the reference only moves when the maximum grew by more than 2^8, so the
-//               O accumulator is rescaled a few times per item, not per block), p = 2^(s - ref) to FP16 into the P
-//               operand columns, row sum in fp32;
-//   warps 4-11  conversion: raw page chunks -> FP16 operand tiles in shared memory (128-byte swizzle, K-major):
+// CTA = (item, kv head): 128 query rows x the item's 64-key blocks; 24 warps (80 registers each) with fixed roles:
+//   warps 0-3   softmax: thread r owns query row r = tensor-memory lane r.  Per block two passes over the 64 scores (they
+//               are read from tensor memory twice rather than kept in registers): row maximum, then p = 2^(s - ref) into
+//               the P operand columns and the row sum.  The reference is lazy: it only moves when the maximum grew by
+//               more than 2^8 (p stays <= 256), so the O accumulator is rescaled a few times per item, not per block;
+//   warps 4-19  conversion: raw page chunks -> FP16 operand tiles in shared memory (128-byte swizzle, K-major):
 //               K [64 keys][128 dims] as (code - zero point) * scale, exact in FP16, one rounding; V^T [128 dims][64 keys];
-//   warp 12     issues the MMAs (lane 0; the whole warp waits) and owns the tensor-memory allocation;
-//   warp 13     bulk-copies the four page chunks of a block into a 3-stage ring.
+//   warp 20     issues the MMAs (lane 0; the whole warp waits) and owns the tensor-memory allocation;
+//   warp 21     bulk-copies the four page chunks of a block into a 3-stage ring (warps 22, 23 idle).
 // Key-only pages (per-token rotation flags) are not rotated back per token: the kernel keeps Q in three bases (identity,
 // per-group H32, whole-head H128) in tensor memory, the conversion drops each (key, group) into the operand tile of its
 // base and zeros into the other two, and S accumulates the three products - three times the QK tensor work, which the
@@ -20,8 +20,10 @@
 // which every wait returns at once and the CTA runs to its end (results are garbage, the status says so).
 #pragma once
 
-constexpr int TQ_THREADS = 448;
-constexpr int TQ_CONV = 256;          // conversion threads
+constexpr int TQ_THREADS = 768;
+constexpr int TQ_SOFT = 128;          // softmax threads (warps 0 .. 3): one per query row
+constexpr int TQ_CONV = 512;          // conversion threads (warps 4 .. 19)
+constexpr int TQ_WMMA = 20, TQ_WLOAD = 21;
 constexpr int TQ_RAWST = 3;
 __device__ int g_mq_status;
 
@@ -52,83 +54,129 @@ FR_DEVI bool tq_wait_at(uint32_t bar, uint32_t parity, volatile uint32_t* abort,
 }
 #define tq_wait(bar, parity, abort) tq_wait_at(bar, parity, abort, __LINE__)
 
-// K operand tiles of one 64-key block.  item = (key, word): word (tg, j) of the key's 16 code words carries dims
-// 32 j + 4 tg + {0..3} in the low fields and + 16 in the high fields of its four bytes.
+// K operand tiles of one 64-key block.  item = (key, tg pair, group j): the two code words (tg = 2 tgp, 2 tgp + 1) of group j
+// carry dims 32 j + 8 tgp + {0..7} in the low fields and + 16 in the high fields of their bytes -> two 16-byte chunks.
+// Key-only pages: the chunks go to the tile of the (key, group)'s base; the other two tiles must hold zeros there.  A
+// thread meets the same slots of a buffer every second block, so it remembers the base it wrote last (prev, two bits per
+// item and buffer) and only clears that tile when the base changed; the first use of a buffer clears both others.
 template <int NB, bool KO>
-FR_DEVI void tq_convert_k(uint32_t raw, uint32_t kt, int nvalid, int ctid) {
+FR_DEVI void tq_convert_k(uint32_t raw, uint32_t kt, int nvalid, int ctid, bool first, int buf, uint32_t& prev) {
   using L = MLay<NB>;
-  constexpr int NBASE = KO ? 3 : 1;
   constexpr uint32_t FM = NB == 4 ? 0x000F000Fu : 0x00030003u;
 #pragma unroll
-  for (int it = 0; it < (BN * 16) / TQ_CONV; ++it) {
-    const int item = ctid + TQ_CONV * it, tok = item >> 4, tg = (item >> 2) & 3, j = item & 3;
+  for (int it = 0; it < (BN * 8) / TQ_CONV; ++it) {
+    const int item = ctid + TQ_CONV * it, tok = item >> 3, tgp = (item >> 2) & 1, j = item & 3;
     const int pos = tok & 15;
     const uint32_t rc = raw + (tok >> 4) * L::CHUNK;
-    // destination inside a tile: dim half j >> 1, 16-byte chunk 4 (j & 1) + (tg >> 1) (+ 2 for the high fields), 8 (tg & 1)
-    const uint32_t dlo = (j >> 1) * 8192 + tc5::sw128_off(tok, 4 * (j & 1) + (tg >> 1)) + 8 * (tg & 1);
-    const uint32_t dhi = (j >> 1) * 8192 + tc5::sw128_off(tok, 4 * (j & 1) + (tg >> 1) + 2) + 8 * (tg & 1);
-    uint32_t o[4] = {0u, 0u, 0u, 0u};     // lo dims 0 1 | lo dims 2 3 | hi dims 0 1 | hi dims 2 3
+    const uint32_t dlo = (j >> 1) * 8192 + tc5::sw128_off(tok, 4 * (j & 1) + tgp);
+    const uint32_t dhi = (j >> 1) * 8192 + tc5::sw128_off(tok, 4 * (j & 1) + tgp + 2);
+    uint32_t o[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};     // lo: tg even dims 0 1 | 2 3 | tg odd 0 1 | 2 3; then hi alike
     int base = 0;
     if (tok < nvalid) {
-      uint32_t w;
-      if (NB == 4) w = lds32(rc + 64 * pos + 16 * tg + 4 * j);
-      else w = lds32(rc + 32 * (pos ^ ((pos >> 1) & 2)) + 8 * tg + 4 * (j >> 1)) >> (4 * (j & 1));
+      uint32_t w0, w1;
+      if (NB == 4) {
+        w0 = lds32(rc + 64 * pos + 32 * tgp + 4 * j);
+        w1 = lds32(rc + 64 * pos + 32 * tgp + 16 + 4 * j);
+      } else {
+        const uint32_t a = rc + 32 * (pos ^ ((pos >> 1) & 2)) + 16 * tgp + 4 * (j >> 1);
+        w0 = lds32(a) >> (4 * (j & 1));
+        w1 = lds32(a + 8) >> (4 * (j & 1));
+      }
       const uint32_t kw = lds16(rc + L::KS_OFF + 8 * pos + 2 * j);
       const uint32_t zz = ((kw & L::ZM) * 0x00010001u) | 0x64006400u;
       const uint32_t sc = (kw & 0x7FFFu) * 0x00010001u;
-      const uint32_t p01 = prmt(w, 0u, 0x4140u), p23 = prmt(w, 0u, 0x4342u);
-      o[0] = hmul2u(hsub2u((p01 & FM) | 0x64006400u, zz), sc);
-      o[1] = hmul2u(hsub2u((p23 & FM) | 0x64006400u, zz), sc);
-      o[2] = hmul2u(hsub2u(((p01 >> NB) & FM) | 0x64006400u, zz), sc);
-      o[3] = hmul2u(hsub2u(((p23 >> NB) & FM) | 0x64006400u, zz), sc);
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const uint32_t w = u ? w1 : w0;
+        const uint32_t p01 = prmt(w, 0u, 0x4140u), p23 = prmt(w, 0u, 0x4342u);
+        o[2 * u] = hmul2u(hsub2u((p01 & FM) | 0x64006400u, zz), sc);
+        o[2 * u + 1] = hmul2u(hsub2u((p23 & FM) | 0x64006400u, zz), sc);
+        o[4 + 2 * u] = hmul2u(hsub2u(((p01 >> NB) & FM) | 0x64006400u, zz), sc);
+        o[5 + 2 * u] = hmul2u(hsub2u(((p23 >> NB) & FM) | 0x64006400u, zz), sc);
+      }
       if constexpr (KO) {
         const bool ffl = (lds16(rc + L::VS_OFF + 2 * (8 * (pos >> 3) + fr::vslot8(pos))) & 0x8000u) != 0;
         base = ffl ? 2 : static_cast<int>(kw >> 15);
       }
     }
+    if constexpr (KO) {
+      const int sh = 2 * (2 * it + buf);
+      const int old = static_cast<int>((prev >> sh) & 3u);
+      prev = (prev & ~(3u << sh)) | (static_cast<uint32_t>(base) << sh);
+      const uint32_t tb = kt + base * 16384;
+      sts128(tb + dlo, o[0], o[1], o[2], o[3]);
+      sts128(tb + dhi, o[4], o[5], o[6], o[7]);
+      if (first) {
 #pragma unroll
-    for (int b = 0; b < NBASE; ++b) {
-      const bool on = b == base;
-      sts64(kt + b * 16384 + dlo, on ? o[0] : 0u, on ? o[1] : 0u);
-      sts64(kt + b * 16384 + dhi, on ? o[2] : 0u, on ? o[3] : 0u);
+        for (int b = 1; b < 3; ++b) {
+          const uint32_t tz = kt + ((base + b) % 3) * 16384;
+          sts128(tz + dlo, 0u, 0u, 0u, 0u);
+          sts128(tz + dhi, 0u, 0u, 0u, 0u);
+        }
+      } else if (old != base) {
+        const uint32_t tz = kt + old * 16384;
+        sts128(tz + dlo, 0u, 0u, 0u, 0u);
+        sts128(tz + dhi, 0u, 0u, 0u, 0u);
+      }
+    } else {
+      sts128(kt + dlo, o[0], o[1], o[2], o[3]);
+      sts128(kt + dhi, o[4], o[5], o[6], o[7]);
     }
   }
 }
 
-// V^T operand tile [128 dims][64 keys]: item = the 8 tokens of one (page, dim) code word -> one 16-byte chunk
+// V^T operand tile [128 dims][64 keys]: item = (page, entry e, half m): the two code words (r8 = 0, 1) of dims
+// 64 m + 16 w + gid + 8 r8 with the 8 tokens 8 c8 .. + 7 each -> two 16-byte chunks; they share the group's scale words.
 template <int NB>
 FR_DEVI void tq_convert_v(uint32_t raw, uint32_t vt, int nvalid, int ctid) {
   using L = MLay<NB>;
+  constexpr uint32_t NM = NB == 4 ? 0x0F0F0F0Fu : 0x03030303u;
 #pragma unroll
-  for (int it = 0; it < (PPB * 64 * 4) / TQ_CONV; ++it) {
+  for (int it = 0; it < (PPB * 64 * 2) / TQ_CONV; ++it) {
     const int item = ctid + TQ_CONV * it;
-    const int pg = item >> 8, e = (item >> 2) & 63, s = item & 3;
+    const int pg = item >> 7, e = (item >> 1) & 63, m = item & 1;
     const int c8 = e & 1, gid = (e >> 1) & 7, w = e >> 4;
-    const int m = s >> 1, r8 = s & 1;
-    const int d = 64 * m + 16 * w + gid + 8 * r8, j = 2 * m + (w >> 1);
+    const int d0 = 64 * m + 16 * w + gid, j = 2 * m + (w >> 1);
     const uint32_t rc = raw + pg * L::CHUNK;
     const int t0 = 16 * pg + 8 * c8;
-    uint32_t o[4] = {0u, 0u, 0u, 0u};
+    uint32_t o[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
     if (t0 < nvalid) {
-      uint32_t word;
-      if (NB == 4) word = lds32(rc + L::V_OFF + 16 * e + 4 * s);
-      else word = lds32(rc + L::V_OFF + 8 * e + 4 * m) >> (4 * r8);
+      uint32_t wd[2];
+      if (NB == 4) {
+        const uint2 ww = lds64(rc + L::V_OFF + 16 * e + 8 * m);
+        wd[0] = ww.x; wd[1] = ww.y;
+      } else {
+        const uint32_t ww = lds32(rc + L::V_OFF + 8 * e + 4 * m);
+        wd[0] = ww; wd[1] = ww >> 4;
+      }
       const uint4 sw = lds128(rc + L::VS_OFF + 2 * (j * PAGE + 8 * c8));     // scale words of tokens 0 2 4 6 | 1 3 5 7
       const uint32_t sp[4] = {prmt(sw.x, sw.z, 0x5410u), prmt(sw.x, sw.z, 0x7632u), prmt(sw.y, sw.w, 0x5410u), prmt(sw.y, sw.w, 0x7632u)};
+      uint32_t zz[4], sc[4];
 #pragma unroll
       for (int ii = 0; ii < 4; ++ii) {
-        const uint32_t b = (word >> (8 * ii)) & 0xFFu;
-        uint32_t u;
-        if (NB == 4) u = (b & 15u) | ((b >> 4) << 16);
-        else u = (b & 3u) | (((b >> 2) & 3u) << 16);
-        const uint32_t zz = (sp[ii] & (L::ZM | (L::ZM << 16))) | 0x64006400u;
-        uint32_t v = hmul2u(hsub2u(u | 0x64006400u, zz), sp[ii] & 0x7FFF7FFFu);
-        if (t0 + 2 * ii >= nvalid) v &= 0xFFFF0000u;
-        if (t0 + 2 * ii + 1 >= nvalid) v &= 0x0000FFFFu;
-        o[ii] = v;
+        zz[ii] = (sp[ii] & (L::ZM | (L::ZM << 16))) | 0x64006400u;
+        sc[ii] = sp[ii] & 0x7FFF7FFFu;
+      }
+#pragma unroll
+      for (int r8 = 0; r8 < 2; ++r8) {
+        const uint32_t ve = wd[r8] & NM, vo = (wd[r8] >> NB) & NM;     // even tokens | odd tokens, one byte each
+#pragma unroll
+        for (int ii = 0; ii < 4; ++ii) {
+          const uint32_t u = (prmt(ve, vo, 0x0400u + 0x101u * ii) & 0x00FF00FFu) | 0x64006400u;
+          o[4 * r8 + ii] = hmul2u(hsub2u(u, zz[ii]), sc[ii]);
+        }
+      }
+      if (t0 + 8 > nvalid) {      // ragged end of the last block: tokens >= nvalid are zeros
+#pragma unroll
+        for (int q8 = 0; q8 < 8; ++q8) {
+          const int ii = q8 & 3;
+          if (t0 + 2 * ii >= nvalid) o[q8] &= 0xFFFF0000u;
+          if (t0 + 2 * ii + 1 >= nvalid) o[q8] &= 0x0000FFFFu;
+        }
       }
     }
-    sts128(vt + tc5::sw128_off(d, 2 * pg + c8), o[0], o[1], o[2], o[3]);
+    sts128(vt + tc5::sw128_off(d0, 2 * pg + c8), o[0], o[1], o[2], o[3]);
+    sts128(vt + tc5::sw128_off(d0 + 8, 2 * pg + c8), o[4], o[5], o[6], o[7]);
   }
 }
 
@@ -146,7 +194,7 @@ __global__ void __launch_bounds__(TQ_THREADS, 1) k_mq_tc(const MqParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t sb = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem = smem_raw + (sb - smem_u32(smem_raw));
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int tid = threadIdx.x, warp = __shfl_sync(FULLMASK, tid >> 5, 0), lane = tid & 31;   // warp: provably uniform
   const int item = blockIdx.x, h = blockIdx.y;
   const int* itp = p.items + ITEM_INTS * item;
   const int* tl = p.tiles + TILE_INTS * itp[0];
@@ -181,14 +229,14 @@ __global__ void __launch_bounds__(TQ_THREADS, 1) k_mq_tc(const MqParams p) {
     for (int i = 0; i < 2; ++i) {
       tc5::mbar_init(b_kf + 8 * i, TQ_CONV); tc5::mbar_init(b_ke + 8 * i, 1);
       tc5::mbar_init(b_vf + 8 * i, TQ_CONV); tc5::mbar_init(b_ve + 8 * i, 1);
-      tc5::mbar_init(b_sf + 8 * i, 1); tc5::mbar_init(b_pf + 8 * i, 128);
+      tc5::mbar_init(b_sf + 8 * i, 1); tc5::mbar_init(b_pf + 8 * i, TQ_SOFT);
     }
     tc5::mbar_init(b_od, 1);
-    tc5::mbar_init(b_q, 128);
+    tc5::mbar_init(b_q, TQ_SOFT);
     misc[1] = 0;
     tc5::mbar_init_fence();
   }
-  if (warp == 12) {
+  if (warp == TQ_WMMA) {
     tc5::tmem_alloc(sb + S::MISC, 512);
     tc5::tmem_relinquish();
   }
@@ -203,7 +251,7 @@ __global__ void __launch_bounds__(TQ_THREADS, 1) k_mq_tc(const MqParams p) {
   tc5::fence_before_sync();
   __syncthreads();
   tc5::fence_after_sync();
-  const uint32_t tbase = misc[0];
+  const uint32_t tbase = __shfl_sync(FULLMASK, misc[0], 0);
   if constexpr (KO) {       // the two rotated bases: warp per row, lane = 4 dims (fp32 butterflies, one rounding)
     for (int r = warp; r < 128; r += TQ_THREADS / 32) {
       const uint32_t src = sb + r * S::QSTAGE_STRIDE + lane * 8;
@@ -223,10 +271,10 @@ __global__ void __launch_bounds__(TQ_THREADS, 1) k_mq_tc(const MqParams p) {
   const uint8_t* poolh = p.pool + static_cast<long long>(h) * L::CHUNK;
   const int* bt = p.bt + static_cast<long long>(req) * p.bt_stride;
 
-  if (warp < 4) {
+  if (warp < TQ_SOFT / 32) {
     // =========================================================================== softmax warps (thread = query row)
-    const uint32_t lanebase = static_cast<uint32_t>(warp * 32) << 16;
     const int r = tid, t = r / G;
+    const uint32_t lanebase = static_cast<uint32_t>(warp * 32) << 16;
     const bool rval = r < TQr * G && t < ntok;
     const int lim = min(kend - 1, max(pos0 + t - p.shift, ext));
     // Q operand: this thread's row of every base -> tensor memory (64 packed columns per base)
@@ -251,30 +299,28 @@ __global__ void __launch_bounds__(TQ_THREADS, 1) k_mq_tc(const MqParams p) {
       const int sbuf = j & 1, j0 = (kblk0 + j) * BN;
       tq_wait(b_sf + 8 * sbuf, (j >> 1) & 1, abortf);
       tc5::fence_after_sync();
-      uint32_t sv[64];
-      {
-        uint32_t a[32], b2[32];
-        tc5::tmem_ld32(tbase + TQ_S + sbuf * 64 + lanebase, a);
-        tc5::tmem_ld32(tbase + TQ_S + sbuf * 64 + 32 + lanebase, b2);
-        tc5::tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) { sv[i] = a[i]; sv[32 + i] = b2[i]; }
-      }
       const bool full = rval && j0 >= p.kmin && j0 + BN - 1 <= lim;
-      float mx = MQ_NEG_INF;
-      if (full) {
+      const uint32_t ts = tbase + TQ_S + sbuf * 64 + lanebase;
+      // pass 1: row maximum (four independent chains)
+      float m4[4] = {MQ_NEG_INF, MQ_NEG_INF, MQ_NEG_INF, MQ_NEG_INF};
 #pragma unroll
-        for (int i = 0; i < 64; ++i) mx = fmaxf(mx, __uint_as_float(sv[i]));
-      } else {
+      for (int hf = 0; hf < 2; ++hf) {
+        uint32_t sv[32];
+        tc5::tmem_ld32(ts + 32 * hf, sv);
+        tc5::tmem_ld_wait();
+        if (!full) {
 #pragma unroll
-        for (int i = 0; i < 64; ++i) {
-          const int key = j0 + i;
-          const float x = (rval && key >= p.kmin && key <= lim) ? __uint_as_float(sv[i]) : MQ_NEG_INF;
-          sv[i] = __float_as_uint(x);
-          mx = fmaxf(mx, x);
+          for (int i = 0; i < 32; ++i) {
+            const int key = j0 + 32 * hf + i;
+            if (!(rval && key >= p.kmin && key <= lim)) sv[i] = __float_as_uint(MQ_NEG_INF);
+          }
         }
+#pragma unroll
+        for (int i = 0; i < 32; i += 8)
+#pragma unroll
+          for (int c = 0; c < 4; ++c) m4[c] = fmaxf(m4[c], fmaxf(__uint_as_float(sv[i + 2 * c]), __uint_as_float(sv[i + 2 * c + 1])));
       }
-      // lazy reference: move it only when the maximum outgrew it by 2^8 (p stays <= 256, far inside FP16)
+      const float mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
       float alpha = 1.f;
       const bool moved = mx > mref + 8.f || (mref == MQ_NEG_INF && mx > MQ_NEG_INF);
       if (moved) {
@@ -282,15 +328,31 @@ __global__ void __launch_bounds__(TQ_THREADS, 1) k_mq_tc(const MqParams p) {
         mref = mx;
       }
       const float base = mref == MQ_NEG_INF ? 0.f : mref;
-      uint32_t pk[32];
-      float sum = 0.f;
+      // pass 2: p = 2^(s - ref) as packed FP16 straight into the P operand columns; row sum of the rounded values in fp32
+      float s4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        const float p0 = ex2(__uint_as_float(sv[2 * i]) - base), p1 = ex2(__uint_as_float(sv[2 * i + 1]) - base);
-        sum += p0 + p1;
-        pk[i] = pack_h2_rn(p0, p1);
+      for (int hf = 0; hf < 2; ++hf) {
+        uint32_t sv[32];
+        tc5::tmem_ld32(ts + 32 * hf, sv);
+        tc5::tmem_ld_wait();
+        if (!full) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int key = j0 + 32 * hf + i;
+            if (!(rval && key >= p.kmin && key <= lim)) sv[i] = __float_as_uint(MQ_NEG_INF);
+          }
+        }
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const float x0 = __uint_as_float(sv[2 * i]) - base, x1 = __uint_as_float(sv[2 * i + 1]) - base;
+          const float p0 = ex2(x0), p1 = ex2(x1);
+          s4[i & 3] += p0 + p1;
+          pk[i] = pack_h2_rn(p0, p1);
+        }
+        tc5::tmem_st16(tbase + TQ_P + sbuf * 32 + 16 * hf + lanebase, pk);
       }
-      lsum = lsum * alpha + sum;
+      lsum = lsum * alpha + ((s4[0] + s4[1]) + (s4[2] + s4[3]));
       // rescale of O (warp-collective) before P is released: the PV of the previous block must have landed
       if (j > 0 && __any_sync(FULLMASK, moved)) {
         tq_wait(b_od, (j - 1) & 1, abortf);
@@ -305,7 +367,6 @@ __global__ void __launch_bounds__(TQ_THREADS, 1) k_mq_tc(const MqParams p) {
           tc5::tmem_st32(tbase + TQ_O + c0 + lanebase, o);
         }
       }
-      tc5::tmem_st32(tbase + TQ_P + sbuf * 32 + lanebase, pk);
       tc5::tmem_st_wait();
       tc5::fence_before_sync();
       tc5::mbar_arrive(b_pf + 8 * sbuf);
@@ -333,26 +394,34 @@ __global__ void __launch_bounds__(TQ_THREADS, 1) k_mq_tc(const MqParams p) {
       if (rval) *reinterpret_cast<float2*>(p.ml + (pbase + r) * 2) = make_float2(mref, lsum);
     }
     tc5::fence_before_sync();
-  } else if (warp < 12) {
+  } else if (warp < (TQ_SOFT + TQ_CONV) / 32) {
     // =========================================================================== conversion warps
-    const int ctid = tid - 128;
+    const int ctid = tid - TQ_SOFT;
     tq_wait(b_q, 0, abortf);          // the q staging (which lies over the operand tiles) has been read
-    for (int j = 0; j < nblk; ++j) {
+    uint32_t prev = 0;
+    // K runs one block ahead of V: K(j + 1) only needs QK(j - 1) to be done, while V(j) has to wait for PV(j - 2), which
+    // hangs on the softmax - so the next scores can be under way while the softmax still holds the V tile back
+    auto conv_k = [&](int j) {
       const int buf = j & 1, rs = j % TQ_RAWST;
-      const uint32_t raw = sb + S::RAW + rs * S::RAW_STAGE;
-      const int nvalid = kend - (kblk0 + j) * BN;
       tq_wait(b_rawf + 8 * rs, (j / TQ_RAWST) & 1, abortf);
       if (j >= 2) tq_wait(b_ke + 8 * buf, ((j >> 1) - 1) & 1, abortf);
-      tq_convert_k<NB, KO>(raw, sb + S::KT + buf * NBASE * S::KT_TILE, nvalid, ctid);
-      tc5::fence_async_smem();
-      tc5::mbar_arrive(b_kf + 8 * buf);
+      tq_convert_k<NB, KO>(sb + S::RAW + rs * S::RAW_STAGE, sb + S::KT + buf * NBASE * S::KT_TILE, kend - (kblk0 + j) * BN, ctid,
+                           j < 2, buf, prev);
+    };
+    conv_k(0);
+    tc5::fence_async_smem();
+    tc5::mbar_arrive(b_kf);
+    for (int j = 0; j < nblk; ++j) {
+      const int buf = j & 1, rs = j % TQ_RAWST;
+      if (j + 1 < nblk) conv_k(j + 1);
       if (j >= 2) tq_wait(b_ve + 8 * buf, ((j >> 1) - 1) & 1, abortf);
-      tq_convert_v<NB>(raw, sb + S::VT + buf * 16384, nvalid, ctid);
-      tc5::fence_async_smem();
+      tq_convert_v<NB>(sb + S::RAW + rs * S::RAW_STAGE, sb + S::VT + buf * 16384, kend - (kblk0 + j) * BN, ctid);
+      tc5::fence_async_smem();                 // one fence for the K tile of the next block and the V tile of this one
+      if (j + 1 < nblk) tc5::mbar_arrive(b_kf + 8 * (buf ^ 1));
       tc5::mbar_arrive(b_vf + 8 * buf);
       tc5::mbar_arrive(b_rawe + 8 * rs);
     }
-  } else if (warp == 12) {
+  } else if (warp == TQ_WMMA) {
     // =========================================================================== MMA issue (the warp waits, lane 0 issues)
     constexpr uint32_t id_qk = tc5::idesc(1, 0, 0, 128, BN), id_pv = tc5::idesc(1, 0, 0, 128, 128);
     tq_wait(b_q, 0, abortf);
@@ -362,7 +431,7 @@ __global__ void __launch_bounds__(TQ_THREADS, 1) k_mq_tc(const MqParams p) {
       tq_wait(b_pf + 8 * buf, (i >> 1) & 1, abortf);
       tq_wait(b_vf + 8 * buf, (i >> 1) & 1, abortf);
       tc5::fence_after_sync();
-      if (lane == 0) {
+      if (tc5::elect_one()) {
         const uint32_t vt = sb + S::VT + buf * 16384;
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
@@ -376,7 +445,7 @@ __global__ void __launch_bounds__(TQ_THREADS, 1) k_mq_tc(const MqParams p) {
       const int buf = j & 1;
       tq_wait(b_kf + 8 * buf, (j >> 1) & 1, abortf);
       tc5::fence_after_sync();
-      if (lane == 0) {
+      if (tc5::elect_one()) {
         const uint32_t kt = sb + S::KT + buf * NBASE * S::KT_TILE;
 #pragma unroll
         for (int b = 0; b < NBASE; ++b)
@@ -391,7 +460,7 @@ __global__ void __launch_bounds__(TQ_THREADS, 1) k_mq_tc(const MqParams p) {
       if (j > 0) pv(j - 1);
     }
     pv(nblk - 1);
-  } else {
+  } else if (warp == TQ_WLOAD) {
     // =========================================================================== page loader (the warp waits, lane 0 copies)
     for (int j = 0; j < nblk; ++j) {
       const int rs = j % TQ_RAWST, kb = kblk0 + j;
@@ -408,7 +477,7 @@ __global__ void __launch_bounds__(TQ_THREADS, 1) k_mq_tc(const MqParams p) {
   }
   tc5::fence_before_sync();
   __syncthreads();
-  if (warp == 12) tc5::tmem_dealloc(tbase, 512);
+  if (warp == TQ_WMMA) tc5::tmem_dealloc(tbase, 512);
 }
 
 template <int NB, bool KO>

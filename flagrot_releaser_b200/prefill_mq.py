@@ -130,8 +130,27 @@ class Plan:
         return self.buf[a:a + self.m]
 
 
-def plan_arrays(reqs, G: int, Hkv: int, shift: int, nsm: int, kernel: int, waves: float, min_blocks: int, ext=None):
-    """The plan as host arrays (tiles [nt, 9], items [ni, 4], idx [m]); pure numpy, no device."""
+def _balanced_split(blocks, Hkv: int, nsm: int, ctas_per_sm: int, min_blocks: int, start: int) -> int:
+    """key blocks per item that minimise the estimated makespan: CTAs are dealt to nsm * ctas_per_sm slots in waves, an
+    item costs its blocks plus a fixed start-up of about three blocks (q staging, pipeline fill, partial store)."""
+    slots = nsm * ctas_per_sm
+    top = int(blocks.max()) if blocks.size else 1
+    best, best_cost = start, None
+    for parts in range(1, 33):
+        per = max(min_blocks, -(-top // parts))
+        n = int(np.maximum(1, -(-blocks // per)).sum()) * Hkv
+        cost = -(-n // slots) * (min(per, top) + 3)
+        if best_cost is None or cost < best_cost:
+            best, best_cost = per, cost
+        if per == min_blocks:
+            break
+    return best
+
+
+def plan_arrays(reqs, G: int, Hkv: int, shift: int, nsm: int, kernel: int, waves: float, min_blocks: int, ext=None,
+                balance: bool = False):
+    """The plan as host arrays (tiles [nt, 9], items [ni, 4], idx [m]); pure numpy, no device.  balance=False is the
+    reference's split rule; balance=True picks the split that fills whole waves of CTAs."""
     rows = KROWS[kernel]
     tq = rows // G
     tile_rows, last_key, idx = [], [], []
@@ -149,6 +168,8 @@ def plan_arrays(reqs, G: int, Hkv: int, shift: int, nsm: int, kernel: int, waves
     blocks = -(-np.asarray(last_key, dtype=np.int64) // BN)
     target = max(int(waves * KCTAS[kernel] * nsm), 1)
     per_item = max(min_blocks, -(-int(blocks.sum()) * Hkv // target))           # key blocks per work item
+    if balance:
+        per_item = _balanced_split(blocks, Hkv, nsm, KCTAS[kernel], min_blocks, per_item)
     nitem = np.maximum(1, -(-blocks // per_item)).astype(np.int64)
     first = np.cumsum(nitem) - nitem
     tiles[:, 6] = first
@@ -162,15 +183,19 @@ def plan_arrays(reqs, G: int, Hkv: int, shift: int, nsm: int, kernel: int, waves
 
 
 def build_plan(reqs, G: int, Hkv: int, shift: int, device, sink: int = 0, kernel: int | None = None,
-               waves: float | None = None, min_blocks: int | None = None, D: int = D, ext: dict | None = None) -> Plan:
+               waves: float | None = None, min_blocks: int | None = None, D: int = D, ext: dict | None = None,
+               balance: bool | None = None) -> Plan:
     """reqs: list of (block-table row r, q0, q1, L, s): batch rows q0 .. q1 - 1 are positions s .. L - 1 of request r.
     The query at position i sees the page keys sink <= j <= max(i - shift, ext[r]).  The split size is chosen so that
-    the grid has about waves x resident CTAs x SMs CTAs, with at least min_blocks 64-key blocks per item."""
+    the grid has about waves x resident CTAs x SMs CTAs, with at least min_blocks 64-key blocks per item; balance
+    (default: on unless waves is given) instead picks the split whose CTAs fill whole waves of the GPU."""
     if D != 128:
         raise RuntimeError(f"build_plan: head size {D} is not built for B200 (128 only)")
     kernel = KERNEL if kernel is None else kernel
+    balance = (waves is None) if balance is None else balance
     tiles, items, idx, m = plan_arrays(reqs, G, Hkv, shift, num_sms(device), kernel,
-                                       WAVES if waves is None else waves, MIN_BLOCKS if min_blocks is None else min_blocks, ext)
+                                       WAVES if waves is None else waves, MIN_BLOCKS if min_blocks is None else min_blocks, ext,
+                                       balance)
     host = np.concatenate([tiles.reshape(-1), items.reshape(-1), idx]).astype(np.int32)
     return Plan(ntiles=tiles.shape[0], nitems=items.shape[0], m=m, buf=torch.from_numpy(host).to(device), reqs=list(reqs),
                 kernel=kernel, rows=KROWS[kernel], D=D, kmin=int(sink))

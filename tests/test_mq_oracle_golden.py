@@ -48,7 +48,7 @@ def test_build_plan_cpu_buffer(plans, monkeypatch):
     monkeypatch.setattr(MQ, "KCTAS", REF_KCTAS)
     monkeypatch.setitem(MQ._NSM, "cpu", 132)
     reqs, G, Hkv, shift, sink, ext = PLAN_CASES[-1]
-    p = MQ.build_plan(reqs, G, Hkv, shift, "cpu", sink=sink, kernel=3, ext=ext)
+    p = MQ.build_plan(reqs, G, Hkv, shift, "cpu", sink=sink, kernel=3, ext=ext, balance=False)
     key = f"c{len(PLAN_CASES) - 1}_s132_k3"
     assert p.buf.dtype == torch.int32 and p.kmin == sink and p.rows == 128 and p.kernel == 3
     np.testing.assert_array_equal(p.tiles.numpy().reshape(-1, 9), plans[key + "_tiles"])
@@ -61,7 +61,8 @@ def test_build_plan_cpu_buffer(plans, monkeypatch):
 def test_plan_covers_every_visible_key():
     """every tile's items tile [0, ceil(last visible key / 64)) without gaps or overlap"""
     for reqs, G, Hkv, shift, sink, ext in PLAN_CASES:
-        tiles, items, _, _ = MQ.plan_arrays(reqs, G, Hkv, shift, 148, 3, 2.0, 4, ext)
+      for balance in (False, True):
+        tiles, items, _, _ = MQ.plan_arrays(reqs, G, Hkv, shift, 148, 3, 2.0, 4, ext, balance)
         for ti, tl in enumerate(tiles):
             own = items[tl[6]:tl[6] + tl[7]]
             assert (own[:, 0] == ti).all() and own[0, 1] == 0
