@@ -86,7 +86,7 @@ __global__ void __launch_bounds__(TC_THREADS, 2) k_decode_tc(const DecodeParams 
   constexpr int NS = S::NS;
   extern __shared__ __align__(128) uint8_t smem[];
   __shared__ int last_flag;
-  const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+  const int tid = threadIdx.x, lane = tid & 31, w = __shfl_sync(FULLMASK, tid >> 5, 0);   // w: provably warp-uniform
   const int NT = (p.G + 3) >> 2;
   const int kvh = blockIdx.x / NT, qt = blockIdx.x % NT, split = blockIdx.y, b = blockIdx.z;
   const int has_tail = p.tail != nullptr;
@@ -138,7 +138,7 @@ __global__ void __launch_bounds__(TC_THREADS, 2) k_decode_tc(const DecodeParams 
   tc5::fence_before_sync();
   __syncthreads();
   tc5::fence_after_sync();
-  const uint32_t tbase = misc[0];
+  const uint32_t tbase = __shfl_sync(FULLMASK, misc[0], 0);
   const uint32_t tS = tbase, tO = tbase + 4 * NS;
 
   const uint8_t* poolh = p.pool + static_cast<size_t>(kvh) * L::CHUNK;
@@ -230,13 +230,16 @@ __global__ void __launch_bounds__(TC_THREADS, 2) k_decode_tc(const DecodeParams 
     tc5::fence_async_smem();
     tc5::fence_before_sync();
     bar_tokens();
-    if (tid == 0) {
+    if (w == 0) {                 // issued under elect.sync: the operands stay in the uniform datapath
       tc5::fence_after_sync();
+      if (tc5::elect_one()) {
 #pragma unroll
-      for (int g = 0; g < 4; ++g)
-        tc5::mma_i8_ss(tS + g * NS, tc5::desc_plain(sb + S::KA + g * 4096, 128, 256),
-                       tc5::desc_plain(sb + S::QB + g * NS * 32, 128, 256), id_qk, 0);
-      tc5::mma_commit(mb_qk);
+        for (int g = 0; g < 4; ++g)
+          tc5::mma_i8_ss(tS + g * NS, tc5::desc_plain(sb + S::KA + g * 4096, 128, 256),
+                         tc5::desc_plain(sb + S::QB + g * NS * 32, 128, 256), id_qk, 0);
+        tc5::mma_commit(mb_qk);
+      }
+      __syncwarp();
     }
     // ---- under the QK: fold of the previous step, then the V mask pass (the V and P' tiles are free once that PV is done)
     if (s > 0) fold(s - 1);
@@ -346,13 +349,16 @@ __global__ void __launch_bounds__(TC_THREADS, 2) k_decode_tc(const DecodeParams 
     }
     tc5::fence_async_smem();
     bar_tokens();
-    if (tid == 0) {
+    if (w == 0) {
       tc5::fence_after_sync();
+      if (tc5::elect_one()) {
 #pragma unroll
-      for (int sl = 0; sl < 4; ++sl)
-        tc5::mma_i8_ss(tO, tc5::desc_plain(sb + S::VA + sl * 4096, 128, 256), tc5::desc_plain(sb + S::PB + sl * 1024, 128, 256),
-                       id_pv, sl > 0);
-      tc5::mma_commit(mb_pv);
+        for (int sl = 0; sl < 4; ++sl)
+          tc5::mma_i8_ss(tO, tc5::desc_plain(sb + S::VA + sl * 4096, 128, 256), tc5::desc_plain(sb + S::PB + sl * 1024, 128, 256),
+                         id_pv, sl > 0);
+        tc5::mma_commit(mb_pv);
+      }
+      __syncwarp();
     }
   }
   fold(nsteps - 1);

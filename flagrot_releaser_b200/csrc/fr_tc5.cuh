@@ -34,32 +34,28 @@ FR_DEVI bool mbar_try(uint32_t a, uint32_t parity) {
                : "memory");
   return ok != 0;
 }
-// one probe that lets the hardware park the warp for up to `ns` nanoseconds (it wakes as soon as the phase completes):
-// a waiting warp then costs no issue slots, unlike a spin of plain probes
-FR_DEVI bool mbar_try_sleep(uint32_t a, uint32_t parity, uint32_t ns) {
-  uint32_t ok;
-  asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n selp.u32 %0, 1, 0, p;\n}\n"
-               : "=r"(ok)
-               : "r"(a), "r"(parity), "r"(ns)
-               : "memory");
-  return ok != 0;
-}
-// false after WAIT_CYCLES: the caller records the failure and leaves without touching what it waited for
+// false after WAIT_CYCLES: the caller records the failure and leaves without touching what it waited for.  The clock is
+// read once per 32 probes: a waiting warp should cost as few issue slots as possible.
 FR_DEVI bool mbar_wait(uint32_t a, uint32_t parity) {
   if (mbar_try(a, parity)) return true;
   const long long t0 = clock64();
-  while (clock64() - t0 < WAIT_CYCLES)
-    if (mbar_try_sleep(a, parity, 20000u)) return true;
+  do {
+#pragma unroll 1
+    for (int i = 0; i < 32; ++i)
+      if (mbar_try(a, parity)) return true;
+  } while (clock64() - t0 < WAIT_CYCLES);
   return false;
 }
 // the same, ended early when another thread of the CTA has set *abort; a wait that runs out sets *abort itself
 FR_DEVI bool mbar_wait_abortable(uint32_t a, uint32_t parity, volatile uint32_t* abort) {
   if (mbar_try(a, parity)) return true;
   const long long t0 = clock64();
-  while (clock64() - t0 < WAIT_CYCLES) {
-    if (mbar_try_sleep(a, parity, 20000u)) return true;
+  do {
+#pragma unroll 1
+    for (int i = 0; i < 32; ++i)
+      if (mbar_try(a, parity)) return true;
     if (*abort) return false;
-  }
+  } while (clock64() - t0 < WAIT_CYCLES);
   *abort = 1;
   return false;
 }
