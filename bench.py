@@ -41,6 +41,10 @@ WORKLOADS = {
     # Qwen3-8B-shaped INT2 FlagRot decode, batch 256 x 8192 (per-GPU batch = 256 / n when sharded)
     "cfg3": dict(kind="konlya2", nb=2, B=256, L=8192, Hq=32, Hkv=8, S=4, W=128, center=True,
                  name="qwen3-8b-shaped int2 konlya2 decode, batch 256 x ctx 8192, page 16, s4w128, centred keys"),
+    # one very long sequence, INT4 konlya, context 131072: the KV sequence is sharded over the ranks, every rank emits
+    # (o, m, l) rows (fr_attn_partial), an NCCL all-gather of 130 floats per (row, head) and the LSE merge finish the step
+    "cfg5b": dict(kind="konlya", nb=4, B=1, L=131072, Hq=32, Hkv=8, S=4, W=128, center=False, shard="kvseq",
+                  name="int4 konlya decode, batch 1 x ctx 131072, page 16, s4w128, KV-sequence sharded"),
 }
 
 
@@ -104,13 +108,16 @@ class ClockSampler:
 
 
 # ---------------------------------------------------------------------------------------------- workload state
-def make_state(w, B, dev, seed, ncopy):
+def make_state(w, B, dev, seed, ncopy, rank=0, world=1):
     """synthetic inputs of the named shape and the quantised caches (written by the library's own dynamic writer, which
     the parity tests hold bit-exact).  ncopy distinct pools (distinct random page tables over distinct memory) are cycled
     so that no page is L2-resident between steps."""
     from flagrot_releaser_b200 import kernels as K
     g = torch.Generator().manual_seed(seed)
     Hkv, Hq, L = w["Hkv"], w["Hq"], w["L"]
+    kvseq = w.get("shard") == "kvseq"
+    if kvseq:                                   # this rank's slice of the page tokens [0, L - W); window rows stay BF16
+        L = kvseq_local_len(w["L"], w["W"], world)
     npages_seq = L // P
     npool = B * npages_seq + 7
     qs = torch.randn(Hkv, 512, 128, generator=g) * (torch.rand(Hkv, 1, 128, generator=g) + 0.5).sqrt()
@@ -154,6 +161,10 @@ def make_state(w, B, dev, seed, ncopy):
               out=torch.empty(B, Hq * 128, dtype=torch.bfloat16, device=dev))
     st["q"] = st["q_host"].to(dev)
     st["kv"] = st["kv_host"].to(dev)
+    st["Lloc"], st["rank"], st["world"] = L, rank, world
+    if kvseq:
+        st["part"] = torch.zeros(B, Hq, 130, dtype=torch.float32, device=dev)
+        st["parts"] = torch.zeros(world, B, Hq, 130, dtype=torch.float32, device=dev)
     # the appended token of every sequence goes to position L - W - 1 of its row (a scattered slot per sequence)
     st["slots"] = [(bt.long()[:, (L - w["W"] - 1) // P] * P + (L - w["W"] - 1) % P).contiguous() for bt in bts]
     st["slots_host"] = [s.cpu().pin_memory() for s in st["slots"]]
@@ -162,7 +173,7 @@ def make_state(w, B, dev, seed, ncopy):
 
 def plan(st, nsplit):
     K, w = st["K"], st["w"]
-    ns, ch = K.plan_cb(st["B"], w["L"] - w["W"], w["Hkv"], P, w["kind"], nsplit)
+    ns, ch = K.plan_cb(st["B"], st["Lloc"] - w["W"], w["Hkv"], P, w["kind"], nsplit)
     st["plan"] = (ns, ch)
     st["ws"] = K.Workspace(st["B"], w["Hkv"], st["B"] * w["Hkv"] * (ns + 1), st["pools"][0].device)
 
@@ -186,6 +197,35 @@ def step(st, i, e2e=False):
         torch.cuda.current_stream().synchronize()
 
 
+def step_kvseq(st, i, e2e=False, dist=None):
+    """KV-sequence sharded step: the last rank appends the new token, every rank attends over its slice (rank 0 also over
+    the BF16 sink / window rows), partial rows are all-gathered (NCCL) and merged."""
+    K, w = st["K"], st["w"]
+    c = i % len(st["pools"])
+    pool, bt = st["pools"][c], st["bts"][c]
+    ns, ch = st["plan"]
+    first, last = st["rank"] == 0, st["rank"] == st["world"] - 1
+    if e2e:
+        st["q"].copy_(st["q_host"], non_blocking=True)
+        if last:
+            st["kv"].copy_(st["kv_host"], non_blocking=True)
+            st["slots"][c].copy_(st["slots_host"][c], non_blocking=True)
+    if last:
+        K.cb_write(st["kv"], st["slots"][c], st["CT"], st["co"], w["kind"], pool, P, kmu=st["kmu"])
+    ring = st["ring"]
+    tkw = dict(tail=ring, tail_len=st["tail_len"], tail_idx=None, tail_bs=ring.stride(0), tail_ts=ring.stride(1)) if first else {}
+    K.attn_partial(st["q"], pool, bt, st["seq"], st["part"], ns, ch, st["ws"], LOG2E / math.sqrt(128), w["kind"], page=P,
+                   kv_start=w["S"] if first else 0, **tkw)
+    if dist is not None:
+        dist.all_gather_into_tensor(st["parts"].view(-1, *st["part"].shape[1:]), st["part"])   # concatenated along dim 0
+        K.merge_partials_into(st["parts"], st["out"])
+    else:
+        K.merge_partials_into(st["part"][None], st["out"])
+    if e2e:
+        st["out_host"].copy_(st["out"], non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+
 def decode_only(st, i):
     K, w = st["K"], st["w"]
     c = i % len(st["pools"])
@@ -194,6 +234,21 @@ def decode_only(st, i):
     K.cb_attn(st["q"], st["pools"][c], st["bts"][c], st["seq"], st["out"], ns, ch, st["ws"], LOG2E / math.sqrt(128), w["kind"],
               tail=ring, tail_len=st["tail_len"], tail_idx=None, tail_bs=ring.stride(0), tail_ts=ring.stride(1), page=P,
               kv_start=w["S"])
+
+
+def kvseq_local_len(L, W, world):
+    """context length of one rank when the page tokens [0, L - W) of a sequence are split evenly over `world` ranks (every
+    rank keeps the W window rows in its count, as the single-GPU convention does)."""
+    return (L - W) // world + W
+
+
+def max_over_ranks(ms, dist, device):
+    """the slowest rank's time (all-reduce MAX), identical on every rank"""
+    if dist is None:
+        return ms
+    t = torch.tensor([ms], dtype=torch.float32, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
 
 
 def timed(fn, steps, warmup, dist=None):
@@ -211,10 +266,8 @@ def timed(fn, steps, warmup, dist=None):
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1)
     if dist is not None:
-        t = torch.tensor([ms], device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = max_over_ranks(ms, dist, "cuda")
         dist.barrier()
-        ms = float(t.item())
     return ms / steps
 
 
@@ -293,13 +346,21 @@ def main():
         torch.cuda.set_device(0)
     dev = torch.device("cuda", local if world > 1 else 0)
     B = w["B"]                                          # weak scaling: every rank runs the full per-GPU batch
-    st = make_state(w, B, dev, seed=1234 + rank, ncopy=a.ncopy)
+    kvseq = w.get("shard") == "kvseq"
+    if kvseq:                                           # strong scaling: the pools shrink with the rank count; keep the cycled set > L2
+        local = B * kvseq_local_len(w["L"], w["W"], world) * w["Hkv"] * (144 if w["nb"] == 4 else 80)
+        a.ncopy = max(a.ncopy, -(-(192 << 20) // local))
+    st = make_state(w, B, dev, seed=1234 + rank, ncopy=a.ncopy, rank=rank, world=world)
     plan(st, a.nsplit or None)
     sampler = ClockSampler(local if world > 1 else 0)
     if rank == 0:
         sampler.start()
-    ms = timed(lambda i: step(st, i), a.steps, a.warmup, dist)
-    ms_e2e = timed(lambda i: step(st, i, e2e=True), a.steps, a.warmup, dist)
+    if kvseq:
+        ms = timed(lambda i: step_kvseq(st, i, dist=dist), a.steps, a.warmup, dist)
+        ms_e2e = timed(lambda i: step_kvseq(st, i, e2e=True, dist=dist), a.steps, a.warmup, dist)
+    else:
+        ms = timed(lambda i: step(st, i), a.steps, a.warmup, dist)
+        ms_e2e = timed(lambda i: step(st, i, e2e=True), a.steps, a.warmup, dist)
     ms_dec = timed(lambda i: decode_only(st, i), a.steps, a.warmup, None)
     clocks = sampler.stop() if rank == 0 else None
     status = st["K"].device_status()
@@ -309,26 +370,34 @@ def main():
         return
     nbytes = algorithmic_bytes(w)
     peak, which = peaks()
-    ach = nbytes / (ms_dec * 1e-3) / 1e9
+    nloc = nbytes
+    if kvseq:                                           # bytes of this rank's decode launch (rank 0 carries the BF16 rows)
+        cell = 144 if w["nb"] == 4 else 80
+        nloc = nbytes - B * w["Hkv"] * cell * (w["L"] - w["W"] - w["S"]) + B * w["Hkv"] * cell * (st["Lloc"] - w["W"] - w["S"])
+    ach = nloc / (ms_dec * 1e-3) / 1e9
+    nwork = nbytes if kvseq else world * nbytes          # strong scaling: the job is one sequence
     traffic = None
     tf = ROOT / "profiles" / "traffic.json"
     if tf.exists():
         traffic = json.loads(tf.read_text()).get(a.workload)
     line = {
-        "metric": "decode_attention_kv_gbps", "value": world * nbytes / (ms * 1e-3) / 1e9, "unit": "GB/s", "n_gpus": world,
-        "steps": a.steps, "warmup": a.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "metric": "decode_attention_kv_gbps", "value": nwork / (ms * 1e-3) / 1e9, "unit": "GB/s", "n_gpus": world,
+        "steps": a.steps, "warmup": a.warmup, "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "strong" if kvseq else "weak",
         "vs_baseline": None, "dtype": "u8", "data": "synthetic",
         "config": {"workload": w["name"], "batch_per_gpu": B, "nsplit": st["plan"][0], "chunk": st["plan"][1],
                    "l2": f"{a.ncopy} distinct {st['pools'][0].numel() >> 20} MiB pools cycled (each larger than L2)",
-                   "parallelism": f"batch-sharded x{world}" if world > 1 else "single gpu",
-                   "step": "fr_cb_write (T = batch) + fr_cb_attn", "device_status": status},
-        "e2e": {"value": world * nbytes / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s",
+                   "parallelism": ((f"kv-sequence sharded x{world}, NCCL all-gather of (o, m, l) rows + LSE merge" if kvseq
+                                    else f"batch-sharded x{world}") if world > 1 else "single gpu"),
+                   "step": ("fr_cb_write (last rank) + fr_attn_partial + all-gather + merge" if kvseq
+                            else "fr_cb_write (T = batch) + fr_cb_attn"), "device_status": status},
+        "e2e": {"value": nwork / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s",
                 "h2d_bytes_per_step": int(st["q_host"].numel() * 2 + st["kv_host"].numel() * 2 + B * 8),
                 "d2h_bytes_per_step": int(st["out_host"].numel() * 2), "ms_per_step": ms_e2e},
-        "gpu_launches": 3 * a.steps,
+        "gpu_launches": (4 if kvseq else 3) * a.steps,
         "roofline": {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak, "traffic": traffic,
                      "kernel": "k_decode<4, key-only>" if w["nb"] == 4 else "k_decode<2, key-only>", "peak_source": which,
-                     "us_per_launch": ms_dec * 1e3, "algorithmic_bytes": nbytes, "frac_of_8000": ach / 8000.0},
+                     "us_per_launch": ms_dec * 1e3, "algorithmic_bytes": nloc, "frac_of_8000": ach / 8000.0},
         "clocks": clocks,
     }
     if world == 1:

@@ -8,6 +8,7 @@
 // konlya2 (9 / kind 11); the symmetric INT4 formats and the ablation codebooks answer -4.
 #include <cstdint>
 #include <cstdio>
+#include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
 #include "fr_kernels.h"
@@ -185,6 +186,51 @@ int fr_attn_partial(int fmt, const void* q, long long q_bs, const uint8_t* pool,
 }
 
 int fr_device_status() { return fr::decode_status(); }
+
+}  // extern "C"
+
+namespace {
+// one warp per (row, q head): o = sum_r w_r l_r o_r / sum_r w_r l_r with w_r = 2^(m_r - max m); parts [R][rows][130]
+__global__ void __launch_bounds__(128) k_merge_partials(const float* parts, int R, int rows, void* out, int out_fp32) {
+  const int row = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  float M = -INFINITY;
+  for (int r = 0; r < R; ++r) {
+    const float* p = parts + (static_cast<size_t>(r) * rows + row) * 130;
+    if (p[129] > 0.f) M = fmaxf(M, p[128]);
+  }
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  float den = 0.f;
+  for (int r = 0; r < R; ++r) {
+    const float* p = parts + (static_cast<size_t>(r) * rows + row) * 130;
+    const float l = p[129];
+    if (!(l > 0.f)) continue;
+    const float wgt = exp2f(p[128] - M) * l;
+    const float2 a = *reinterpret_cast<const float2*>(p + 4 * lane), b = *reinterpret_cast<const float2*>(p + 4 * lane + 2);
+    acc.x = fmaf(wgt, a.x, acc.x); acc.y = fmaf(wgt, a.y, acc.y); acc.z = fmaf(wgt, b.x, acc.z); acc.w = fmaf(wgt, b.y, acc.w);
+    den += wgt;
+  }
+  const float inv = den > 0.f ? 1.f / den : 0.f;
+  acc.x *= inv; acc.y *= inv; acc.z *= inv; acc.w *= inv;
+  if (out_fp32) {
+    *reinterpret_cast<float4*>(static_cast<float*>(out) + static_cast<size_t>(row) * 128 + 4 * lane) = acc;
+  } else {
+    const __nv_bfloat162 x = __floats2bfloat162_rn(acc.x, acc.y), y = __floats2bfloat162_rn(acc.z, acc.w);
+    uint2 v;
+    v.x = *reinterpret_cast<const uint32_t*>(&x);
+    v.y = *reinterpret_cast<const uint32_t*>(&y);
+    *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(out) + static_cast<size_t>(row) * 128 + 4 * lane) = v;
+  }
+}
+}  // namespace
+
+extern "C" {
+
+int fr_merge_partials(const float* parts, int R, int rows, void* out, int out_fp32, void* stream) {
+  if (rows <= 0 || R <= 0) return 0;
+  k_merge_partials<<<(rows + 3) / 4, 128, 0, static_cast<cudaStream_t>(stream)>>>(parts, R, rows, out, out_fp32);
+  return cudaPeekAtLastError() == cudaSuccess ? 0 : -1;
+}
 
 // ---- decode attention for callers that may not allocate device memory
 // Some hosts of this library cannot hand over a workspace: a serving worker whose memory pool was sized and frozen at

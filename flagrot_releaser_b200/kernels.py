@@ -72,9 +72,10 @@ def lib():
     L.fr_w3_static_write.argtypes = [P, LL, P, I, I, I, P, P, I, P, I, P, P]
     L.fr_cb_attn_noalloc.argtypes = [P, LL, P, P, I, P, I, I, I, I, I, F, I, P, LL, P, P, P, LL, LL, P, I]
     L.fr_attn_partial.argtypes = [I, P, LL, P, P, I, P, I, I, I, I, I, F, P, P, P, P, P, P, P, P, P, LL, LL, P, I, I]
+    L.fr_merge_partials.argtypes = [P, I, I, P, I, P]
     for n in ("fr_v2_attn", "fr_v2_write", "fr_v2_occupancy", "fr_v2_chunk_bytes", "fr_cb_write", "fr_cb_attn",
               "fr_cb_occupancy", "fr_cb_chunk_bytes", "fr_cb_nsg", "fr_head_fwht", "fr_cb_write3",
-              "fr_w3_static_write", "fr_cb_write_smem", "fr_attn_partial", "fr_device_status", "fr_cb_attn_noalloc"):
+              "fr_w3_static_write", "fr_cb_write_smem", "fr_attn_partial", "fr_device_status", "fr_cb_attn_noalloc", "fr_merge_partials"):
         getattr(L, n).restype = I
     _LIB = L
     return L
@@ -392,6 +393,17 @@ def merge_partials(parts: torch.Tensor) -> torch.Tensor:
     w = torch.where(l > 0, torch.exp2(m - torch.where(torch.isinf(M), torch.zeros_like(M), M)), torch.zeros_like(l)) * l
     den = w.sum(0)
     return (w[..., None] * o).sum(0) / torch.where(den > 0, den, torch.ones_like(den))[..., None]
+
+
+def merge_partials_into(parts: torch.Tensor, out: torch.Tensor):
+    """merge_partials as one kernel launch (fr_merge_partials): parts fp32 [R, B, Hq, 130] contiguous on the device ->
+    out [B, Hq * 128] (or [B, Hq, 128]) bf16 or fp32, contiguous."""
+    R, B, Hq, _ = parts.shape
+    assert parts.dtype == torch.float32 and parts.is_contiguous() and out.is_contiguous() and out.numel() == B * Hq * 128
+    assert out.dtype in (torch.bfloat16, torch.float32)
+    _check(lib().fr_merge_partials(parts.data_ptr(), R, B * Hq, out.data_ptr(), int(out.dtype == torch.float32), _stream()),
+           "fr_merge_partials")
+    return out
 
 
 def device_status() -> int:

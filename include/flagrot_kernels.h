@@ -104,6 +104,11 @@ int fr_attn_partial(int fmt, const void* q, long long q_bs, const uint8_t* pool,
                     const void* tail, const int* tail_len, const int* tail_idx, long long tail_bs, long long tail_ts,
                     void* stream, int gqa, int kv_start);
 
+/* No counterpart in the reference.  Merges the rows of R KV-sequence shards written by fr_attn_partial: parts fp32
+ * [R, rows, 130] (rows = B * q heads; 128 normalised values, m in log2 units, l; l = 0: the shard saw no key) -> out
+ * [rows, 128] bf16 (or fp32 when out_fp32).  o = sum_r w_r l_r o_r / sum_r w_r l_r, w_r = 2^(m_r - max m). */
+int fr_merge_partials(const float* parts, int R, int rows, void* out, int out_fp32, void* stream);
+
 /* 0, or the source line of a bounded device-side wait that gave up (sticky; synchronises the device). */
 int fr_device_status(void);
 

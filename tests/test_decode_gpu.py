@@ -201,6 +201,26 @@ def test_decode_partial_rows_merge(K):
     check(run_case(K, "konlya", [300, 1000, 17], win=(32, 9), seed=50, partial=True), "partial")
 
 
+def test_merge_partials_kernel(K):
+    """fr_merge_partials against the torch merge: shards with no key (l = 0), -inf maxima, bf16 and fp32 outputs"""
+    g = torch.Generator().manual_seed(5)
+    R, B, Hq = 5, 3, 8
+    parts = torch.randn(R, B, Hq, 130, generator=g)
+    parts[..., 128] *= 6
+    parts[..., 129] = torch.rand(R, B, Hq, generator=g) * 50
+    parts[1, :, :, 129] = 0
+    parts[1, :, :, 128] = float("-inf")
+    parts[:, 2, 3, 129] = 0                      # a row nobody saw
+    ref = K.merge_partials(parts)
+    pd = parts.to(DEV).contiguous()
+    o32 = K.merge_partials_into(pd, torch.empty(B, Hq, 128, dtype=torch.float32, device=DEV))
+    o16 = K.merge_partials_into(pd, torch.empty(B, Hq * 128, dtype=torch.bfloat16, device=DEV))
+    torch.cuda.synchronize()
+    assert torch.allclose(o32.cpu(), ref, rtol=1e-5, atol=1e-5)
+    assert torch.equal(o16.cpu().view(B, Hq, 128), o32.cpu().to(torch.bfloat16))
+    assert float(o32[2, 3].abs().sum()) == 0.0
+
+
 def test_decode_golden_baseline_config(K, golden_dir):
     """the reference-generated expectation of the small baseline configuration (batch 2, 8 q / 2 kv heads, context 512,
     4 sinks + 32 window): pools packed by the oracle in the CPU reference's arithmetic, outputs from the reference's
