@@ -386,7 +386,8 @@ def main():
         "scaling": "strong" if kvseq else "weak",
         "vs_baseline": None, "dtype": "u8", "data": "synthetic",
         "config": {"workload": w["name"], "batch_per_gpu": B, "nsplit": st["plan"][0], "chunk": st["plan"][1],
-                   "l2": f"{a.ncopy} distinct {st['pools'][0].numel() >> 20} MiB pools cycled (each larger than L2)",
+                   "l2": f"{a.ncopy} distinct {st['pools'][0].numel() >> 20} MiB pools cycled "
+                         f"({a.ncopy * st['pools'][0].numel() >> 20} MiB in all, more than the 126 MB L2)",
                    "parallelism": ((f"kv-sequence sharded x{world}, NCCL all-gather of (o, m, l) rows + LSE merge" if kvseq
                                     else f"batch-sharded x{world}") if world > 1 else "single gpu"),
                    "step": ("fr_cb_write (last rank) + fr_attn_partial + all-gather + merge" if kvseq
