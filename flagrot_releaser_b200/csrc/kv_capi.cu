@@ -10,12 +10,15 @@
 // operation rounded separately (reference kivi.cu:99-109).
 //
 // Kernels: k_v_write (warp per (token, head)), k_k_encode (CTA per (group, head); fp32 CUDA cores: the selection is
-// defined by fp32 sums), k_kv_attn (CTA per (row, head, split); fp32 CUDA cores, three value classes accumulated
-// separately and inverse-transformed once), k_kv_merge.  Head dim 128; the FP8-metadata pages (f8) and head dim 256
+// defined by fp32 sums), kvm::k_kv_attn_mma (kv_attn_mma.cuh: page splits on the tensor cores for GQA groups <= 8),
+// k_kv_attn (CTA per (row, head, split); fp32 CUDA cores, three value classes accumulated separately and
+// inverse-transformed once: the BF16 sink / window split, larger GQA groups, FLAGROT_KIVI_ATTN=cuda), k_kv_merge.  Head dim 128; the FP8-metadata pages (f8) and head dim 256
 // answer code 2 with a message, as the reference does for unsupported shapes.
 #include <cmath>
 #include <cstdint>
 #include <cstdio>
+#include <cstdlib>
+#include <cstring>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
@@ -398,10 +401,10 @@ __global__ void __launch_bounds__(128) k_kv_attn(const __nv_bfloat16* __restrict
                                                  const int* __restrict__ cached, int kv_start, int Hkv, int NS, int chunk,
                                                  float qscale, const __nv_bfloat16* __restrict__ ring,
                                                  const int* __restrict__ tail_len, const int* __restrict__ tail_idx, int T,
-                                                 float* __restrict__ opart, float* __restrict__ ml) {
+                                                 float* __restrict__ opart, float* __restrict__ ml, int sp0) {
   extern __shared__ __align__(16) uint8_t smraw[];
   AttnSmem<G>& S = *reinterpret_cast<AttnSmem<G>*>(smraw);
-  const int h = blockIdx.x, sp = blockIdx.y, b = blockIdx.z;
+  const int h = blockIdx.x, sp = blockIdx.y + sp0, b = blockIdx.z;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const long long pidx = static_cast<long long>(b * Hkv + h) * (NS + 1) + sp;
   float* op = opart + pidx * G * D;
@@ -690,6 +693,14 @@ __global__ void k_kv_lse_merge(const __nv_bfloat16* __restrict__ oa, const float
   out[r * out_rs + static_cast<long long>(hh) * Dd + c] = __float2bfloat16_rn(__fdiv_rn(num, __fadd_rn(wa, wb)));
 }
 
+#include "kv_attn_mma.cuh"
+
+// FLAGROT_KIVI_ATTN=cuda keeps the page splits on the fp32 CUDA-core kernel (read at every launch)
+bool kivi_use_mma() {
+  const char* e = std::getenv("FLAGROT_KIVI_ATTN");
+  return !(e != nullptr && std::strcmp(e, "cuda") == 0);
+}
+
 template <int G>
 int launch_attn(const void* q, long long q_rs, const void* pool, const void* bt, long long bt_rs, const void* cached,
                 int kv_start, int B, int Hkv, int NS, int chunk, float qscale, const void* ring, const void* tail_len,
@@ -700,10 +711,31 @@ int launch_attn(const void* q, long long q_rs, const void* pool, const void* bt,
     if (cudaFuncSetAttribute(k_kv_attn<G>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return 1;
     set = true;
   }
-  k_kv_attn<G><<<dim3(Hkv, NS + 1, B), 128, smem, st>>>(
-      static_cast<const __nv_bfloat16*>(q), q_rs, static_cast<const uint8_t*>(pool), static_cast<const int*>(bt), bt_rs,
-      static_cast<const int*>(cached), kv_start, Hkv, NS, chunk, qscale, static_cast<const __nv_bfloat16*>(ring),
-      static_cast<const int*>(tail_len), static_cast<const int*>(tail_idx), T, static_cast<float*>(opart), static_cast<float*>(ml));
+  const auto* qp = static_cast<const __nv_bfloat16*>(q);
+  const auto* pp = static_cast<const uint8_t*>(pool);
+  const auto* btp = static_cast<const int*>(bt);
+  const auto* cp = static_cast<const int*>(cached);
+  const auto* rp = static_cast<const __nv_bfloat16*>(ring);
+  const auto* tlp = static_cast<const int*>(tail_len);
+  const auto* tip = static_cast<const int*>(tail_idx);
+  auto* opp = static_cast<float*>(opart);
+  auto* mlp = static_cast<float*>(ml);
+  if constexpr (G <= 8) {
+    if (kivi_use_mma()) {          // page splits on the tensor cores, the BF16 sink / window split on the CUDA-core kernel
+      static bool set2 = false;
+      if (!set2) {
+        if (cudaFuncSetAttribute(kvm::k_kv_attn_mma<G>, cudaFuncAttributeMaxDynamicSharedMemorySize, kvm::SMEM) != cudaSuccess) return 1;
+        set2 = true;
+      }
+      kvm::k_kv_attn_mma<G><<<dim3(Hkv, NS, B), 128, kvm::SMEM, st>>>(qp, q_rs, pp, btp, bt_rs, cp, kv_start, Hkv, NS, chunk, qscale,
+                                                                      opp, mlp);
+      k_kv_attn<G><<<dim3(Hkv, 1, B), 128, smem, st>>>(qp, q_rs, pp, btp, bt_rs, cp, kv_start, Hkv, NS, chunk, qscale, rp, tlp, tip, T,
+                                                       opp, mlp, NS);
+      return 0;
+    }
+  }
+  k_kv_attn<G><<<dim3(Hkv, NS + 1, B), 128, smem, st>>>(qp, q_rs, pp, btp, bt_rs, cp, kv_start, Hkv, NS, chunk, qscale, rp, tlp, tip, T,
+                                                        opp, mlp, 0);
   return 0;
 }
 
