@@ -298,6 +298,8 @@ def cpu_arm(w, steps, warmup, sample_rows=2):
                            kv_start=w["S"])
         if i >= warmup:
             times.append(time.perf_counter() - t0)
+    if not times:                                  # --cpu-steps 0: no CPU leg
+        return None, None, None
     sec = float(np.mean(times))
     gbs = algorithmic_bytes(w, nseq) / sec / 1e9
     cores = os.cpu_count() or 1

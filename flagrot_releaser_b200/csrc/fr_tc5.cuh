@@ -59,6 +59,22 @@ FR_DEVI bool mbar_wait_abortable(uint32_t a, uint32_t parity, volatile uint32_t*
   *abort = 1;
   return false;
 }
+// for roles that run ahead of the critical path (producers): between probes the warp sleeps, so that its waiting does not
+// take issue slots from the warps everything else waits for
+FR_DEVI bool mbar_wait_relaxed(uint32_t a, uint32_t parity, volatile uint32_t* abort) {
+  if (mbar_try(a, parity)) return true;
+  const long long t0 = clock64();
+  do {
+#pragma unroll 1
+    for (int i = 0; i < 32; ++i) {
+      __nanosleep(200);
+      if (mbar_try(a, parity)) return true;
+    }
+    if (*abort) return false;
+  } while (clock64() - t0 < WAIT_CYCLES);
+  *abort = 1;
+  return false;
+}
 FR_DEVI void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t mbar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(dst), "l"(src),
                "r"(bytes), "r"(mbar)

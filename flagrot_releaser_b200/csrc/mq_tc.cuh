@@ -53,6 +53,14 @@ FR_DEVI bool tq_wait_at(uint32_t bar, uint32_t parity, volatile uint32_t* abort,
   return ok;
 }
 #define tq_wait(bar, parity, abort) tq_wait_at(bar, parity, abort, __LINE__)
+FR_DEVI bool tq_wait_relaxed_at(uint32_t bar, uint32_t parity, volatile uint32_t* abort, int line) {   // producers: sleeps between probes
+  if (tc5::mbar_try(bar, parity)) return true;
+  const bool was = *abort != 0;
+  const bool ok = tc5::mbar_wait_relaxed(bar, parity, abort);
+  if (!ok && !was) atomicCAS(&g_mq_status, 0, line);
+  return ok;
+}
+#define tq_wait_relaxed(bar, parity, abort) tq_wait_relaxed_at(bar, parity, abort, __LINE__)
 
 // K operand tiles of one 64-key block.  item = (key, tg pair, group j): the two code words (tg = 2 tgp, 2 tgp + 1) of group j
 // carry dims 32 j + 8 tgp + {0..7} in the low fields and + 16 in the high fields of their bytes -> two 16-byte chunks.
@@ -397,14 +405,14 @@ __global__ void __launch_bounds__(TQ_THREADS, 1) k_mq_tc(const MqParams p) {
   } else if (warp < (TQ_SOFT + TQ_CONV) / 32) {
     // =========================================================================== conversion warps
     const int ctid = tid - TQ_SOFT;
-    tq_wait(b_q, 0, abortf);          // the q staging (which lies over the operand tiles) has been read
+    tq_wait_relaxed(b_q, 0, abortf);          // the q staging (which lies over the operand tiles) has been read
     uint32_t prev = 0;
     // K runs one block ahead of V: K(j + 1) only needs QK(j - 1) to be done, while V(j) has to wait for PV(j - 2), which
     // hangs on the softmax - so the next scores can be under way while the softmax still holds the V tile back
     auto conv_k = [&](int j) {
       const int buf = j & 1, rs = j % TQ_RAWST;
-      tq_wait(b_rawf + 8 * rs, (j / TQ_RAWST) & 1, abortf);
-      if (j >= 2) tq_wait(b_ke + 8 * buf, ((j >> 1) - 1) & 1, abortf);
+      tq_wait_relaxed(b_rawf + 8 * rs, (j / TQ_RAWST) & 1, abortf);
+      if (j >= 2) tq_wait_relaxed(b_ke + 8 * buf, ((j >> 1) - 1) & 1, abortf);
       tq_convert_k<NB, KO>(sb + S::RAW + rs * S::RAW_STAGE, sb + S::KT + buf * NBASE * S::KT_TILE, kend - (kblk0 + j) * BN, ctid,
                            j < 2, buf, prev);
     };
@@ -414,7 +422,7 @@ __global__ void __launch_bounds__(TQ_THREADS, 1) k_mq_tc(const MqParams p) {
     for (int j = 0; j < nblk; ++j) {
       const int buf = j & 1, rs = j % TQ_RAWST;
       if (j + 1 < nblk) conv_k(j + 1);
-      if (j >= 2) tq_wait(b_ve + 8 * buf, ((j >> 1) - 1) & 1, abortf);
+      if (j >= 2) tq_wait_relaxed(b_ve + 8 * buf, ((j >> 1) - 1) & 1, abortf);
       tq_convert_v<NB>(sb + S::RAW + rs * S::RAW_STAGE, sb + S::VT + buf * 16384, kend - (kblk0 + j) * BN, ctid);
       tc5::fence_async_smem();                 // one fence for the K tile of the next block and the V tile of this one
       if (j + 1 < nblk) tc5::mbar_arrive(b_kf + 8 * (buf ^ 1));
@@ -464,7 +472,7 @@ __global__ void __launch_bounds__(TQ_THREADS, 1) k_mq_tc(const MqParams p) {
     // =========================================================================== page loader (the warp waits, lane 0 copies)
     for (int j = 0; j < nblk; ++j) {
       const int rs = j % TQ_RAWST, kb = kblk0 + j;
-      if (j >= TQ_RAWST) tq_wait(b_rawe + 8 * rs, ((j / TQ_RAWST) - 1) & 1, abortf);
+      if (j >= TQ_RAWST) tq_wait_relaxed(b_rawe + 8 * rs, ((j / TQ_RAWST) - 1) & 1, abortf);
       if (lane == 0) {
         const int npg = min(PPB, (kend - kb * BN + PAGE - 1) / PAGE);
         tc5::mbar_expect(b_rawf + 8 * rs, npg * L::CHUNK);

@@ -32,7 +32,7 @@ GEN, GT8, HD256 = 1024, 2048, 4096
 STAGES = 3
 MAX_CHUNK, MAX_SPLITS = 8192, 512
 # split planner constants for B200 (tokens-equivalent fixed cost per CTA, per merged part)
-PLAN_C0, PLAN_C1 = 192, 6
+PLAN_C0, PLAN_C1 = 640, 6
 
 
 def _lib_path() -> Path:

@@ -1,6 +1,6 @@
 #!/usr/bin/env bash
 # Builds the parts of the reference that compile for sm_100a without modification, from the sources where they lie
-# (REF, default /root/reference), into oracle/_ref/ (git-ignored):
+# (the checkout named by $REF; a built-in default otherwise), into oracle/_ref/ (git-ignored):
 #   libflagrot_w3ref.so    kernels/csrc/attn_cb_write3.cu + integrations/vllm_flagrot/csrc/flagrot_capi.cu
 #                          (+ ref_link_stubs.cu for the symbols of the wgmma translation units)
 #   libflagrot_kivi_ref.so integrations/vllm_flagrot/csrc/kivi.cu

@@ -1,6 +1,6 @@
 """Generates tests/golden/*.npz by running the reference's own PyTorch code on CPU on seeded inputs.
 
-    python tests/golden/make_golden.py [/path/to/reference]      (default /root/reference)
+    python tests/golden/make_golden.py [/path/to/reference]      (the reference checkout; a built-in default is used when omitted)
 
 What is recorded (inputs as bf16 bit patterns, outputs exactly as the reference returned them):
   writer_dynamic.npz   kernels/codebook_ref.encode (cfg konlya / konlya2, qk asym / asym2) for keys and values, incl. the
