@@ -322,6 +322,138 @@ FR_DEVI void tail_cta(const DecodeParams& p, float* scr, int b, int kvh, int qt,
   }
 }
 
+// The same CTA on the tensor cores (mma.sync m16n8k16 BF16, fp32 accumulation).  Warp w owns the 16-token slices w, w + 4, ...
+// of the window with its own running (m, l) and accumulators; rows 0 - 3 of the M tile are the q heads.  K fragments come
+// straight from global memory (a lane's two registers of a k-step cover one whole 32-byte sector of a row), V rows go
+// through the warp's shared-memory tile and ldmatrix.trans.  q and K are BF16 already, so the scores are exact products
+// summed in fp32; p is split into two BF16 parts (hi + lo) so that P V keeps 16 bits of p.  Output format = tail_cta's.
+constexpr int TAILM_VSTR = 272;                       // bytes per V row in the warp tile (256 + 16)
+constexpr int TAILM_BYTES = NWARP * (4 * 128 + 8) * 4 + 128 + NWARP * 16 * TAILM_VSTR;
+FR_DEVI void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+FR_DEVI uint32_t pack_bf2(float a, float b) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+FR_DEVI void tail_cta_mma(const DecodeParams& p, uint8_t* smem, float* scr, int b, int kvh, int qt, int tl) {
+  const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5, g8 = lane >> 2, c4 = lane & 3;
+  constexpr int WS = 4 * 128 + 8;
+  const uint32_t vt = smem_u32(smem) + NWARP * WS * 4 + 128 + w * 16 * TAILM_VSTR;
+  // A fragments of q: rows 0 - 3 = the tile's heads
+  uint32_t qa[8][2];
+  {
+    const __nv_bfloat16* qb = static_cast<const __nv_bfloat16*>(p.q) + b * p.q_bs + (kvh * p.G + qt * 4) * HD;
+    const bool on = g8 < 4 && qt * 4 + g8 < p.G;
+#pragma unroll
+    for (int kk = 0; kk < 8; ++kk) {
+      qa[kk][0] = on ? *reinterpret_cast<const uint32_t*>(qb + g8 * HD + 16 * kk + 2 * c4) : 0u;
+      qa[kk][1] = on ? *reinterpret_cast<const uint32_t*>(qb + g8 * HD + 16 * kk + 2 * c4 + 8) : 0u;
+    }
+  }
+  const __nv_bfloat16* tb = static_cast<const __nv_bfloat16*>(p.tail) + (p.tail_idx ? p.tail_idx[b] : b) * p.tail_bs;
+  const __nv_bfloat16* kbase = tb + kvh * HD;
+  const __nv_bfloat16* vbase = tb + (p.Hkv + kvh) * HD;
+  float o[16][2];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) o[i][0] = o[i][1] = 0.f;
+  float m = NEG_INF, l = 0.f;
+  for (int t0 = 16 * w; t0 < tl; t0 += 16 * NWARP) {
+    // V rows of the slice -> shared tile (rows past the window are zeros: p = 0 must not meet stale bytes)
+    __syncwarp();
+    for (int i = lane; i < 16 * 16; i += 32) {
+      const int r = i >> 4, c16 = i & 15;
+      const uint32_t dst = vt + r * TAILM_VSTR + 16 * c16;
+      if (t0 + r < tl) {
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(vbase + (t0 + r) * p.tail_ts + 8 * c16) : "memory");
+      } else {
+        sts128(dst, 0u, 0u, 0u, 0u);
+      }
+    }
+    asm volatile("cp.async.commit_group;\n" ::: "memory");
+    // K fragments of tokens t0 + 8 nt + g8
+    uint32_t kb[2][8][2];
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt) {
+      const int t = t0 + 8 * nt + g8;
+      const __nv_bfloat16* kr = kbase + t * p.tail_ts + 2 * c4;
+#pragma unroll
+      for (int kk = 0; kk < 8; ++kk) {
+        kb[nt][kk][0] = t < tl ? __ldg(reinterpret_cast<const uint32_t*>(kr + 16 * kk)) : 0u;
+        kb[nt][kk][1] = t < tl ? __ldg(reinterpret_cast<const uint32_t*>(kr + 16 * kk + 8)) : 0u;
+      }
+    }
+    float s[2][4];
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt) {
+      s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+#pragma unroll
+      for (int kk = 0; kk < 8; ++kk) mma_bf16(s[nt], qa[kk][0], 0u, qa[kk][1], 0u, kb[nt][kk][0], kb[nt][kk][1]);
+    }
+    float mx = NEG_INF;
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const float v = (t0 + 8 * nt + 2 * c4 + e < tl) ? s[nt][e] * p.qscale : NEG_INF;
+        s[nt][e] = v;
+        mx = fmaxf(mx, v);
+      }
+    mx = fmaxf(mx, __shfl_xor_sync(FULLMASK, mx, 1));
+    mx = fmaxf(mx, __shfl_xor_sync(FULLMASK, mx, 2));
+    const float mn = fmaxf(m, mx), base = mn == NEG_INF ? 0.f : mn;
+    const float alpha = m == NEG_INF ? 0.f : ex2(m - base);
+    m = mn;
+    float ps = 0.f;
+    uint32_t ph[2], pl[2];
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt) {
+      const float p0 = ex2(s[nt][0] - base), p1 = ex2(s[nt][1] - base);
+      ps += p0 + p1;
+      ph[nt] = pack_bf2(p0, p1);
+      pl[nt] = pack_bf2(p0 - bf16_lo(ph[nt]), p1 - bf16_hi(ph[nt]));
+    }
+    l = l * alpha + ps;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) { o[i][0] *= alpha; o[i][1] *= alpha; }
+    asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+    __syncwarp();
+#pragma unroll
+    for (int np = 0; np < 8; ++np) {
+      uint32_t b0, b1, b2, b3;
+      asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                   : "=r"(b0), "=r"(b1), "=r"(b2), "=r"(b3)
+                   : "r"(vt + ((lane & 7) + 8 * ((lane >> 3) & 1)) * TAILM_VSTR + (16 * np + 8 * (lane >> 4)) * 2));
+      float c0[4] = {o[2 * np][0], o[2 * np][1], 0.f, 0.f}, c1[4] = {o[2 * np + 1][0], o[2 * np + 1][1], 0.f, 0.f};
+      mma_bf16(c0, ph[0], 0u, ph[1], 0u, b0, b1);
+      mma_bf16(c0, pl[0], 0u, pl[1], 0u, b0, b1);
+      mma_bf16(c1, ph[0], 0u, ph[1], 0u, b2, b3);
+      mma_bf16(c1, pl[0], 0u, pl[1], 0u, b2, b3);
+      o[2 * np][0] = c0[0]; o[2 * np][1] = c0[1]; o[2 * np + 1][0] = c1[0]; o[2 * np + 1][1] = c1[1];
+    }
+  }
+  // partial of this warp in tail_cta's format: [4 heads][128] o, [4] m, [4] l (lanes g8 < 4 hold the heads)
+  l += __shfl_xor_sync(FULLMASK, l, 1);
+  l += __shfl_xor_sync(FULLMASK, l, 2);
+  if (g8 < 4) {
+#pragma unroll
+    for (int nt = 0; nt < 16; ++nt) *reinterpret_cast<float2*>(scr + w * WS + g8 * 128 + 8 * nt + 2 * c4) = make_float2(o[nt][0], o[nt][1]);
+    if (c4 == 0) { scr[w * WS + 512 + g8] = m; scr[w * WS + 516 + g8] = l; }
+  }
+  __syncwarp();
+  if (p.vmask_tail != nullptr) {     // static formats with V flags: move the partial into the stored V basis
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      float4 v = *reinterpret_cast<float4*>(scr + w * WS + g * 128 + 4 * lane);
+      float x[4] = {v.x, v.y, v.z, v.w};
+      rot_blocks(x, p.vmask_tail + kvh * 4, lane);
+      *reinterpret_cast<float4*>(scr + w * WS + g * 128 + 4 * lane) = make_float4(x[0], x[1], x[2], x[3]);
+    }
+  }
+}
+
 // ------------------------------------------------------------------------------------------------ q prologue
 // warp g prepares q head g of the tile (row mapping): the NV variants in fixed point, their per-group sums, the scale.
 template <int NV>
@@ -391,7 +523,7 @@ __global__ void __launch_bounds__(128, FR_DEC_MINB) k_decode(const DecodeParams 
     if (len <= 0 && tl <= 0 && nparts * NT > 1) {
       // nothing to attend: still publish an empty part so that the tickets add up
     }
-    tail_cta(p, scr, b, kvh, qt, tl);
+    tail_cta_mma(p, smem + S::RING, scr, b, kvh, qt, tl);
     cta_finish(p, scr, b, kvh, qt, NT, ns_b, nparts, nsp, &last_flag);
     return;
   }
@@ -740,7 +872,7 @@ __global__ void __launch_bounds__(128, FR_DEC_MINB) k_decode(const DecodeParams 
 
 template <int NB, bool KO> int launch_k(const DecodeParams& p, cudaStream_t st) {
   constexpr int NV = KO ? 3 : 1;
-  constexpr int smem = SMap<NB, NV>::TOTAL;
+  constexpr int smem = SMap<NB, NV>::TOTAL > TAILM_BYTES ? SMap<NB, NV>::TOTAL : TAILM_BYTES;
   static bool set = false;
   if (!set) {
     if (cudaFuncSetAttribute(k_decode<NB, KO>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -2;

@@ -98,7 +98,7 @@ __global__ void __launch_bounds__(TC_THREADS, 2) k_decode_tc(const DecodeParams 
   constexpr int WS = 4 * 128 + 8;
 
   if (split >= p.nsplit) {   // the BF16 window CTA
-    tail_cta(p, scr, b, kvh, qt, min(p.tail_len[b], 256));
+    tail_cta_mma(p, smem + S::RAW, scr, b, kvh, qt, min(p.tail_len[b], 256));
     cta_finish(p, scr, b, kvh, qt, NT, ns_b, nparts, nsp, &last_flag);
     return;
   }

@@ -729,8 +729,7 @@ int launch_attn(const void* q, long long q_rs, const void* pool, const void* bt,
       }
       kvm::k_kv_attn_mma<G><<<dim3(Hkv, NS, B), 128, kvm::SMEM, st>>>(qp, q_rs, pp, btp, bt_rs, cp, kv_start, Hkv, NS, chunk, qscale,
                                                                       opp, mlp);
-      k_kv_attn<G><<<dim3(Hkv, 1, B), 128, smem, st>>>(qp, q_rs, pp, btp, bt_rs, cp, kv_start, Hkv, NS, chunk, qscale, rp, tlp, tip, T,
-                                                       opp, mlp, NS);
+      kvm::k_kv_tail_mma<G><<<dim3(Hkv, 1, B), 128, kvm::TAIL_SMEM, st>>>(qp, q_rs, Hkv, NS, qscale, rp, tlp, tip, T, opp, mlp);
       return 0;
     }
   }
