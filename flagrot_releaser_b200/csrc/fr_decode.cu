@@ -9,7 +9,8 @@
 // lanes of an SM can retire at HBM speed, so the dot products run on the integer tensor path (mma.sync m16n8k32
 // u8 x s8 -> s32) directly on the packed codes; everything that touches a scale, a flag or the softmax stays on the
 // CUDA cores.
-//   * grid (Hkv * ceil(G / 4), nsplit [+ 1 window CTA], B), 128 threads; a CTA serves 4 q heads of one kv head;
+//   * grid (Hkv * ceil(G / 4), nsplit, B [x 2 with BF16 rows: the window CTAs come last and fill the final wave]),
+//     128 threads; a CTA serves 4 q heads of one kv head;
 //   * each warp owns every 4th 32-token block (two pages) of the split and a private ring of bulk-copy stages:
 //     lane 0 issues one cp.async.bulk per page (one contiguous 2304 / 1280-byte chunk) completing on the stage's
 //     mbarrier; waits are bounded and report through a status word instead of spinning forever;
@@ -257,76 +258,12 @@ FR_DEVI void cta_finish(const DecodeParams& p, float* scr, int b, int kvh, int q
 }
 
 // ------------------------------------------------------------------------------------------------ BF16 window CTA
-// one CTA per (row, kv head, q tile): fp32 softmax over the <= 256 BF16 rows of the row's ring entry; warp w takes
-// tokens w, w + 4, ...; lane = 4 dims.
-FR_DEVI void tail_cta(const DecodeParams& p, float* scr, int b, int kvh, int qt, int tl) {
-  const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
-  constexpr int WS = 4 * 128 + 8;
-  const __nv_bfloat16* qb = static_cast<const __nv_bfloat16*>(p.q) + b * p.q_bs + (kvh * p.G + qt * 4) * HD;
-  float q[4][4];
-#pragma unroll
-  for (int g = 0; g < 4; ++g) {
-    uint2 raw = make_uint2(0, 0);
-    if (qt * 4 + g < p.G) raw = *reinterpret_cast<const uint2*>(qb + g * HD + 4 * lane);
-    q[g][0] = bf16_lo(raw.x) * p.qscale; q[g][1] = bf16_hi(raw.x) * p.qscale;
-    q[g][2] = bf16_lo(raw.y) * p.qscale; q[g][3] = bf16_hi(raw.y) * p.qscale;
-  }
-  const __nv_bfloat16* tb = static_cast<const __nv_bfloat16*>(p.tail) + (p.tail_idx ? p.tail_idx[b] : b) * p.tail_bs;
-  const __nv_bfloat16* kr = tb + kvh * HD + 4 * lane;
-  const __nv_bfloat16* vr = tb + (p.Hkv + kvh) * HD + 4 * lane;
-  float m[4], l[4], o[4][4];
-#pragma unroll
-  for (int g = 0; g < 4; ++g) {
-    m[g] = NEG_INF; l[g] = 0.f;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) o[g][i] = 0.f;
-  }
-  constexpr int U = 4;
-  for (int t0 = w; t0 < tl; t0 += NWARP * U) {
-    uint2 kk[U], vv[U];
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const int t = t0 + NWARP * u;
-      kk[u] = t < tl ? __ldg(reinterpret_cast<const uint2*>(kr + t * p.tail_ts)) : make_uint2(0, 0);
-      vv[u] = t < tl ? __ldg(reinterpret_cast<const uint2*>(vr + t * p.tail_ts)) : make_uint2(0, 0);
-    }
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
-      if (t0 + NWARP * u >= tl) break;
-      const float k4[4] = {bf16_lo(kk[u].x), bf16_hi(kk[u].x), bf16_lo(kk[u].y), bf16_hi(kk[u].y)};
-      const float v4[4] = {bf16_lo(vv[u].x), bf16_hi(vv[u].x), bf16_lo(vv[u].y), bf16_hi(vv[u].y)};
-      float s[4];
-#pragma unroll
-      for (int g = 0; g < 4; ++g) s[g] = fmaf(q[g][0], k4[0], fmaf(q[g][1], k4[1], fmaf(q[g][2], k4[2], q[g][3] * k4[3])));
-#pragma unroll
-      for (int off = 16; off > 0; off >>= 1)
-#pragma unroll
-        for (int g = 0; g < 4; ++g) s[g] += __shfl_xor_sync(FULLMASK, s[g], off);
-#pragma unroll
-      for (int g = 0; g < 4; ++g) {
-        const float mn = fmaxf(m[g], s[g]);
-        const float a = m[g] == NEG_INF ? 0.f : ex2(m[g] - mn), pr = ex2(s[g] - mn);
-        l[g] = l[g] * a + pr;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) o[g][i] = fmaf(pr, v4[i], o[g][i] * a);
-        m[g] = mn;
-      }
-    }
-  }
-  // static formats with V flags: move the partial into the stored V basis (the final back-rotation serves all parts)
-#pragma unroll
-  for (int g = 0; g < 4; ++g) {
-    rot_blocks(o[g], p.vmask_tail ? p.vmask_tail + kvh * 4 : nullptr, lane);
-    *reinterpret_cast<float4*>(scr + w * WS + g * 128 + 4 * lane) = make_float4(o[g][0], o[g][1], o[g][2], o[g][3]);
-    if (lane == 0) { scr[w * WS + 512 + g] = m[g]; scr[w * WS + 516 + g] = l[g]; }
-  }
-}
-
-// The same CTA on the tensor cores (mma.sync m16n8k16 BF16, fp32 accumulation).  Warp w owns the 16-token slices w, w + 4, ...
+// One CTA per (row, kv head, q tile) over the <= 256 BF16 rows of the row's ring entry, on the tensor cores (mma.sync
+// m16n8k16 BF16, fp32 accumulation).  Warp w owns the 16-token slices w, w + 4, ...
 // of the window with its own running (m, l) and accumulators; rows 0 - 3 of the M tile are the q heads.  K fragments come
 // straight from global memory (a lane's two registers of a k-step cover one whole 32-byte sector of a row), V rows go
 // through the warp's shared-memory tile and ldmatrix.trans.  q and K are BF16 already, so the scores are exact products
-// summed in fp32; p is split into two BF16 parts (hi + lo) so that P V keeps 16 bits of p.  Output format = tail_cta's.
+// summed in fp32; p is split into two BF16 parts (hi + lo) so that P V keeps 16 bits of p.
 constexpr int TAILM_VSTR = 272;                       // bytes per V row in the warp tile (256 + 16)
 constexpr int TAILM_BYTES = NWARP * (4 * 128 + 8) * 4 + 128 + NWARP * 16 * TAILM_VSTR;
 FR_DEVI void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
@@ -434,7 +371,7 @@ FR_DEVI void tail_cta_mma(const DecodeParams& p, uint8_t* smem, float* scr, int 
       o[2 * np][0] = c0[0]; o[2 * np][1] = c0[1]; o[2 * np + 1][0] = c1[0]; o[2 * np + 1][1] = c1[1];
     }
   }
-  // partial of this warp in tail_cta's format: [4 heads][128] o, [4] m, [4] l (lanes g8 < 4 hold the heads)
+  // partial of this warp: [4 heads][128] o, [4] m, [4] l (lanes g8 < 4 hold the heads)
   l += __shfl_xor_sync(FULLMASK, l, 1);
   l += __shfl_xor_sync(FULLMASK, l, 2);
   if (g8 < 4) {
@@ -509,7 +446,12 @@ __global__ void __launch_bounds__(128, FR_DEC_MINB) k_decode(const DecodeParams 
   __shared__ int last_flag;
   const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5, gid = lane >> 2, tig = lane & 3;
   const int NT = (p.G + 3) >> 2;
-  const int kvh = blockIdx.x / NT, qt = blockIdx.x % NT, split = blockIdx.y, b = blockIdx.z;
+  // grid z: rows 0 .. B - 1 run the page splits (y = split); rows B .. 2 B - 1 (only with BF16 rows, only y = 0) run the
+  // window CTAs, so that these short CTAs are dealt last and fill the partly empty final wave of the page CTAs
+  const bool wcta = static_cast<int>(blockIdx.z) >= p.B;
+  if (wcta && blockIdx.y != 0) return;
+  const int kvh = blockIdx.x / NT, qt = blockIdx.x % NT, split = wcta ? p.nsplit : static_cast<int>(blockIdx.y);
+  const int b = wcta ? static_cast<int>(blockIdx.z) - p.B : static_cast<int>(blockIdx.z);
   const int has_tail = p.tail != nullptr;
   const int nsp = p.nsplit + has_tail;
   const int len = p.seq_lens[b];
@@ -879,7 +821,7 @@ template <int NB, bool KO> int launch_k(const DecodeParams& p, cudaStream_t st) 
     set = true;
   }
   const int NT = (p.G + 3) / 4;
-  const dim3 grid(p.Hkv * NT, p.nsplit + (p.tail != nullptr ? 1 : 0), p.B);
+  const dim3 grid(p.Hkv * NT, p.nsplit, p.B * (p.tail != nullptr ? 2 : 1));
   k_decode<NB, KO><<<grid, 128, smem, st>>>(p);
   return cudaPeekAtLastError() == cudaSuccess ? 0 : -1;
 }

@@ -88,7 +88,12 @@ __global__ void __launch_bounds__(TC_THREADS, 2) k_decode_tc(const DecodeParams 
   __shared__ int last_flag;
   const int tid = threadIdx.x, lane = tid & 31, w = __shfl_sync(FULLMASK, tid >> 5, 0);   // w: provably warp-uniform
   const int NT = (p.G + 3) >> 2;
-  const int kvh = blockIdx.x / NT, qt = blockIdx.x % NT, split = blockIdx.y, b = blockIdx.z;
+  // grid z: rows 0 .. B - 1 run the page splits (y = split); rows B .. 2 B - 1 (only with BF16 rows, only y = 0) run the
+  // window CTAs, so that these short CTAs are dealt last and fill the partly empty final wave of the page CTAs
+  const bool wcta = static_cast<int>(blockIdx.z) >= p.B;
+  if (wcta && blockIdx.y != 0) return;
+  const int kvh = blockIdx.x / NT, qt = blockIdx.x % NT, split = wcta ? p.nsplit : static_cast<int>(blockIdx.y);
+  const int b = wcta ? static_cast<int>(blockIdx.z) - p.B : static_cast<int>(blockIdx.z);
   const int has_tail = p.tail != nullptr;
   const int nsp = p.nsplit + has_tail;
   const int len = p.seq_lens[b];
@@ -407,7 +412,7 @@ template <int NB, bool KO> int launch_tc(const DecodeParams& p, cudaStream_t st)
     set = true;
   }
   const int NT = (p.G + 3) / 4;
-  const dim3 grid(p.Hkv * NT, p.nsplit + (p.tail != nullptr ? 1 : 0), p.B);
+  const dim3 grid(p.Hkv * NT, p.nsplit, p.B * (p.tail != nullptr ? 2 : 1));
   k_decode_tc<NB, KO><<<grid, TC_THREADS, smem, st>>>(p);
   return cudaPeekAtLastError() == cudaSuccess ? 0 : -1;
 }

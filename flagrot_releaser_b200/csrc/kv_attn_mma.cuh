@@ -64,12 +64,26 @@ FR_DEVI float ex2(float x) { float y; asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(
 #define KVM_MINB 2
 #endif
 template <int G>
+FR_DEVI void kv_tail_mma(uint8_t* smraw, int h, int b, const __nv_bfloat16* __restrict__ q, long long q_rs, int Hkv, int NS, float qscale,
+                         const __nv_bfloat16* __restrict__ ring, const int* __restrict__ tail_len,
+                         const int* __restrict__ tail_idx, int T, float* __restrict__ opart, float* __restrict__ ml);
+
+// grid (Hkv, NS, 2 B): z < B are the page splits; z >= B (y == 0 only) are the BF16 sink / window splits, dispatched last so
+// that they fill the final, partly empty wave of the page splits
+template <int G>
 __global__ void __launch_bounds__(128, KVM_MINB) k_kv_attn_mma(const __nv_bfloat16* __restrict__ q, long long q_rs,
                                                         const uint8_t* __restrict__ pool, const int* __restrict__ bt, long long bt_rs,
                                                         const int* __restrict__ cached, int kv_start, int Hkv, int NS, int chunk,
-                                                        float qscale, float* __restrict__ opart, float* __restrict__ ml) {
+                                                        float qscale, const __nv_bfloat16* __restrict__ ring,
+                                                        const int* __restrict__ tail_len, const int* __restrict__ tail_idx, int T,
+                                                        int B, float* __restrict__ opart, float* __restrict__ ml) {
   static_assert(G <= 8, "one M tile of q heads");
   extern __shared__ __align__(16) uint8_t smraw[];
+  if (static_cast<int>(blockIdx.z) >= B) {
+    if (blockIdx.y == 0) kv_tail_mma<G>(smraw, blockIdx.x, static_cast<int>(blockIdx.z) - B, q, q_rs, Hkv, NS, qscale, ring, tail_len,
+                                        tail_idx, T, opart, ml);
+    return;
+  }
   float (*qb)[8][D] = reinterpret_cast<float (*)[8][D]>(smraw);
   const int h = blockIdx.x, sp = blockIdx.y, b = blockIdx.z;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g8 = lane >> 2, c4 = lane & 3;
@@ -381,13 +395,10 @@ constexpr int TAIL_VSTR = 272;
 constexpr int TAIL_SMEM = 4 * 16 * TAIL_VSTR + 4 * (8 * D + 16) * 4;      // V tiles + per-warp partials
 
 template <int G>
-__global__ void __launch_bounds__(128) k_kv_tail_mma(const __nv_bfloat16* __restrict__ q, long long q_rs, int Hkv, int NS, float qscale,
-                                                     const __nv_bfloat16* __restrict__ ring, const int* __restrict__ tail_len,
-                                                     const int* __restrict__ tail_idx, int T, float* __restrict__ opart,
-                                                     float* __restrict__ ml) {
+FR_DEVI void kv_tail_mma(uint8_t* smraw, int h, int b, const __nv_bfloat16* __restrict__ q, long long q_rs, int Hkv, int NS, float qscale,
+                         const __nv_bfloat16* __restrict__ ring, const int* __restrict__ tail_len,
+                         const int* __restrict__ tail_idx, int T, float* __restrict__ opart, float* __restrict__ ml) {
   static_assert(G <= 8, "one M tile of q heads");
-  extern __shared__ __align__(16) uint8_t smraw[];
-  const int h = blockIdx.x, b = blockIdx.z;
   const int tid = threadIdx.x, w = tid >> 5, lane = tid & 31, g8 = lane >> 2, c4 = lane & 3;
   const long long pidx = static_cast<long long>(b * Hkv + h) * (NS + 1) + NS;
   float* op = opart + pidx * G * D;

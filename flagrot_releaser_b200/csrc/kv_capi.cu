@@ -721,15 +721,15 @@ int launch_attn(const void* q, long long q_rs, const void* pool, const void* bt,
   auto* opp = static_cast<float*>(opart);
   auto* mlp = static_cast<float*>(ml);
   if constexpr (G <= 8) {
-    if (kivi_use_mma()) {          // page splits on the tensor cores, the BF16 sink / window split on the CUDA-core kernel
+    if (kivi_use_mma()) {          // page splits and the BF16 sink / window split in one launch
       static bool set2 = false;
       if (!set2) {
         if (cudaFuncSetAttribute(kvm::k_kv_attn_mma<G>, cudaFuncAttributeMaxDynamicSharedMemorySize, kvm::SMEM) != cudaSuccess) return 1;
         set2 = true;
       }
-      kvm::k_kv_attn_mma<G><<<dim3(Hkv, NS, B), 128, kvm::SMEM, st>>>(qp, q_rs, pp, btp, bt_rs, cp, kv_start, Hkv, NS, chunk, qscale,
-                                                                      opp, mlp);
-      kvm::k_kv_tail_mma<G><<<dim3(Hkv, 1, B), 128, kvm::TAIL_SMEM, st>>>(qp, q_rs, Hkv, NS, qscale, rp, tlp, tip, T, opp, mlp);
+      static_assert(kvm::TAIL_SMEM <= kvm::SMEM, "the window split runs in the page-split kernel's shared memory");
+      kvm::k_kv_attn_mma<G><<<dim3(Hkv, NS, 2 * B), 128, kvm::SMEM, st>>>(qp, q_rs, pp, btp, bt_rs, cp, kv_start, Hkv, NS, chunk, qscale,
+                                                                          rp, tlp, tip, T, B, opp, mlp);
       return 0;
     }
   }
