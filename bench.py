@@ -179,9 +179,19 @@ def plan(st, nsplit):
 
 
 def step(st, i, e2e=False):
-    """one pass of the hot path on pool copy i; returns nothing (asynchronous unless e2e reads the result back)."""
+    """one pass of the hot path on pool copy i; returns nothing (asynchronous unless e2e reads the result back).
+    e2e: the step from pinned host buffers and back, replayed as one CUDA graph per pool copy (captured at first use)."""
     K, w = st["K"], st["w"]
     c = i % len(st["pools"])
+    if e2e and st.get("graphs", False):
+        gs = st.setdefault("_graphs", {})
+        if c not in gs:
+            from flagrot_releaser_b200.graphs import HostStep
+            step(st, c, e2e=False)                                      # first calls set kernel attributes
+            gs[c] = HostStep([(st["q"], st["q_host"]), (st["kv"], st["kv_host"]), (st["slots"][c], st["slots_host"][c])],
+                             lambda: step(st, c, e2e=False), [(st["out_host"], st["out"])])
+        gs[c].run()
+        return
     pool, bt = st["pools"][c], st["bts"][c]
     ns, ch = st["plan"]
     if e2e:
@@ -319,6 +329,8 @@ def main():
     ap.add_argument("--nsplit", type=int, default=0, help="force the split count (0: the planner's choice)")
     ap.add_argument("--ncopy", type=int, default=3)
     ap.add_argument("--cpu-steps", type=int, default=3)
+    ap.add_argument("--graph", action="store_true", help="e2e: one CUDA graph per step (flagrot_releaser_b200.graphs.HostStep) "
+                                                         "instead of separate launches from Python; measured equal within noise")
     a = ap.parse_args()
     a.warmup = max(a.warmup, 3) if a.impl == "ours" else a.warmup
     w = WORKLOADS[a.workload]
@@ -354,6 +366,7 @@ def main():
         a.ncopy = max(a.ncopy, -(-(192 << 20) // local))
     st = make_state(w, B, dev, seed=1234 + rank, ncopy=a.ncopy, rank=rank, world=world)
     plan(st, a.nsplit or None)
+    st["graphs"] = a.graph
     sampler = ClockSampler(local if world > 1 else 0)
     if rank == 0:
         sampler.start()
@@ -396,7 +409,9 @@ def main():
                             else "fr_cb_write (T = batch) + fr_cb_attn"), "device_status": status},
         "e2e": {"value": nwork / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s",
                 "h2d_bytes_per_step": int(st["q_host"].numel() * 2 + st["kv_host"].numel() * 2 + B * 8),
-                "d2h_bytes_per_step": int(st["out_host"].numel() * 2), "ms_per_step": ms_e2e},
+                "d2h_bytes_per_step": int(st["out_host"].numel() * 2), "ms_per_step": ms_e2e,
+                "launch": ("separate launches from Python" if (not a.graph or kvseq) else
+                           "one CUDA graph per step: 3 host-to-device copies, writer, decode, copy back")},
         "gpu_launches": (4 if kvseq else 3) * a.steps,
         "roofline": {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak, "traffic": traffic,
                      "kernel": "k_decode<4, key-only>" if w["nb"] == 4 else "k_decode<2, key-only>", "peak_source": which,

@@ -44,12 +44,6 @@ constexpr int BLK = 32;            // tokens per warp step
 #ifndef FR_DEC_MINB
 #define FR_DEC_MINB 3
 #endif
-#ifndef FR_DEC_OSMEM
-#define FR_DEC_OSMEM 0             // 1: the folded fp32 accumulators live in shared memory (touched only when the maximum moves)
-#endif
-#ifndef FR_DEC_QSMEM
-#define FR_DEC_QSMEM 0             // 1: q B fragments and q sums are read from shared memory at every use (fewer registers)
-#endif
 constexpr int ST = FR_DEC_ST;      // bulk-copy stages per warp
 constexpr int MAXPG = 512;         // pages per split (chunk <= 8192 tokens of 16)
 #define NEG_INF (-INFINITY)
@@ -131,12 +125,9 @@ template <int NB, int NV> struct SMap {
   static constexpr int RING_BYTES = NWARP * ST * DLay<NB>::STAGE;
   static constexpr int PBUF = RING + RING_BYTES;
   static constexpr int QT = PBUF + NWARP * PBUF_WORDS * 4;             // int16 [NV][4][128]
-  static constexpr int OFS = QT;                                        // float [16][128 threads] (FR_DEC_OSMEM; aliases the q table)
-  static constexpr int SQ = QT + (FR_DEC_OSMEM && 16 * 128 * 4 > NV * 4 * 128 * 2 ? 16 * 128 * 4 : NV * 4 * 128 * 2);   // int [NV][4][4]
+  static constexpr int SQ = QT + NV * 4 * 128 * 2;                      // int [NV][4][4]
   static constexpr int SF = SQ + NV * 16 * 4;                           // float [4]
-  static constexpr int QFT = SF + 16;                                   // u32 [NV][4][32 lanes][2] q B fragments (FR_DEC_QSMEM)
-  static constexpr int SQT = QFT + (FR_DEC_QSMEM ? NV * 4 * 32 * 8 : 0);  // int [NV][4 heads][4 groups] scaled q sums
-  static constexpr int PIDX = SQT + (FR_DEC_QSMEM ? NV * 16 * 4 : 0);    // int [MAXPG]
+  static constexpr int PIDX = SF + 16;                                  // int [MAXPG]
   static constexpr int MBAR = PIDX + MAXPG * 4;                         // u64 [NWARP][ST]
   static constexpr int TOTAL = MBAR + NWARP * ST * 8;
   static_assert(RING_BYTES >= NWARP * (4 * 128 + 8) * 4, "merge scratch aliases the ring");
@@ -522,31 +513,6 @@ __global__ void __launch_bounds__(128, FR_DEC_MINB) k_decode(const DecodeParams 
 
   // ---- per-thread constants
   // q B fragments: column gid = (head gid >> 1, part gid & 1: hi / lo); k = 4 tig .. (b0), 16 + 4 tig .. (b1)
-#if FR_DEC_QSMEM
-  {
-    uint32_t* qft = reinterpret_cast<uint32_t*>(smem + S::QFT);
-    int* sqt = reinterpret_cast<int*>(smem + S::SQT);
-    const int hd = gid >> 1, lo_part = gid & 1;
-#pragma unroll
-    for (int cj = w; cj < NV * 4; cj += NWARP) {
-      const int c = cj >> 2, j = cj & 3;
-#pragma unroll
-      for (int r = 0; r < 2; ++r) {
-        uint32_t word = 0;
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          const int qi = qtab[(c * 4 + hd) * 128 + 32 * j + 16 * r + 4 * tig + k];
-          const int hi = (qi + 64) >> 7, lw = qi - (hi << 7);
-          word |= static_cast<uint32_t>((lo_part ? lw : hi) & 0xFF) << (8 * k);
-        }
-        qft[(cj * 32 + lane) * 2 + r] = word;
-      }
-    }
-    for (int e = tid; e < NV * 16; e += 128) sqt[e] = sqs[e] * L::kf(e & 3);
-    __syncthreads();
-  }
-  const uint32_t qft_a = smem_u32(smem + S::QFT) + 8 * lane, sqt_a = smem_u32(smem + S::SQT) + 16 * tig;
-#else
   uint32_t qf[NV][4][2];
   int SQ[NV][4];   // per-group sums of the fixed-point q, pre-multiplied by the code scaling of the group (KF)
   {
@@ -569,7 +535,6 @@ __global__ void __launch_bounds__(128, FR_DEC_MINB) k_decode(const DecodeParams 
         SQ[c][j] = sqs[(c * 4 + tig) * 4 + j] * L::kf(j);
       }
   }
-#endif
   const float sfac = NB == 4 ? sfs[tig] * L::kfinv(0) : sfs[tig];
   // tokens of this lane inside a block: tau_i = 8 c + 2 i + e, (c, e) = (gid >> 1, gid & 1)
   const int tc = gid >> 1, te = gid & 1;
@@ -595,14 +560,7 @@ __global__ void __launch_bounds__(128, FR_DEC_MINB) k_decode(const DecodeParams 
   uint32_t nmax16 = 0;                           // fp16 bits of the largest V scale admitted by the normaliser
   float nrm = 0.f, inrm = 0.f;                   // P~ = rint(p * sv * nrm), nrm = 2^14 / (2 max sv)
   int Oi[2][4][4];                               // [m][w][frag] integer PV accumulators
-#if FR_DEC_OSMEM
-  float* ofs = reinterpret_cast<float*>(smem + S::OFS) + tid;     // element (a, c, k) at ofs[((a * 4 + c) * 2 + k) * 128]
-  __syncthreads();                                                // the q table under it has been read
-#define OF(a, c, k) ofs[(((a) * 4 + (c)) * 2 + (k)) * 128]
-#else
   float Of[2][4][2];                             // folded fp32 accumulators, rows gid / gid + 8 of tile (m, w), head tig
-#define OF(a, c, k) Of[a][c][k]
-#endif
   int Zi[4];
   float Zf[4];
 #pragma unroll
@@ -611,7 +569,7 @@ __global__ void __launch_bounds__(128, FR_DEC_MINB) k_decode(const DecodeParams 
     for (int c = 0; c < 4; ++c) {
 #pragma unroll
       for (int k = 0; k < 4; ++k) Oi[a][c][k] = 0;
-      OF(a, c, 0) = 0.f; OF(a, c, 1) = 0.f;
+      Of[a][c][0] = Of[a][c][1] = 0.f;
     }
 #pragma unroll
   for (int j = 0; j < 4; ++j) { Zi[j] = 0; Zf[j] = 0.f; }
@@ -621,8 +579,8 @@ __global__ void __launch_bounds__(128, FR_DEC_MINB) k_decode(const DecodeParams 
     for (int a = 0; a < 2; ++a)
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
-        OF(a, c, 0) = (OF(a, c, 0) + static_cast<float>(Oi[a][c][0] * 256 + Oi[a][c][1]) * (inrm * L::VF0)) * alpha;
-        OF(a, c, 1) = (OF(a, c, 1) + static_cast<float>(Oi[a][c][2] * 256 + Oi[a][c][3]) * (inrm * L::VF1)) * alpha;
+        Of[a][c][0] = (Of[a][c][0] + static_cast<float>(Oi[a][c][0] * 256 + Oi[a][c][1]) * (inrm * L::VF0)) * alpha;
+        Of[a][c][1] = (Of[a][c][1] + static_cast<float>(Oi[a][c][2] * 256 + Oi[a][c][3]) * (inrm * L::VF1)) * alpha;
 #pragma unroll
         for (int k = 0; k < 4; ++k) Oi[a][c][k] = 0;
       }
@@ -714,29 +672,14 @@ __global__ void __launch_bounds__(128, FR_DEC_MINB) k_decode(const DecodeParams 
         }
         int acc[NV][4];
 #pragma unroll
-        for (int c = 0; c < NV; ++c) {
-#if FR_DEC_QSMEM
-          const uint2 qw = lds64(qft_a + (c * 4 + j) * 256);
-          mma_u8s8_z(acc[c], a0, a1, a2, a3, qw.x, qw.y);
-#else
-          mma_u8s8_z(acc[c], a0, a1, a2, a3, qf[c][j][0], qf[c][j][1]);
-#endif
-        }
-#if FR_DEC_QSMEM
-        int SQj[NV];
-#pragma unroll
-        for (int c = 0; c < NV; ++c) asm volatile("ld.shared.u32 %0, [%1];\n" : "=r"(SQj[c]) : "r"(sqt_a + c * 64 + 4 * j));
-#define SQV(c, j) SQj[c]
-#else
-#define SQV(c, j) SQ[c][j]
-#endif
+        for (int c = 0; c < NV; ++c) mma_u8s8_z(acc[c], a0, a1, a2, a3, qf[c][j][0], qf[c][j][1]);
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
           const int i = 2 * u + r;
-          int val = acc[0][2 * r] * 128 + acc[0][2 * r + 1] + nz[r][j] * SQV(0, j);
+          int val = acc[0][2 * r] * 128 + acc[0][2 * r + 1] + nz[r][j] * SQ[0][j];
           if constexpr (KO) {
-            const int vh = acc[1][2 * r] * 128 + acc[1][2 * r + 1] + nz[r][j] * SQV(1, j);
-            const int vf = acc[2][2 * r] * 128 + acc[2][2 * r + 1] + nz[r][j] * SQV(2, j);
+            const int vh = acc[1][2 * r] * 128 + acc[1][2 * r + 1] + nz[r][j] * SQ[1][j];
+            const int vf = acc[2][2 * r] * 128 + acc[2][2 * r + 1] + nz[r][j] * SQ[2][j];
             const bool hfl = (j & 1) ? static_cast<int>(ksw[i][j >> 1]) < 0 : (ksw[i][j >> 1] & 0x8000u) != 0;
             val = ffl[i] ? vf : (hfl ? vh : val);
           }
@@ -862,8 +805,8 @@ __global__ void __launch_bounds__(128, FR_DEC_MINB) k_decode(const DecodeParams 
 #pragma unroll
     for (int ww = 0; ww < 4; ++ww) {
       const int j = 2 * mm + (ww >> 1), d = 64 * mm + 16 * ww + gid;
-      scr[w * WS + tig * 128 + d] = OF(mm, ww, 0) - Zf[j];
-      scr[w * WS + tig * 128 + d + 8] = OF(mm, ww, 1) - Zf[j];
+      scr[w * WS + tig * 128 + d] = Of[mm][ww][0] - Zf[j];
+      scr[w * WS + tig * 128 + d + 8] = Of[mm][ww][1] - Zf[j];
     }
   if (gid == 0) { scr[w * WS + 512 + tig] = m_run; scr[w * WS + 516 + tig] = l_run; }
   cta_finish(p, scr, b, kvh, qt, NT, split, nparts, nsp, &last_flag);
