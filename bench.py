@@ -412,7 +412,7 @@ def main():
                 "d2h_bytes_per_step": int(st["out_host"].numel() * 2), "ms_per_step": ms_e2e,
                 "launch": ("separate launches from Python" if (not a.graph or kvseq) else
                            "one CUDA graph per step: 3 host-to-device copies, writer, decode, copy back")},
-        "gpu_launches": (4 if kvseq else 3) * a.steps,
+        "gpu_launches": (3 if kvseq else 2) * a.steps,   # append (keys + value rows, one launch), decode [, merge]
         "roofline": {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak, "traffic": traffic,
                      "kernel": "k_decode<4, key-only>" if w["nb"] == 4 else "k_decode<2, key-only>", "peak_source": which,
                      "us_per_launch": ms_dec * 1e3, "algorithmic_bytes": nloc, "frac_of_8000": ach / 8000.0},

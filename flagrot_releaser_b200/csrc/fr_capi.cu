@@ -103,9 +103,7 @@ int fr_cb_write(const void* kv, long long kv_ts, const long long* slots, int slo
   if (!kind_info(kind, nb)) return -4;
   if (page != 16 && page != 32) return -5;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const int rc = fr::dyn_keys_launch(nb, kv, kv_ts, slots, slot_ph, T, Hkv, page, CT, kmu, pool, st);
-  if (rc) return rc;
-  return fr::rows_launch(nb, kv, kv_ts, slots, slot_ph, T, Hkv, page, nullptr, nullptr, nullptr, pool, Hkv, Hkv, 1, st);
+  return fr::dyn_keys_launch(nb, kv, kv_ts, slots, slot_ph, T, Hkv, page, CT, kmu, pool, st, 1);   // keys and value rows
 }
 
 int fr_cb_write3(const void* kv, long long kv_ts, const long long* slots, int slot_ph, int T, int Hkv, int page,
@@ -117,10 +115,8 @@ int fr_cb_write3(const void* kv, long long kv_ts, const long long* slots, int sl
   if (!kind_info(kind, nb)) return -4;
   if (page != 16 && page != 32) return -5;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (nchunk >= 0) {
-    const int rc = fr::dyn_keys_launch(nb, kv, kv_ts, slots, slot_ph, T, Hkv, page, CT, kmu, pool, st);
-    if (rc) return rc;
-  }
+  if (nchunk >= 0 && nchunk_v >= 0) return fr::dyn_keys_launch(nb, kv, kv_ts, slots, slot_ph, T, Hkv, page, CT, kmu, pool, st, 1);
+  if (nchunk >= 0) return fr::dyn_keys_launch(nb, kv, kv_ts, slots, slot_ph, T, Hkv, page, CT, kmu, pool, st, 0);
   if (nchunk_v >= 0)
     return fr::rows_launch(nb, kv, kv_ts, slots, slot_ph, T, Hkv, page, nullptr, nullptr, nullptr, pool, Hkv, Hkv, 1, st);
   return 0;
@@ -185,7 +181,10 @@ int fr_attn_partial(int fmt, const void* q, long long q_bs, const uint8_t* pool,
                      nullptr, 0, tail, tail_len, tail_idx, tail_bs, tail_ts, stream, kv_start, part);
 }
 
-int fr_device_status() { return fr::decode_status(); }
+int fr_device_status() {
+  const int d = fr::decode_status();
+  return d != 0 ? d : fr::writer_status();
+}
 
 }  // extern "C"
 

@@ -12,7 +12,7 @@ int rows_launch(int nb, const void* kv, long long kv_ts, const long long* slots,
                 const uint8_t* mask, const uint8_t* hfull, const float* kmu, uint8_t* pool, int row0, int nrow,
                 int shared15, cudaStream_t st);
 int dyn_keys_launch(int nb, const void* kv, long long kv_ts, const long long* slots, int slot_ph, int T, int Hkv, int page,
-                    const float* CT, const float* kmu, uint8_t* pool, cudaStream_t st);
+                    const float* CT, const float* kmu, uint8_t* pool, cudaStream_t st, int with_values = 0);
 
 // paged decode attention (fr_decode.cu)
 struct DecodeParams {
@@ -34,6 +34,7 @@ struct DecodeParams {
 };
 int decode_launch(const DecodeParams& p, cudaStream_t st);
 int decode_occupancy(int nb, int key_only);
+int writer_status();   // 0, or the source line of the staging wait that gave up (sticky; results stay correct)
 int decode_status();   // 0, or the source line of a bounded wait that gave up (sticky)
 
 }  // namespace fr

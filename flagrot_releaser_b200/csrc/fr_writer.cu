@@ -11,13 +11,15 @@
 //               key centring, per-block H32, group quantizer, scatter into the page.  Used for the static formats
 //               (all rows) and for the value rows of the dynamic kinds.
 //   k_dyn_keys  one CTA of 128 threads per (kv head, TG tokens).  Thread i owns dimension i, so the 32 x 32 and
-//               128 x 128 weighted-error products read C_q^T rows fully coalesced (L1 / L2 resident, 64 KB per head) and
-//               accumulate in the reference's sequential fp32 order; the whole-head candidate is evaluated by one warp
+//               128 x 128 weighted-error products read C_q^T rows fully coalesced (L1 / L2 resident, 64 KB per head; for a
+//               decode append of a few tokens the head's C_q^T is first staged in shared memory by a bulk copy, which
+//               takes the L2 latency out of the 128-step sums) and accumulate in the reference's sequential fp32 order; the whole-head candidate is evaluated by one warp
 //               per token in the row mapping.  No tensor cores: the criterion is defined by its fp32 operation order.
 // V^T code words are shared by 8 tokens; a token only ever flips the bits of its own field (fr::put_field), so tokens
 // of one word may be written by different warps, kernels or streams in any order.
 #include "fr_common.cuh"
 #include "fr_kernels.h"
+#include "fr_tc5.cuh"
 
 namespace fr {
 
@@ -99,9 +101,9 @@ struct RowParams {
 };
 
 template <int NB>
-__global__ void __launch_bounds__(128) k_rows(const RowParams p) {
+FR_DEVI void rows_block(const RowParams& p, long long block) {
   const int lane = threadIdx.x & 31;
-  const long long item = static_cast<long long>(blockIdx.x) * 4 + (threadIdx.x >> 5);
+  const long long item = block * 4 + (threadIdx.x >> 5);
   if (item >= static_cast<long long>(p.T) * p.nrow) return;
   const int t = static_cast<int>(item / p.nrow), hr = p.row0 + static_cast<int>(item % p.nrow);
   const bool isv = hr >= p.Hkv;
@@ -144,6 +146,9 @@ __global__ void __launch_bounds__(128) k_rows(const RowParams p) {
   else store_v_row<NB>(chunk, P, pos, lane, code, word, p.shared15 != 0);
 }
 
+template <int NB>
+__global__ void __launch_bounds__(128) k_rows(const RowParams p) { rows_block<NB>(p, blockIdx.x); }
+
 // ------------------------------------------------------------------------------------------------ dynamic key writer
 struct DynParams {
   const __nv_bfloat16* kv; long long kv_ts;
@@ -154,8 +159,22 @@ struct DynParams {
   uint8_t* pool;
 };
 
-template <int NB, int TG>
-__global__ void __launch_bounds__(128) k_dyn_keys(const DynParams p) {
+static __device__ __forceinline__ uint32_t wsmem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+__device__ int g_wstatus;                   // != 0: the staging copy of C_q^T did not arrive in time (the kernel then read global memory)
+
+// rows.T > 0 (STAGED launches only): the grid has extra rows y >= ceil(T / TG) whose CTAs write the value rows of the same
+// tokens (rows_block), so that an append is one launch; key and value writers only flip bits of their own fields
+template <int NB, int TG, bool STAGED>
+__global__ void __launch_bounds__(128) k_dyn_keys(const DynParams p, const RowParams rows) {
+  if (STAGED && rows.T > 0) {
+    const int groups = (p.T + TG - 1) / TG;
+    if (static_cast<int>(blockIdx.y) >= groups) {
+      rows_block<NB>(rows, static_cast<long long>(blockIdx.y - groups) * gridDim.x + blockIdx.x);
+      return;
+    }
+  }
+  extern __shared__ __align__(128) float cts[];   // STAGED: C_q^T of this head [128 (k)][128 (i)]
+  __shared__ __align__(8) uint64_t ctbar;
   __shared__ float xs[TG][HD];              // centred key rows
   __shared__ float es[TG][2][HD];           // reconstruction errors of the head candidates (base, F)
   __shared__ float ps[TG][2][HD];           // e_i * u_i
@@ -163,9 +182,21 @@ __global__ void __launch_bounds__(128) k_dyn_keys(const DynParams p) {
   __shared__ uint16_t ws[TG][2][4];         // stored scale words (base: with the H32 flag)
   __shared__ float herr[TG][2];
   const int i = threadIdx.x, lane = i & 31, j = i >> 5;
-  const int h = blockIdx.x, t0 = blockIdx.y * TG;
+  const int h = blockIdx.x;
+  const float* CT = p.CT + static_cast<size_t>(h) * HD * HD;
+  if (STAGED && i == 0) {
+    tc5::mbar_init(wsmem_u32(&ctbar), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    tc5::mbar_expect(wsmem_u32(&ctbar), HD * HD * 4);
+#pragma unroll
+    for (int c = 0; c < 4; ++c)
+      tc5::bulk_g2s(wsmem_u32(cts) + c * (HD * HD), reinterpret_cast<const uint8_t*>(CT) + c * (HD * HD), HD * HD,
+                    wsmem_u32(&ctbar));
+  }
+  if (STAGED) __syncthreads();
+  bool staged = !STAGED;
+  for (int t0 = blockIdx.y * TG; t0 < p.T; t0 += gridDim.y * TG) {
   const int ntok = min(TG, p.T - t0);
-  const float* __restrict__ CT = p.CT + static_cast<size_t>(h) * HD * HD;
 
   // ---- A1: local candidates I / H32 of 32-vector j (dim mapping), block-diagonal weighted error, first argmin
 #pragma unroll
@@ -179,9 +210,14 @@ __global__ void __launch_bounds__(128) k_dyn_keys(const DynParams p) {
     const float e0 = __fsub_rn(quant_err_deq<NB>(z, mn0, mx0), z);
     const float e1 = __fsub_rn(fwht32_lane(quant_err_deq<NB>(y1, mn1, mx1), lane), z);
     float u0 = 0.f, u1 = 0.f;
+    if (!staged) {                     // first use of C_q^T: the copy has had the loads and the Hadamard above to arrive
+      staged = true;
+      if (tc5::mbar_wait(wsmem_u32(&ctbar), 0)) CT = cts;
+      else if (i == 0) atomicExch(&g_wstatus, __LINE__);
+    }
 #pragma unroll
     for (int k = 0; k < 32; ++k) {   // fully unrolled: the 32 loads do not depend on the sum chain and go out together
-      const float cv = __ldg(CT + (32 * j + k) * HD + i);                  // C[i][32 j + k]
+      const float cv = STAGED ? CT[(32 * j + k) * HD + i] : __ldg(CT + (32 * j + k) * HD + i);   // C[i][32 j + k]
       const float p0 = __fmul_rn(cv, __shfl_sync(FULLMASK, e0, k));
       const float p1 = __fmul_rn(cv, __shfl_sync(FULLMASK, e1, k));
       u0 = k == 0 ? p0 : __fadd_rn(u0, p0);
@@ -230,7 +266,7 @@ __global__ void __launch_bounds__(128) k_dyn_keys(const DynParams p) {
       float U[TG][2];
 #pragma unroll 16
       for (int k = 0; k < 32; ++k) {
-        const float cv = __ldg(CT + (32 * b + k) * HD + i);
+        const float cv = STAGED ? CT[(32 * b + k) * HD + i] : __ldg(CT + (32 * b + k) * HD + i);
 #pragma unroll
         for (int t = 0; t < TG; ++t)
 #pragma unroll
@@ -263,7 +299,7 @@ __global__ void __launch_bounds__(128) k_dyn_keys(const DynParams p) {
   if (j < ntok) {
     const int t = j;
     const long long slot = p.slot_ph ? p.slots[static_cast<long long>(t0 + t) * p.Hkv + h] : p.slots[t0 + t];
-    if (slot < 0) return;
+    if (slot >= 0) {
     const bool F = herr[t][1] < herr[t][0];
     const int c = F ? 1 : 0;
     const int P = p.page;
@@ -276,6 +312,9 @@ __global__ void __launch_bounds__(128) k_dyn_keys(const DynParams p) {
     store_k_row<NB>(chunk, P, pos, lane, code, ws[t][c][lane >> 3]);
     if (lane == 0)   // the key's whole-head flag rides in bit 15 of the token's V group-0 scale word
       put_word_bit15(chunk, Lay<NB>::vs_off(P) + 2 * (8 * (pos >> 3) + vslot8(pos)), F);
+    }
+  }
+  __syncthreads();                     // the next group of tokens reuses the shared arrays
   }
 }
 
@@ -304,22 +343,66 @@ int rows_launch(int nb, const void* kv, long long kv_ts, const long long* slots,
   return check_launch();
 }
 
-template <int NB>
-static int dyn_keys_nb(const DynParams& p, cudaStream_t st) {
-  const long long items = static_cast<long long>(p.T) * p.Hkv;
-  const int tg = items <= 1024 ? 1 : items <= 4096 ? 2 : 4;
-  const dim3 grid(p.Hkv, (p.T + tg - 1) / tg);
-  if (tg == 1) k_dyn_keys<NB, 1><<<grid, 128, 0, st>>>(p);
-  else if (tg == 2) k_dyn_keys<NB, 2><<<grid, 128, 0, st>>>(p);
-  else k_dyn_keys<NB, 4><<<grid, 128, 0, st>>>(p);
+constexpr int DYN_SMEM = HD * HD * 4;        // the staged C_q^T
+
+// a decode append (a few tokens per head): one wave of CTAs with C_q^T staged in shared memory, the latency of the
+// 128-step sums is then shared-memory latency; returns 1 when the shape does not fit one wave
+template <int NB, int TG>
+static int dyn_keys_staged(const DynParams& p, const RowParams& rows, cudaStream_t st) {
+  static int slots = -1;                     // resident CTAs of the staged kernel on this device
+  if (slots < 0) {
+    int dev = 0, sms = 0, occ = 0;
+    if (cudaFuncSetAttribute(k_dyn_keys<NB, TG, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, DYN_SMEM) != cudaSuccess ||
+        cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, k_dyn_keys<NB, TG, true>, 128, DYN_SMEM) != cudaSuccess || occ < 1)
+      return -2;
+    slots = sms * occ;
+  }
+  const int groups = (p.T + TG - 1) / TG;
+  if (static_cast<long long>(groups) * p.Hkv > slots) return 1;
+  const long long rblocks = (static_cast<long long>(rows.T) * rows.nrow + 3) / 4;
+  const int extra = static_cast<int>((rblocks + p.Hkv - 1) / p.Hkv);
+  k_dyn_keys<NB, TG, true><<<dim3(p.Hkv, groups + extra), 128, DYN_SMEM, st>>>(p, rows);
   return check_launch();
 }
 
+// rows.T > 0: also write those value rows (in the same launch when the append path takes it, else in a second launch)
+template <int NB>
+static int dyn_keys_nb(const DynParams& p, const RowParams& rows, cudaStream_t st) {
+  const long long items = static_cast<long long>(p.T) * p.Hkv;
+  if (items <= 1024) {
+    const int rc = items <= 256 ? dyn_keys_staged<NB, 1>(p, rows, st) : dyn_keys_staged<NB, 2>(p, rows, st);
+    if (rc != 1) return rc;
+  }
+  if (rows.T > 0) {
+    const unsigned blocks = static_cast<unsigned>((static_cast<long long>(rows.T) * rows.nrow + 3) / 4);
+    k_rows<NB><<<blocks, 128, 0, st>>>(rows);
+  }
+  RowParams none = rows;
+  none.T = 0;
+  // many tokens: C_q^T through L1 / L2 (coalesced rows), more resident CTAs, groups of up to 4 tokens share every value read
+  const int tg = items <= 1024 ? 1 : items <= 4096 ? 2 : 4;
+  const dim3 grid(p.Hkv, (p.T + tg - 1) / tg);
+  if (tg == 1) k_dyn_keys<NB, 1, false><<<grid, 128, 0, st>>>(p, none);
+  else if (tg == 2) k_dyn_keys<NB, 2, false><<<grid, 128, 0, st>>>(p, none);
+  else k_dyn_keys<NB, 4, false><<<grid, 128, 0, st>>>(p, none);
+  return check_launch();
+}
+
+int writer_status() {
+  int v = 0;
+  cudaMemcpyFromSymbol(&v, g_wstatus, sizeof(int));
+  return v;
+}
+
+// with_values: also the value rows [Hkv, 2 Hkv) of the same tokens (one launch for a decode append, else two)
 int dyn_keys_launch(int nb, const void* kv, long long kv_ts, const long long* slots, int slot_ph, int T, int Hkv, int page,
-                    const float* CT, const float* kmu, uint8_t* pool, cudaStream_t st) {
+                    const float* CT, const float* kmu, uint8_t* pool, cudaStream_t st, int with_values) {
   if (T <= 0) return 0;
   DynParams p{static_cast<const __nv_bfloat16*>(kv), kv_ts, slots, slot_ph, T, Hkv, page, CT, kmu, pool};
-  return nb == 4 ? dyn_keys_nb<4>(p, st) : dyn_keys_nb<2>(p, st);
+  RowParams rows{static_cast<const __nv_bfloat16*>(kv), kv_ts, slots, slot_ph, with_values ? T : 0, Hkv, page, nullptr, nullptr,
+                 nullptr, pool, Hkv, Hkv, 1};
+  return nb == 4 ? dyn_keys_nb<4>(p, rows, st) : dyn_keys_nb<2>(p, rows, st);
 }
 
 }  // namespace fr
