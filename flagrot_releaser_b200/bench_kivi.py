@@ -110,7 +110,7 @@ def main():
         "config": {"workload": f"kivi2:32 decode, batch {a.batch} x ctx {a.ctx}, {a.hq} q / {a.hkv} kv heads, page 16, s4w128",
                    "nsplit": ns, "chunk": chunk, "l2": f"{len(pools)} distinct {pools[0].numel() >> 20} MiB pools cycled"},
         "roofline": {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak, "peak_source": which,
-                     "kernel": "k_kv_attn_mma (page splits + BF16 window split) + k_kv_merge", "us_per_launch": ms * 1e3, "algorithmic_bytes": nbytes},
+                     "kernel": "k_kv_attn_mma2 (page splits + BF16 window split) + k_kv_merge", "us_per_launch": ms * 1e3, "algorithmic_bytes": nbytes},
         "writers": {"kv_v_write_us_per_token": us_v, "kv_k_encode_us_per_token": us_k},
         "gpu_launches": 3 * a.steps, "data": "synthetic"}))
 

@@ -694,11 +694,15 @@ __global__ void k_kv_lse_merge(const __nv_bfloat16* __restrict__ oa, const float
 }
 
 #include "kv_attn_mma.cuh"
+#include "kv_attn_mma2.cuh"
 
-// FLAGROT_KIVI_ATTN=cuda keeps the page splits on the fp32 CUDA-core kernel (read at every launch)
-bool kivi_use_mma() {
+// FLAGROT_KIVI_ATTN (read at every launch): "cuda" keeps the page splits on the fp32 CUDA-core kernel, "warp" uses the
+// tensor-core kernel with per-warp accumulators (k_kv_attn_mma); default: the CTA-synchronous one (k_kv_attn_mma2)
+int kivi_path() {
   const char* e = std::getenv("FLAGROT_KIVI_ATTN");
-  return !(e != nullptr && std::strcmp(e, "cuda") == 0);
+  if (e != nullptr && std::strcmp(e, "cuda") == 0) return 0;
+  if (e != nullptr && std::strcmp(e, "warp") == 0) return 1;
+  return 2;
 }
 
 template <int G>
@@ -721,7 +725,19 @@ int launch_attn(const void* q, long long q_rs, const void* pool, const void* bt,
   auto* opp = static_cast<float*>(opart);
   auto* mlp = static_cast<float*>(ml);
   if constexpr (G <= 8) {
-    if (kivi_use_mma()) {          // page splits and the BF16 sink / window split in one launch
+    const int path = kivi_path();
+    if (path == 2) {
+      static bool set3 = false;
+      if (!set3) {
+        if (cudaFuncSetAttribute(kvm::k_kv_attn_mma2<G>, cudaFuncAttributeMaxDynamicSharedMemorySize, kvm::SMEM2) != cudaSuccess) return 1;
+        set3 = true;
+      }
+      static_assert(kvm::TAIL_SMEM <= kvm::SMEM2, "the window split runs in the page-split kernel's shared memory");
+      kvm::k_kv_attn_mma2<G><<<dim3(Hkv, NS, 2 * B), 128, kvm::SMEM2, st>>>(qp, q_rs, pp, btp, bt_rs, cp, kv_start, Hkv, NS, chunk, qscale,
+                                                                            rp, tlp, tip, T, B, opp, mlp);
+      return 0;
+    }
+    if (path == 1) {          // page splits and the BF16 sink / window split in one launch
       static bool set2 = false;
       if (!set2) {
         if (cudaFuncSetAttribute(kvm::k_kv_attn_mma<G>, cudaFuncAttributeMaxDynamicSharedMemorySize, kvm::SMEM) != cudaSuccess) return 1;
