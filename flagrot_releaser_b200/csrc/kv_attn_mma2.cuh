@@ -44,7 +44,8 @@ __global__ void __launch_bounds__(128, KVM2_MINB) k_kv_attn_mma2(const __nv_bflo
     for (int e = tid; e < G; e += 128) { mlp[2 * e] = KV_NEG_INF; mlp[2 * e + 1] = 0.f; }
     return;
   }
-  // ---- q in three bases (rows >= G are zero), rows re-laid with a padded stride, times qscale * 16
+  // ---- q in three bases (rows >= G are zero), rows re-laid with a padded stride, times qscale * 16 (channels 8 - 15 of
+  // every 16: times qscale / 16, their key codes enter the MMA 2^8 larger, see the QK step)
   {
     const __nv_bfloat16* qp = q + static_cast<long long>(b) * q_rs + static_cast<long long>(h) * G * D;
     for (int e = tid; e < 8 * D; e += 128) {
@@ -61,7 +62,7 @@ __global__ void __launch_bounds__(128, KVM2_MINB) k_kv_attn_mma2(const __nv_bflo
 #pragma unroll
     for (int i = 0; i < 24; ++i) {
       const int e = tid + 128 * i;
-      reinterpret_cast<float*>(smraw)[(e / D) * QSTR + e % D] = v[i] * (qscale * 16.f);
+      reinterpret_cast<float*>(smraw)[(e / D) * QSTR + e % D] = v[i] * ((e & 8) ? qscale * (1.f / 16.f) : qscale * 16.f);
     }
     __syncthreads();
   }
@@ -118,7 +119,7 @@ __global__ void __launch_bounds__(128, KVM2_MINB) k_kv_attn_mma2(const __nv_bflo
       const bool useF = ((lds32(rA + OFF_KM + 16) >> 15) & 1u) != 0;
       // ---- A fragments of QK: lane (head g8, c4) holds channels 16 kk + 2 c4 + {0, 1, 8, 9}
       uint32_t qa[8][2];
-      float bias = 0.f;
+      float bias = 0.f, bias8 = 0.f;                 // bias8: the terms of channels 8 - 15 of every 16 (q there is 2^-8 small)
 #pragma unroll
       for (int kk = 0; kk < 8; ++kk) {
         const int which = useF ? 2 : static_cast<int>((lmask >> (kk >> 1)) & 1u);
@@ -128,22 +129,28 @@ __global__ void __launch_bounds__(128, KVM2_MINB) k_kv_attn_mma2(const __nv_bflo
         const uint2 qx = lds64(qbs + ((which * 8 + g8) * QSTR + c0) * 4), qy = lds64(qbs + ((which * 8 + g8) * QSTR + c0 + 8) * 4);
         const float2 a0 = unpack_h2(ma.x), a1 = unpack_h2(ma.y), b0 = unpack_h2(mb.x), b1 = unpack_h2(mb.y);   // (scale | flag, min)
         const float q0 = __uint_as_float(qx.x), q1 = __uint_as_float(qx.y), q2 = __uint_as_float(qy.x), q3 = __uint_as_float(qy.y);
-        qa[kk][0] = pack_h2(q0 * fabsf(a0.x), q1 * fabsf(a1.x));      // q is stored times qscale * 16
+        qa[kk][0] = pack_h2(q0 * fabsf(a0.x), q1 * fabsf(a1.x));      // q is stored times qscale * 16 | qscale / 16
         qa[kk][1] = pack_h2(q2 * fabsf(b0.x), q3 * fabsf(b1.x));
-        bias = fmaf(q0, a0.y, fmaf(q1, a1.y, fmaf(q2, b0.y, fmaf(q3, b1.y, bias))));
+        bias = fmaf(q0, a0.y, fmaf(q1, a1.y, bias));
+        bias8 = fmaf(q2, b0.y, fmaf(q3, b1.y, bias8));
       }
+      bias = fmaf(bias8, 256.f, bias);
       bias += __shfl_xor_sync(FULLMASK, bias, 1);
       bias += __shfl_xor_sync(FULLMASK, bias, 2);
       bias *= 1.f / 16.f;
-      // ---- QK: B = key codes of token 8 nt + g8, word kk: pairs (2 c4, 2 c4 + 1) and (2 c4 + 8, 2 c4 + 9) of the word
+      // ---- QK: B = key codes of token 8 nt + g8, word kk rotated right by 2 c4: the pair (2 c4, 2 c4 + 1) then sits in
+      // mantissa bits 0 - 1 of the two halves (code * 2^-24), the pair (2 c4 + 8, 2 c4 + 9) in bits 8 - 9 (code * 2^-16): two
+      // masks, no further shifts; the 2^8 between them is in the q table, the common 2^20 in the score epilogue
 #pragma unroll
       for (int nt = 0; nt < 4; ++nt) {
         const uint32_t kp = (nt < 2 ? rA : rB) + ((8 * nt + g8) & 15) * 32;
         const uint4 w0 = lds128(kp), w1 = lds128(kp + 16);
         const uint32_t wd[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk)
-          mma(s[nt], qa[kk][0], 0u, qa[kk][1], 0u, (wd[kk] << (8 - 2 * c4)) & 0x03000300u, (wd[kk] >> (2 * c4)) & 0x03000300u);
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t r = __funnelshift_r(wd[kk], wd[kk], 2 * c4);
+          mma(s[nt], qa[kk][0], 0u, qa[kk][1], 0u, r & 0x00030003u, r & 0x03000300u);
+        }
       }
       // ---- scores of head g8 (this lane: tokens 8 nt + 2 c4 + e), the group's maximum
 #pragma unroll
@@ -151,13 +158,15 @@ __global__ void __launch_bounds__(128, KVM2_MINB) k_kv_attn_mma2(const __nv_bflo
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
           const int pos = base + 8 * nt + 2 * c4 + e;
-          const float v = (pos >= t0 && pos < t1) ? fmaf(s[nt][e], 4096.f, bias) : KV_NEG_INF;
+          const float v = (pos >= t0 && pos < t1) ? fmaf(s[nt][e], 1048576.f, bias) : KV_NEG_INF;
           s[nt][e] = v;
           mx = fmaxf(mx, v);
         }
       mx = fmaxf(mx, __shfl_xor_sync(FULLMASK, mx, 1));
       mx = fmaxf(mx, __shfl_xor_sync(FULLMASK, mx, 2));
-      // ---- value tile: lane = token; word w -> pairs (i, i + 8) of its 16 channels, code in mantissa bits 8 - 9
+      // ---- value tile: lane = token; word w -> pairs (i, i + 8) of its 16 channels.  The code stays where it is in the word
+      // (fields 0 - 4) or where one shift by 10 puts it (fields 5 - 7): mantissa bits 2 i' .. 2 i' + 1, i' = i mod 5, i.e.
+      // code * 2^(2 i' - 24); the power of two of a tile column is taken out once, in the epilogue
       {
         const uint32_t vp = (lane < 16 ? rA : rB) + OFF_VC + (lane & 15) * 32;
         const uint4 w0 = lds128(vp), w1 = lds128(vp + 16);
@@ -166,7 +175,7 @@ __global__ void __launch_bounds__(128, KVM2_MINB) k_kv_attn_mma2(const __nv_bflo
         for (int w = 0; w < 8; ++w) {
           uint32_t o[8];
 #pragma unroll
-          for (int i = 0; i < 8; ++i) o[i] = (2 * i <= 8 ? (wd[w] << (8 - 2 * i)) : (wd[w] >> (2 * i - 8))) & 0x03000300u;
+          for (int i = 0; i < 8; ++i) o[i] = i < 5 ? (wd[w] & (0x00030003u << (2 * i))) : ((wd[w] >> 10) & (0x00030003u << (2 * (i - 5))));
           sts128(wvt + lane * VT_STRIDE + 32 * w, o[0], o[1], o[2], o[3]);
           sts128(wvt + lane * VT_STRIDE + 32 * w + 16, o[4], o[5], o[6], o[7]);
         }
@@ -291,9 +300,11 @@ __global__ void __launch_bounds__(128, KVM2_MINB) k_kv_attn_mma2(const __nv_bflo
     for (int e = 0; e < 2; ++e) {
       const int col = 32 * warp + 8 * nt + 2 * c4 + e;
       const int ch = (col & ~15) + ((col & 15) >> 1) + 8 * (col & 1);
-      accs[(0 * 8 + g8) * D + ch] = accIH[nt][e];
-      accs[(1 * 8 + g8) * D + ch] = accIH[nt][2 + e];
-      accs[(2 * 8 + g8) * D + ch] = sawF ? accF[nt][e] : 0.f;
+      const int fi = (col & 15) >> 1;                      // field of the column's channel pair: code * 2^(2 (fi mod 5) - 24)
+      const float cf = __int_as_float((127 + 8 - 2 * (fi < 5 ? fi : fi - 5)) << 23);   // relative to the 2^-16 the rest assumes
+      accs[(0 * 8 + g8) * D + ch] = accIH[nt][e] * cf;
+      accs[(1 * 8 + g8) * D + ch] = accIH[nt][2 + e] * cf;
+      accs[(2 * 8 + g8) * D + ch] = sawF ? accF[nt][e] * cf : 0.f;
     }
   if (c4 == 0) {
     zs[(0 * 8 + g8) * 4 + warp] = zI;
