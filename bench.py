@@ -329,6 +329,7 @@ def main():
     ap.add_argument("--nsplit", type=int, default=0, help="force the split count (0: the planner's choice)")
     ap.add_argument("--ncopy", type=int, default=3)
     ap.add_argument("--cpu-steps", type=int, default=3)
+    ap.add_argument("--no-step-graph", action="store_true", help="resident step: separate launches from Python instead of a CUDA graph")
     ap.add_argument("--graph", action="store_true", help="e2e: one CUDA graph per step (flagrot_releaser_b200.graphs.HostStep) "
                                                          "instead of separate launches from Python; measured equal within noise")
     a = ap.parse_args()
@@ -374,7 +375,20 @@ def main():
         ms = timed(lambda i: step_kvseq(st, i, dist=dist), a.steps, a.warmup, dist)
         ms_e2e = timed(lambda i: step_kvseq(st, i, e2e=True, dist=dist), a.steps, a.warmup, dist)
     else:
-        ms = timed(lambda i: step(st, i), a.steps, a.warmup, dist)
+        if a.no_step_graph:
+            ms = timed(lambda i: step(st, i), a.steps, a.warmup, dist)
+        else:
+            # the resident step (append + decode) is replayed as one CUDA graph per pool copy: the same two kernels, one launch
+            # from Python, so that the figure does not depend on how fast the host thread of a rank issues launches
+            vg = []
+            for c in range(len(st["pools"])):
+                step(st, c)                                             # first calls set kernel attributes
+                torch.cuda.synchronize()
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g):
+                    step(st, c)
+                vg.append(g)
+            ms = timed(lambda i: vg[i % len(vg)].replay(), a.steps, a.warmup, dist)
         ms_e2e = timed(lambda i: step(st, i, e2e=True), a.steps, a.warmup, dist)
     ms_dec = timed(lambda i: decode_only(st, i), a.steps, a.warmup, None)
     clocks = sampler.stop() if rank == 0 else None
@@ -406,7 +420,8 @@ def main():
                    "parallelism": ((f"kv-sequence sharded x{world}, NCCL all-gather of (o, m, l) rows + LSE merge" if kvseq
                                     else f"batch-sharded x{world}") if world > 1 else "single gpu"),
                    "step": ("fr_cb_write (last rank) + fr_attn_partial + all-gather + merge" if kvseq
-                            else "fr_cb_write (T = batch) + fr_cb_attn"), "device_status": status},
+                            else "fr_cb_write (T = batch) + fr_cb_attn" + ("" if a.no_step_graph else ", replayed as one CUDA graph")),
+                   "device_status": status},
         "e2e": {"value": nwork / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s",
                 "h2d_bytes_per_step": int(st["q_host"].numel() * 2 + st["kv_host"].numel() * 2 + B * 8),
                 "d2h_bytes_per_step": int(st["out_host"].numel() * 2), "ms_per_step": ms_e2e,
