@@ -5,6 +5,7 @@
 
 A step = one pass of the hot path over one batch: the dynamic writer appends one token per sequence (fr_cb_write, T = B)
 and the paged decode attention reads every sequence's cache (fr_cb_attn), with the 4 sink + 128 window tokens in BF16.
+The resident step is captured once per pool copy and replayed as a CUDA graph (--no-step-graph: two launches from Python).
 metric: decode-attention KV GB/s = algorithmic bytes of the decode read (pages [S, L - W) * 144 B per (token, kv head) +
 BF16 window rows + q / out) divided by the step time.  `value` has every input resident in HBM; `e2e` measures the same
 step through the C-ABI front end with this step's q / new kv / slots copied from pinned host memory and the output
