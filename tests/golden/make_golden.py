@@ -1,6 +1,6 @@
 """Generates tests/golden/*.npz by running the reference's own PyTorch code on CPU on seeded inputs.
 
-    python tests/golden/make_golden.py [/path/to/reference]      (the reference checkout; a built-in default is used when omitted)
+    python tests/golden/make_golden.py [/path/to/reference]      (the reference checkout; else $FLAGROT_REFERENCE, else ./reference)
 
 What is recorded (inputs as bf16 bit patterns, outputs exactly as the reference returned them):
   writer_dynamic.npz   kernels/codebook_ref.encode (cfg konlya / konlya2, qk asym / asym2) for keys and values, incl. the
@@ -19,6 +19,7 @@ The reference runs on CPU here, so its scale is a true division ((max - min) / l
 from __future__ import annotations
 
 import math
+import os
 import sys
 from pathlib import Path
 
@@ -26,7 +27,7 @@ import numpy as np
 import torch
 
 HERE = Path(__file__).resolve().parent
-REF = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+REF = Path(sys.argv[1] if len(sys.argv) > 1 else os.environ.get("FLAGROT_REFERENCE", "reference"))   # checkout of the reference
 sys.path.insert(0, str(HERE.parents[1]))
 sys.path.insert(0, str(REF))
 sys.path.insert(0, str(REF / "kernels"))
