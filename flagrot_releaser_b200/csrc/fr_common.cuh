@@ -150,4 +150,17 @@ FR_DEVI void put_word_bit15(uint8_t* chunk, int byte_off, bool on) {
   if (on) atomicOr(wp, bit); else atomicAnd(wp, ~bit);
 }
 
+
+// ------------------------------------------------------------------------------------------------ host: launch set-up
+// The dynamic shared-memory limit of a kernel is a per-device attribute: a process that drives several GPUs has to raise
+// it on each of them.  `done` is one bit per device ordinal (a function-local static of the launcher).
+template <typename Kern> inline bool smem_limit_ready(Kern kernel, int bytes, unsigned long long& done) {
+  int dev = 0;
+  const bool known = cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < 64;
+  if (known && ((done >> dev) & 1ull)) return true;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess) return false;
+  if (known) done |= 1ull << dev;
+  return true;
+}
+
 }  // namespace fr

@@ -25,9 +25,6 @@
 #include <cmath>
 #include <type_traits>
 
-#include <cstdlib>
-#include <cstring>
-
 #include "fr_common.cuh"
 #include "fr_kernels.h"
 #include "fr_tc5.cuh"
@@ -38,13 +35,8 @@ namespace {
 
 constexpr int NWARP = 4;
 constexpr int BLK = 32;            // tokens per warp step
-#ifndef FR_DEC_ST
-#define FR_DEC_ST 3
-#endif
-#ifndef FR_DEC_MINB
-#define FR_DEC_MINB 3
-#endif
-constexpr int ST = FR_DEC_ST;      // bulk-copy stages per warp
+constexpr int ST = 3;              // bulk-copy stages per warp
+constexpr int MINB = 3;            // resident CTAs per SM the register budget is set for
 constexpr int MAXPG = 512;         // pages per split (chunk <= 8192 tokens of 16)
 #define NEG_INF (-INFINITY)
 
@@ -438,7 +430,7 @@ FR_DEVI void q_prologue(const DecodeParams& p, int b, int kvh, int qt, int16_t* 
 
 // ------------------------------------------------------------------------------------------------ the kernel
 template <int NB, bool KO>
-__global__ void __launch_bounds__(128, FR_DEC_MINB) k_decode(const DecodeParams p) {
+__global__ void __launch_bounds__(128, MINB) k_decode(const DecodeParams p) {
   constexpr int NV = KO ? 3 : 1;
   using L = DLay<NB>;
   using S = SMap<NB, NV>;
@@ -815,23 +807,12 @@ __global__ void __launch_bounds__(128, FR_DEC_MINB) k_decode(const DecodeParams 
 template <int NB, bool KO> int launch_k(const DecodeParams& p, cudaStream_t st) {
   constexpr int NV = KO ? 3 : 1;
   constexpr int smem = SMap<NB, NV>::TOTAL > TAILM_BYTES ? SMap<NB, NV>::TOTAL : TAILM_BYTES;
-  static bool set = false;
-  if (!set) {
-    if (cudaFuncSetAttribute(k_decode<NB, KO>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -2;
-    set = true;
-  }
+  static unsigned long long ready = 0;
+  if (!smem_limit_ready(k_decode<NB, KO>, smem, ready)) return -2;
   const int NT = (p.G + 3) / 4;
   const dim3 grid(p.Hkv * NT, p.nsplit, p.B * (p.tail != nullptr ? 2 : 1));
   k_decode<NB, KO><<<grid, 128, smem, st>>>(p);
   return cudaPeekAtLastError() == cudaSuccess ? 0 : -1;
-}
-
-#include "fr_decode_tc.cuh"
-
-// FLAGROT_DECODE_PATH=tc routes INT4 pages to the tcgen05 kernel (read at every launch; default: the mma.sync kernel)
-bool use_tc() {
-  const char* e = std::getenv("FLAGROT_DECODE_PATH");
-  return e != nullptr && std::strcmp(e, "tc") == 0;
 }
 
 }  // namespace
@@ -840,7 +821,6 @@ int decode_launch(const DecodeParams& p, cudaStream_t st) {
   if (p.B <= 0) return 0;
   if (p.page != 16) return -5;
   if (p.chunk <= 0 || p.chunk % 64 != 0 || p.chunk > MAXPG * 16 || p.nsplit < 1) return -3;
-  if (p.nb == 4 && use_tc()) return p.key_only ? launch_tc<4, true>(p, st) : launch_tc<4, false>(p, st);
   if (p.nb == 4) return p.key_only ? launch_k<4, true>(p, st) : launch_k<4, false>(p, st);
   return p.key_only ? launch_k<2, true>(p, st) : launch_k<2, false>(p, st);
 }
@@ -848,15 +828,7 @@ int decode_launch(const DecodeParams& p, cudaStream_t st) {
 int decode_occupancy(int nb, int key_only) {
   int n = 0;
   cudaError_t e;
-  if (nb == 4 && use_tc()) {
-    if (key_only) {
-      cudaFuncSetAttribute(k_decode_tc<4, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, TMap<4, 3>::TOTAL);
-      e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, k_decode_tc<4, true>, TC_THREADS, TMap<4, 3>::TOTAL);
-    } else {
-      cudaFuncSetAttribute(k_decode_tc<4, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, TMap<4, 1>::TOTAL);
-      e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, k_decode_tc<4, false>, TC_THREADS, TMap<4, 1>::TOTAL);
-    }
-  } else if (nb == 4 && key_only) {
+  if (nb == 4 && key_only) {
     cudaFuncSetAttribute(k_decode<4, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMap<4, 3>::TOTAL);
     e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, k_decode<4, true>, 128, SMap<4, 3>::TOTAL);
   } else if (nb == 4) {

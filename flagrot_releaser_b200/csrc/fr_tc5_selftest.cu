@@ -4,7 +4,10 @@
 //   mode 0  FP16 operands in shared memory, 128-byte swizzle            (K a multiple of 64, fp32 accumulators)
 //   mode 1  FP16 A operand in tensor memory, B as in mode 0             (K a multiple of 64)
 //   mode 2  u8 x s8 operands in shared memory, no swizzle, K = 32 steps (K a multiple of 32, s32 accumulators)
-// fr_tc5_selftest has no counterpart in the reference.
+// Built into the test-only library libflagrot_tc5test.so; not part of any C ABI, no counterpart in the reference.
+//   int fr_tc5_selftest(int mode, const void* A, const void* B, void* D, int N, int K, void* stream)
+// N a multiple of 16 <= 128; K a multiple of 64 <= 256 (modes 0 / 1) or of 32 <= 512 (mode 2).  Synchronises the stream.
+// Returns 0, -1 launch error, -3 bad shape, or the source line of a bounded wait that gave up.
 #include <cstdint>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
@@ -127,11 +130,8 @@ extern "C" int fr_tc5_selftest(int mode, const void* A, const void* B, void* D, 
   if (mode < 0 || mode > 2 || N < 16 || N > 128 || N % 16) return -3;
   if (mode == 2 ? (K % 32 || K > 512) : (K % 64 || K > 256)) return -3;
   const int smem = (mode == 2 ? (128 + N) * K : (128 + N) * K * 2) + 1024;
-  static bool set = false;
-  if (!set) {
-    if (cudaFuncSetAttribute(k_tc5_selftest, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess) return -2;
-    set = true;
-  }
+  static unsigned long long ready = 0;
+  if (!fr::smem_limit_ready(k_tc5_selftest, 200 * 1024, ready)) return -2;
   int zero = 0;
   cudaMemcpyToSymbolAsync(g_tc5_status, &zero, sizeof(int), 0, cudaMemcpyHostToDevice, static_cast<cudaStream_t>(stream));
   k_tc5_selftest<<<1, 128, smem, static_cast<cudaStream_t>(stream)>>>(mode, A, B, D, N, K);

@@ -349,15 +349,19 @@ constexpr int DYN_SMEM = HD * HD * 4;        // the staged C_q^T
 // 128-step sums is then shared-memory latency; returns 1 when the shape does not fit one wave
 template <int NB, int TG>
 static int dyn_keys_staged(const DynParams& p, const RowParams& rows, cudaStream_t st) {
-  static int slots = -1;                     // resident CTAs of the staged kernel on this device
-  if (slots < 0) {
-    int dev = 0, sms = 0, occ = 0;
-    if (cudaFuncSetAttribute(k_dyn_keys<NB, TG, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, DYN_SMEM) != cudaSuccess ||
-        cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
+  static int slots_of[64];                   // resident CTAs of the staged kernel, per device ordinal (0: not asked yet)
+  static unsigned long long ready = 0;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -2;
+  if (slots_of[dev] == 0) {
+    int sms = 0, occ = 0;
+    if (!smem_limit_ready(k_dyn_keys<NB, TG, true>, DYN_SMEM, ready) ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
         cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, k_dyn_keys<NB, TG, true>, 128, DYN_SMEM) != cudaSuccess || occ < 1)
       return -2;
-    slots = sms * occ;
+    slots_of[dev] = sms * occ;
   }
+  const int slots = slots_of[dev];
   const int groups = (p.T + TG - 1) / TG;
   if (static_cast<long long>(groups) * p.Hkv > slots) return 1;
   const long long rblocks = (static_cast<long long>(rows.T) * rows.nrow + 3) / 4;

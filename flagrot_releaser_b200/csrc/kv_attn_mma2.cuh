@@ -16,11 +16,8 @@ constexpr int P_BYTES = 4 * 8 * P_HSTR * 2;                // p of the step: [gr
 constexpr int SMEM2 = QB_BYTES + 4 * WARP_SMEM + P_BYTES + 256;   // + [4][8] group maxima, [4] flags
 static_assert(3 * (SMEM2 + 1024) <= 227 * 1024, "three CTAs per SM");
 
-#ifndef KVM2_MINB
-#define KVM2_MINB 3
-#endif
 template <int G>
-__global__ void __launch_bounds__(128, KVM2_MINB) k_kv_attn_mma2(const __nv_bfloat16* __restrict__ q, long long q_rs,
+__global__ void __launch_bounds__(128, 3) k_kv_attn_mma2(const __nv_bfloat16* __restrict__ q, long long q_rs,
                                                           const uint8_t* __restrict__ pool, const int* __restrict__ bt, long long bt_rs,
                                                           const int* __restrict__ cached, int kv_start, int Hkv, int NS, int chunk,
                                                           float qscale, const __nv_bfloat16* __restrict__ ring,
@@ -35,6 +32,7 @@ __global__ void __launch_bounds__(128, KVM2_MINB) k_kv_attn_mma2(const __nv_bflo
   }
   float (*qb)[8][D] = reinterpret_cast<float (*)[8][D]>(smraw);
   const int h = blockIdx.x, sp = blockIdx.y, b = blockIdx.z;
+  if (sp >= NS) return;                          // NS == 0: the grid still has one y row, but there is no page split
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g8 = lane >> 2, c4 = lane & 3;
   const long long pidx = static_cast<long long>(b * Hkv + h) * (NS + 1) + sp;
   float* op = opart + pidx * G * D;

@@ -10,15 +10,12 @@
 // operation rounded separately (reference kivi.cu:99-109).
 //
 // Kernels: k_v_write (warp per (token, head)), k_k_encode (CTA per (group, head); fp32 CUDA cores: the selection is
-// defined by fp32 sums), kvm::k_kv_attn_mma (kv_attn_mma.cuh: page splits on the tensor cores for GQA groups <= 8),
-// k_kv_attn (CTA per (row, head, split); fp32 CUDA cores, three value classes accumulated separately and
-// inverse-transformed once: the BF16 sink / window split, larger GQA groups, FLAGROT_KIVI_ATTN=cuda), k_kv_merge.  Head dim 128; the FP8-metadata pages (f8) and head dim 256
-// answer code 2 with a message, as the reference does for unsupported shapes.
+// defined by fp32 sums), kvm::k_kv_attn_mma2 (kv_attn_mma2.cuh: page splits and the BF16 sink / window split on the tensor
+// cores, GQA groups <= 8, one launch), k_kv_merge, k_kv_dequant, k_kv_lse_merge.  Head dim 128; the FP8-metadata pages
+// (f8) and head dim 256 answer code 2 with a message, as the reference does for unsupported shapes.
 #include <cmath>
 #include <cstdint>
 #include <cstdio>
-#include <cstdlib>
-#include <cstring>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
@@ -359,24 +356,7 @@ __global__ void __launch_bounds__(256) k_k_encode(const __nv_bfloat16* __restric
 }
 
 // ------------------------------------------------------------------------------------------------ decode attention
-// CTA (kv head h, split sp, row b), 128 threads, G <= 8 q heads.  Per 32-token group: stage the two pages' slices,
-// q' * scale and q' . min per head (thread = channel), scores (warp = channel quarter, lane = token), softmax (warp =
-// heads w, w + 4), PV (thread = channel, three classes).  Split sp == NS is the BF16 sink / window rows.
-template <int G>
-struct AttnSmem {
-  float q[3][G][D];
-  float qs[G][D];
-  float part[4][G][33];
-  float bias[4][G];
-  float p[G][32];
-  float alpha[G];
-  uint32_t kc[32][D / 16];        // key code words [token][word]
-  uint32_t km[32][NV];            // group meta [cell][k]
-  uint8_t vc[32][D / 4];
-  uint32_t vm[32][NV];
-  uint8_t vf[32];
-};
-
+// (the page-split kernel and the BF16 sink / window split live in kv_attn_mma2.cuh / kv_attn_mma.cuh)
 template <int G>
 __device__ void smem_hada(float (*x)[D], int n) {   // orthonormal H_n of G rows in shared memory (all 128 threads)
   const int tid = threadIdx.x;
@@ -393,200 +373,6 @@ __device__ void smem_hada(float (*x)[D], int n) {   // orthonormal H_n of G rows
   const float c = n == 32 ? fr::C32 : fr::C128;
   for (int e = tid; e < G * D; e += 128) x[e / D][e % D] = __fmul_rn(x[e / D][e % D], c);
   __syncthreads();
-}
-
-template <int G>
-__global__ void __launch_bounds__(128) k_kv_attn(const __nv_bfloat16* __restrict__ q, long long q_rs,
-                                                 const uint8_t* __restrict__ pool, const int* __restrict__ bt, long long bt_rs,
-                                                 const int* __restrict__ cached, int kv_start, int Hkv, int NS, int chunk,
-                                                 float qscale, const __nv_bfloat16* __restrict__ ring,
-                                                 const int* __restrict__ tail_len, const int* __restrict__ tail_idx, int T,
-                                                 float* __restrict__ opart, float* __restrict__ ml, int sp0) {
-  extern __shared__ __align__(16) uint8_t smraw[];
-  AttnSmem<G>& S = *reinterpret_cast<AttnSmem<G>*>(smraw);
-  const int h = blockIdx.x, sp = blockIdx.y + sp0, b = blockIdx.z;
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const long long pidx = static_cast<long long>(b * Hkv + h) * (NS + 1) + sp;
-  float* op = opart + pidx * G * D;
-  float* mlp = ml + pidx * G * 2;
-  const bool tail = sp == NS;
-  int t0, t1;
-  if (tail) { t0 = 0; t1 = tail_len ? tail_len[b] : 0; }
-  else { t0 = max(sp * chunk, kv_start); t1 = min((sp + 1) * chunk, cached[b]); }
-  if (t1 <= t0) {
-    for (int e = tid; e < G; e += 128) { mlp[2 * e] = KV_NEG_INF; mlp[2 * e + 1] = 0.f; }
-    return;
-  }
-  const __nv_bfloat16* qb = q + static_cast<long long>(b) * q_rs + static_cast<long long>(h) * G * D;
-  for (int e = tid; e < G * D; e += 128) {
-    const float v = __bfloat162float(qb[e]);
-    S.q[0][e / D][e % D] = v; S.q[1][e / D][e % D] = v; S.q[2][e / D][e % D] = v;
-  }
-  __syncthreads();
-  if (!tail) { smem_hada<G>(S.q[1], 32); smem_hada<G>(S.q[2], 128); }
-  float accI[G], accH[G], accF[G];
-#pragma unroll
-  for (int g = 0; g < G; ++g) { accI[g] = 0.f; accH[g] = 0.f; accF[g] = 0.f; }
-  float m_run[2] = {KV_NEG_INF, KV_NEG_INF}, l_run[2] = {0.f, 0.f};
-  const int* btb = bt + static_cast<long long>(b) * bt_rs;
-  const __nv_bfloat16* rbase = ring + static_cast<long long>(tail ? (tail_idx ? tail_idx[b] : 0) : 0) * T * 2 * Hkv * D;
-  for (int base = tail ? 0 : (t0 / GRP) * GRP; base < t1; base += GRP) {
-    if (!tail) {
-      const int g32 = base / GRP;
-      const uint8_t* chA = pool + (static_cast<long long>(btb[2 * g32]) * Hkv + h) * CB;
-      const uint8_t* chB = pool + (static_cast<long long>(btb[2 * g32 + 1]) * Hkv + h) * CB;
-      // stage: key codes (2 x 512 B), key meta (2 x 256 B), value codes (2 x 512 B), value meta (2 x 256 B), value flags
-      {
-        const int pg = tid >> 6, i = tid & 63;               // 64 threads per page
-        const uint8_t* ch = pg ? chB : chA;
-        reinterpret_cast<uint2*>(&S.kc[16 * pg][0])[i] = reinterpret_cast<const uint2*>(ch)[i];
-        reinterpret_cast<uint32_t*>(&S.km[16 * pg][0])[i] = reinterpret_cast<const uint32_t*>(ch + OFF_KM)[i];
-        reinterpret_cast<uint2*>(&S.vc[16 * pg][0])[i] = reinterpret_cast<const uint2*>(ch + OFF_VC)[i];
-        reinterpret_cast<uint32_t*>(&S.vm[16 * pg][0])[i] = reinterpret_cast<const uint32_t*>(ch + OFF_VM)[i];
-        if (i < 4) reinterpret_cast<uint32_t*>(&S.vf[16 * pg])[i] = reinterpret_cast<const uint32_t*>(ch + OFF_VF)[i];
-      }
-      __syncthreads();
-      int lmask = 0;
-#pragma unroll
-      for (int j = 0; j < NV; ++j) lmask |= ((S.km[0][j] >> 15) & 1) << j;
-      const int useF = (S.km[1][0] >> 15) & 1;
-      {  // thread = channel c: q' * scale, partial q' . min
-        const int c = tid;
-        const uint32_t wv = S.km[c / NV][c % NV];
-        const __half2 hv = *reinterpret_cast<const __half2*>(&wv);
-        const float s = fabsf(__low2float(hv)), mn = __high2float(hv);
-        const int which = useF ? 2 : ((lmask >> (c / 32)) & 1);
-#pragma unroll
-        for (int g = 0; g < G; ++g) {
-          const float qp = S.q[which][g][c];
-          S.qs[g][c] = qp * s;
-          float v = qp * mn;
-#pragma unroll
-          for (int m = 16; m >= 1; m >>= 1) v += __shfl_xor_sync(FULLMASK, v, m);
-          if (lane == 0) S.bias[warp][g] = v;
-        }
-      }
-      __syncthreads();
-      {  // partial scores: warp = channel quarter, lane = token
-        float acc[G];
-#pragma unroll
-        for (int g = 0; g < G; ++g) acc[g] = 0.f;
-#pragma unroll
-        for (int wd = 0; wd < 2; ++wd) {
-          const uint32_t word = S.kc[lane][2 * warp + wd];
-#pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const int c = 32 * warp + 16 * wd + i;
-            const float cv = static_cast<float>((word >> kbit(i)) & 3);
-#pragma unroll
-            for (int g = 0; g < G; ++g) acc[g] = fmaf(S.qs[g][c], cv, acc[g]);
-          }
-        }
-#pragma unroll
-        for (int g = 0; g < G; ++g) S.part[warp][g][lane] = acc[g];
-      }
-      __syncthreads();
-    } else {
-      const int j = base + lane;
-      float acc[G];
-#pragma unroll
-      for (int g = 0; g < G; ++g) acc[g] = 0.f;
-      if (j < t1) {
-        const __nv_bfloat16* kr = rbase + static_cast<long long>(j) * 2 * Hkv * D + static_cast<long long>(h) * D + 32 * warp;
-        for (int i = 0; i < 32; i += 8) {
-          const uint4 u = *reinterpret_cast<const uint4*>(kr + i);
-          const float kf[8] = {fr::bf16_lo(u.x), fr::bf16_hi(u.x), fr::bf16_lo(u.y), fr::bf16_hi(u.y),
-                               fr::bf16_lo(u.z), fr::bf16_hi(u.z), fr::bf16_lo(u.w), fr::bf16_hi(u.w)};
-#pragma unroll
-          for (int k = 0; k < 8; ++k)
-#pragma unroll
-            for (int g = 0; g < G; ++g) acc[g] = fmaf(S.q[0][g][32 * warp + i + k], kf[k], acc[g]);
-        }
-      }
-#pragma unroll
-      for (int g = 0; g < G; ++g) S.part[warp][g][lane] = acc[g];
-      if (lane < G) S.bias[warp][lane] = 0.f;
-      __syncthreads();
-    }
-#pragma unroll
-    for (int r = 0; r < 2; ++r) {   // online softmax: warp w owns heads w and w + 4
-      const int g = warp + 4 * r;
-      if (g >= G) continue;
-      const int pos = base + lane;
-      const bool valid = tail ? pos < t1 : (pos >= t0 && pos < t1);
-      float sc = S.part[0][g][lane] + S.part[1][g][lane] + S.part[2][g][lane] + S.part[3][g][lane] + S.bias[0][g] +
-                 S.bias[1][g] + S.bias[2][g] + S.bias[3][g];
-      sc = valid ? sc * qscale : KV_NEG_INF;
-      float mx = sc;
-      for (int m = 16; m >= 1; m >>= 1) mx = fmaxf(mx, __shfl_xor_sync(FULLMASK, mx, m));
-      const float mnew = fmaxf(m_run[r], mx);
-      const float p = (mnew == KV_NEG_INF || !valid) ? 0.f : exp2f(sc - mnew);
-      const float al = m_run[r] == KV_NEG_INF ? 0.f : exp2f(m_run[r] - mnew);
-      float ps = p;
-      for (int m = 16; m >= 1; m >>= 1) ps += __shfl_xor_sync(FULLMASK, ps, m);
-      l_run[r] = l_run[r] * al + ps;
-      m_run[r] = mnew;
-      S.p[g][lane] = p;
-      if (lane == 0) S.alpha[g] = al;
-    }
-    __syncthreads();
-#pragma unroll
-    for (int g = 0; g < G; ++g) { const float al = S.alpha[g]; accI[g] *= al; accH[g] *= al; accF[g] *= al; }
-    const int nt = min(GRP, t1 - base);
-    const int c = tid;
-    if (!tail) {
-      for (int i = max(0, t0 - base); i < nt; ++i) {
-        const float cv = static_cast<float>((S.vc[i][c >> 2] >> (2 * (c & 3))) & 3);
-        const uint32_t wv = S.vm[i][c >> 5];
-        const __half2 hv = *reinterpret_cast<const __half2*>(&wv);
-        const float s = __low2float(hv);
-        const float d = __fadd_rn(__fmul_rn(cv, fabsf(s)), __high2float(hv));
-        if (S.vf[i]) {
-#pragma unroll
-          for (int g = 0; g < G; ++g) accF[g] = fmaf(S.p[g][i], d, accF[g]);
-        } else if (signbit(s)) {
-#pragma unroll
-          for (int g = 0; g < G; ++g) accH[g] = fmaf(S.p[g][i], d, accH[g]);
-        } else {
-#pragma unroll
-          for (int g = 0; g < G; ++g) accI[g] = fmaf(S.p[g][i], d, accI[g]);
-        }
-      }
-    } else {
-      for (int i = 0; i < nt; ++i) {
-        const float d = __bfloat162float(rbase[static_cast<long long>(base + i) * 2 * Hkv * D + static_cast<long long>(Hkv + h) * D + c]);
-#pragma unroll
-        for (int g = 0; g < G; ++g) accI[g] = fmaf(S.p[g][i], d, accI[g]);
-      }
-    }
-    __syncthreads();
-  }
-  if (!tail) {   // inverse transforms of the two rotated classes, once per CTA
-#pragma unroll
-    for (int g = 0; g < G; ++g) {
-      float v = accH[g];                                    // channel c = tid: lane = c % 32
-#pragma unroll
-      for (int hh = 1; hh < 32; hh <<= 1) {
-        const float o = __shfl_xor_sync(FULLMASK, v, hh);
-        v = (lane & hh) ? __fsub_rn(o, v) : __fadd_rn(v, o);
-      }
-      accI[g] = __fadd_rn(accI[g], __fmul_rn(v, fr::C32));
-    }
-    __syncthreads();
-#pragma unroll
-    for (int g = 0; g < G; ++g) S.q[2][g][tid] = accF[g];
-    __syncthreads();
-    smem_hada<G>(S.q[2], 128);
-#pragma unroll
-    for (int g = 0; g < G; ++g) accI[g] = __fadd_rn(accI[g], S.q[2][g][tid]);
-  }
-#pragma unroll
-  for (int g = 0; g < G; ++g) op[g * D + tid] = accI[g];
-#pragma unroll
-  for (int r = 0; r < 2; ++r) {
-    const int g = warp + 4 * r;
-    if (g < G && lane == 0) { mlp[2 * g] = m_run[r]; mlp[2 * g + 1] = l_run[r]; }
-  }
 }
 
 __global__ void __launch_bounds__(128) k_kv_merge(const float* __restrict__ opart, const float* __restrict__ ml, int Hkv, int G,
@@ -696,61 +482,19 @@ __global__ void k_kv_lse_merge(const __nv_bfloat16* __restrict__ oa, const float
 #include "kv_attn_mma.cuh"
 #include "kv_attn_mma2.cuh"
 
-// FLAGROT_KIVI_ATTN (read at every launch): "cuda" keeps the page splits on the fp32 CUDA-core kernel, "warp" uses the
-// tensor-core kernel with per-warp accumulators (k_kv_attn_mma); default: the CTA-synchronous one (k_kv_attn_mma2)
-int kivi_path() {
-  const char* e = std::getenv("FLAGROT_KIVI_ATTN");
-  if (e != nullptr && std::strcmp(e, "cuda") == 0) return 0;
-  if (e != nullptr && std::strcmp(e, "warp") == 0) return 1;
-  return 2;
-}
-
+// one launch: grid (Hkv, max(NS, 1), 2 B); z < B are the page splits (y >= NS exits: a call with NS == 0 has only BF16
+// rows), z >= B (y == 0) the BF16 sink / window splits.
 template <int G>
 int launch_attn(const void* q, long long q_rs, const void* pool, const void* bt, long long bt_rs, const void* cached,
                 int kv_start, int B, int Hkv, int NS, int chunk, float qscale, const void* ring, const void* tail_len,
                 const void* tail_idx, int T, void* opart, void* ml, cudaStream_t st) {
-  static bool set = false;
-  const int smem = static_cast<int>(sizeof(AttnSmem<G>));
-  if (!set) {
-    if (cudaFuncSetAttribute(k_kv_attn<G>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return 1;
-    set = true;
-  }
-  const auto* qp = static_cast<const __nv_bfloat16*>(q);
-  const auto* pp = static_cast<const uint8_t*>(pool);
-  const auto* btp = static_cast<const int*>(bt);
-  const auto* cp = static_cast<const int*>(cached);
-  const auto* rp = static_cast<const __nv_bfloat16*>(ring);
-  const auto* tlp = static_cast<const int*>(tail_len);
-  const auto* tip = static_cast<const int*>(tail_idx);
-  auto* opp = static_cast<float*>(opart);
-  auto* mlp = static_cast<float*>(ml);
-  if constexpr (G <= 8) {
-    const int path = kivi_path();
-    if (path == 2) {
-      static bool set3 = false;
-      if (!set3) {
-        if (cudaFuncSetAttribute(kvm::k_kv_attn_mma2<G>, cudaFuncAttributeMaxDynamicSharedMemorySize, kvm::SMEM2) != cudaSuccess) return 1;
-        set3 = true;
-      }
-      static_assert(kvm::TAIL_SMEM <= kvm::SMEM2, "the window split runs in the page-split kernel's shared memory");
-      kvm::k_kv_attn_mma2<G><<<dim3(Hkv, NS, 2 * B), 128, kvm::SMEM2, st>>>(qp, q_rs, pp, btp, bt_rs, cp, kv_start, Hkv, NS, chunk, qscale,
-                                                                            rp, tlp, tip, T, B, opp, mlp);
-      return 0;
-    }
-    if (path == 1) {          // page splits and the BF16 sink / window split in one launch
-      static bool set2 = false;
-      if (!set2) {
-        if (cudaFuncSetAttribute(kvm::k_kv_attn_mma<G>, cudaFuncAttributeMaxDynamicSharedMemorySize, kvm::SMEM) != cudaSuccess) return 1;
-        set2 = true;
-      }
-      static_assert(kvm::TAIL_SMEM <= kvm::SMEM, "the window split runs in the page-split kernel's shared memory");
-      kvm::k_kv_attn_mma<G><<<dim3(Hkv, NS, 2 * B), 128, kvm::SMEM, st>>>(qp, q_rs, pp, btp, bt_rs, cp, kv_start, Hkv, NS, chunk, qscale,
-                                                                          rp, tlp, tip, T, B, opp, mlp);
-      return 0;
-    }
-  }
-  k_kv_attn<G><<<dim3(Hkv, NS + 1, B), 128, smem, st>>>(qp, q_rs, pp, btp, bt_rs, cp, kv_start, Hkv, NS, chunk, qscale, rp, tlp, tip, T,
-                                                        opp, mlp, 0);
+  static_assert(kvm::TAIL_SMEM <= kvm::SMEM2, "the window split runs in the page-split kernel's shared memory");
+  static unsigned long long ready = 0;
+  if (!fr::smem_limit_ready(kvm::k_kv_attn_mma2<G>, kvm::SMEM2, ready)) return 1;
+  kvm::k_kv_attn_mma2<G><<<dim3(Hkv, NS > 0 ? NS : 1, 2 * B), 128, kvm::SMEM2, st>>>(
+      static_cast<const __nv_bfloat16*>(q), q_rs, static_cast<const uint8_t*>(pool), static_cast<const int*>(bt), bt_rs,
+      static_cast<const int*>(cached), kv_start, Hkv, NS, chunk, qscale, static_cast<const __nv_bfloat16*>(ring),
+      static_cast<const int*>(tail_len), static_cast<const int*>(tail_idx), T, B, static_cast<float*>(opart), static_cast<float*>(ml));
   return 0;
 }
 
@@ -781,12 +525,8 @@ int kv_k_encode(const void* src, long long src_rs, const void* src2, long long s
   if (N <= 0) return 0;
   if (Dd != D) return fail("kv_k_encode: D %d (head dim 128 only)", Dd);
   if (f8) return fail("kv_k_encode: FP8-metadata pages are not built");
-  static bool set = false;
-  if (!set) {
-    if (cudaFuncSetAttribute(k_k_encode, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(KENC_SMEM)) != cudaSuccess)
-      return check_launch("kv_k_encode (shared memory)") ? 1 : 1;
-    set = true;
-  }
+  static unsigned long long ready = 0;
+  if (!fr::smem_limit_ready(k_k_encode, static_cast<int>(KENC_SMEM), ready)) return check_launch("kv_k_encode (shared memory)") ? 1 : 1;
   k_k_encode<<<dim3(N, Hkv), 256, KENC_SMEM, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(src), src_rs, static_cast<const __nv_bfloat16*>(src2), src2_rs,
       static_cast<const long long*>(sidx), static_cast<const long long*>(dslot), Hkv, static_cast<const float*>(qs),

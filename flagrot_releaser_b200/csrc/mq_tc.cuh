@@ -2,7 +2,8 @@
 // with the accumulators, the Q operand and the P operand in tensor memory.  Included by mq_capi.cu inside its anonymous
 // namespace (kernel 3 of frmq_attn); same work list, partial layout and numerics contract as the mma.sync kernel above.
 //
-// CTA = (item, kv head): 128 query rows x the item's 64-key blocks; 24 warps (80 registers each) with fixed roles:
+// CTA = (item, kv head): up to 128 query rows (the M tile; plans with 64-row tiles leave the upper half empty) x the item's
+// 64-key blocks; 24 warps (80 registers each) with fixed roles:
 //   warps 0-3   softmax: thread r owns query row r = tensor-memory lane r.  Per block two passes over the 64 scores (they
 //               are read from tensor memory twice rather than kept in registers): row maximum, then p = 2^(s - ref) into
 //               the P operand columns and the row sum.  The reference is lazy: it only moves when the maximum grew by
@@ -207,11 +208,11 @@ __global__ void __launch_bounds__(TQ_THREADS, 1) k_mq_tc(const MqParams p) {
   const int* itp = p.items + ITEM_INTS * item;
   const int* tl = p.tiles + TILE_INTS * itp[0];
   const int req = tl[0], crow0 = tl[1], ntok = tl[3], pos0 = tl[4], nk = tl[5], ext = tl[8];
-  const int G = p.G, Hq = p.Hkv * G, TQr = 128 / G;
+  const int G = p.G, Hq = p.Hkv * G, TQr = p.rows / G;     // rows = 128 or 64 query rows per tile (the plan's choice)
   const int kend = min(min(nk, itp[2] * BN), max(pos0 + ntok - p.shift, ext + 1));
   const int kb0 = itp[1];
   const int nblk = kend > kb0 * BN ? (kend + BN - 1) / BN - kb0 : 0;
-  const long long pbase = (static_cast<long long>(item) * p.Hkv + h) * 128;
+  const long long pbase = (static_cast<long long>(item) * p.Hkv + h) * p.rows;
 
   if (nblk == 0) {          // nothing visible: empty partials
     if (tid < 128) {
@@ -491,11 +492,8 @@ __global__ void __launch_bounds__(TQ_THREADS, 1) k_mq_tc(const MqParams p) {
 template <int NB, bool KO>
 int launch_mq_tc(const MqParams& p, int nitems, cudaStream_t st) {
   constexpr int smem = TQMap<NB, KO ? 3 : 1>::TOTAL;
-  static bool set = false;
-  if (!set) {
-    if (cudaFuncSetAttribute(k_mq_tc<NB, KO>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -2;
-    set = true;
-  }
+  static unsigned long long ready = 0;
+  if (!fr::smem_limit_ready(k_mq_tc<NB, KO>, smem, ready)) return -2;
   k_mq_tc<NB, KO><<<dim3(nitems, p.Hkv), TQ_THREADS, smem, st>>>(p);
   return cudaPeekAtLastError() == cudaSuccess ? 0 : -1;
 }

@@ -126,13 +126,6 @@ int fr_cb_attn_noalloc(const void* q, long long q_bs, const uint8_t* pool, const
                        void* out, long long o_bs, const void* tail, const int* tail_len, const int* tail_idx,
                        long long tail_bs, long long tail_ts, void* stream, int kv_start);
 
-/* No counterpart in the reference.  Known-answer run of the tcgen05 operand paths the library's kernels use: one CTA computes
- * D[128][N] = A[128][K] * B[N][K]^T through tensor memory.  mode 0: FP16 operands in shared memory (128-byte swizzle), fp32 D;
- * mode 1: FP16 A operand in tensor memory; mode 2: u8 x s8 operands without swizzle, s32 D.  N a multiple of 16 <= 128; K a
- * multiple of 64 <= 256 (modes 0 / 1) or of 32 <= 512 (mode 2).  Synchronises the stream.  Returns 0, -1 launch error,
- * -3 bad shape, or the source line of a bounded wait that gave up. */
-int fr_tc5_selftest(int mode, const void* A, const void* B, void* D, int N, int K, void* stream);
-
 #ifdef __cplusplus
 }
 #endif

@@ -173,29 +173,6 @@ def test_decode_forced_splits(K, fmt, nsplit):
     check(run_case(K, fmt, [300, 4101, 17], win=(32, 9), nsplit=nsplit, seed=40), (fmt, nsplit))
 
 
-@pytest.fixture
-def tc_path(monkeypatch):
-    """routes INT4 pages to the tcgen05 kernel (the library reads the variable at every launch)"""
-    monkeypatch.setenv("FLAGROT_DECODE_PATH", "tc")
-
-
-@pytest.mark.parametrize("fmt", ["int4a", "konlya"])
-def test_decode_tcgen05_kernel(K, tc_path, fmt):
-    """the tensor-memory kernel on the same cases: lengths across step (128) and split boundaries, windows, kv_start,
-    GQA tiles, forced splits, a long sequence"""
-    for i, lens in enumerate(LENS):
-        for win in (None, (32, 9), (256, 7)):
-            check(run_case(K, fmt, lens, win=win, seed=10 * i + (0 if win is None else win[0])), (fmt, lens, win, "tc"))
-    for ks in (4, 37):
-        check(run_case(K, fmt, [300, 4101, 17 + ks], win=(132, 9), kv_start=ks, seed=22), (fmt, ks, "tc kv_start"))
-    for G, Hkv in ((5, 8), (12, 4)):
-        check(run_case(K, fmt, [300, 4101, 17], win=(64, 9), G=G, Hkv=Hkv, seed=31), (fmt, G, Hkv, "tc gqa"))
-    for nsplit in (1, 3):
-        check(run_case(K, fmt, [300, 4101, 17], win=(32, 9), nsplit=nsplit, seed=40), (fmt, nsplit, "tc splits"))
-    check(run_case(K, fmt, [33000], win=(256, 7), seed=3, Hkv=2), (fmt, 33000, "tc"))
-    check(run_case(K, fmt, [127, 128, 129, 255, 257], seed=8, Hkv=2), (fmt, "tc step edges"))
-
-
 def test_decode_partial_rows_merge(K):
     """the extension entry: rows of two KV-sequence shards merged on the host equal attention over the whole sequence."""
     check(run_case(K, "konlya", [300, 1000, 17], win=(32, 9), seed=50, partial=True), "partial")

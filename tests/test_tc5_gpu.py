@@ -1,5 +1,5 @@
 """Known-answer tests of the tcgen05 building blocks (tensor-memory allocation, shared-memory / instruction descriptors,
-MMA issue + commit, tensor-memory loads and stores) through fr_tc5_selftest: D[128][N] = A[128][K] B[N][K]^T against
+MMA issue + commit, tensor-memory loads and stores) through fr_tc5_selftest of the test-only library libflagrot_tc5test.so: D[128][N] = A[128][K] B[N][K]^T against
 torch on the same operands.  FP16 products with fp32 accumulation are compared with a float64 product (tolerance 1e-3 of
 the result scale); the u8 x s8 product must be exact."""
 import ctypes
@@ -12,8 +12,10 @@ pytestmark = pytest.mark.gpu
 
 @pytest.fixture(scope="module")
 def L():
-    from flagrot_releaser_b200 import kernels
-    lib = kernels.lib()
+    from pathlib import Path
+    path = Path(__file__).resolve().parents[1] / "flagrot_releaser_b200" / "lib" / "libflagrot_tc5test.so"
+    assert path.exists(), f"{path} missing: run python -m flagrot_releaser_b200._build"
+    lib = ctypes.CDLL(str(path))
     lib.fr_tc5_selftest.argtypes = [ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int,
                                     ctypes.c_void_p]
     lib.fr_tc5_selftest.restype = ctypes.c_int
