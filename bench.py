@@ -1,23 +1,36 @@
-"""Headline benchmark: FlagRot paged decode over INT4 (konlya) pages on the Llama-3.1-8B-shaped batch-64 x 4K workload.
+"""Benchmarks of the FlagRot KV-cache hot path on B200.  Headline (default): paged decode over INT4 (konlya) pages on the
+Llama-3.1-8B-shaped batch-64 x 4K workload.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload cfg2|cfg3]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload cfg2|cfg3|cfg4|cfg5a|cfg5b|writers]
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
 
-A step = one pass of the hot path over one batch: the dynamic writer appends one token per sequence (fr_cb_write, T = B)
-and the paged decode attention reads every sequence's cache (fr_cb_attn), with the 4 sink + 128 window tokens in BF16.
-The resident step is captured once per pool copy and replayed as a CUDA graph (--no-step-graph: two launches from Python).
-metric: decode-attention KV GB/s = algorithmic bytes of the decode read (pages [S, L - W) * 144 B per (token, kv head) +
-BF16 window rows + q / out) divided by the step time.  `value` has every input resident in HBM; `e2e` measures the same
-step through the C-ABI front end with this step's q / new kv / slots copied from pinned host memory and the output
-copied back, inside the timed region (the KV cache itself is the path's state and lives in HBM, as in the plugin).
-Multi-GPU: the batch shards across ranks with no data-path collective (weak scaling: every rank runs the same per-GPU
-batch on its own pool); time = max over ranks.
-The reference arm (--impl reference) times the reference's CPU path for this workload (fp32 dequantise + attention over
-the same pages, oracle/cpu_decode.py, numpy with all host threads) on a bounded sample of the batch.
+Workloads (the configurations of the baseline; all inputs seeded synthetic, caches written by the library's own writers):
+  cfg2   INT4 konlya decode, 32 q / 8 kv heads, batch 64 x ctx 4096, s4w128.  N GPUs: every rank runs the full batch on its
+         own pool (weak scaling, no data-path collective).
+  cfg3   INT2 konlya2 decode with centred keys, batch 256 x ctx 8192.  N GPUs: rows [r B / N, (r + 1) B / N) per rank (strong).
+  cfg4   KIVI-style INT2 decode, 64 q / 8 kv heads, batch 32 x ctx 16384.  N GPUs: kv heads [r Hkv / N, ...) and their q heads
+         per rank (tensor parallel by kv head, strong); calibration rows sliced the same way.
+  cfg5a  prefix-cached prefill, 4 requests x 512 new tokens over 32768 cached, INT4 konlya pages (tensor-bound; requests
+         are dealt over the ranks).
+  cfg5b  one sequence of 131072 tokens, INT4 konlya: the KV sequence is split over the ranks, every rank emits (o, m, l)
+         rows (fr_attn_partial), an NCCL all-gather of 130 floats per (row, head) and fr_merge_partials finish the step.
+  writers  the cache writers against the reference's own sm_100a-capable kernels (oracle/_ref), T = 64 and T = 65536.
+
+A step = one pass of the hot path over one batch: the writer appends one token per sequence and the decode attention reads
+every sequence's cache (prefill: q staging + attention + item merge).  `value` has every input resident in HBM (the
+resident step is replayed as one CUDA graph per pool copy); `e2e` measures the same step through the C-ABI front end with
+this step's inputs copied from pinned host memory and the output copied back inside the timed region (the KV cache is the
+path's state and lives in HBM, as in the plugin).  Pools larger than L2 are cycled.  Before the K timed steps the same step
+runs untimed for --sustain-s seconds, so that clocks and power are those of a loaded GPU; the roofline figure comes from a
+kernel-only loop of at least --sustain-s seconds with the SM clock sampled over that loop.
+The reference arm (--impl reference) times the reference's own CPU implementation of the path on the host cores: its
+PyTorch page parser (kernels.py dequant_cb_pages / kivi.py dequant_groups, byte code under oracle/_ref/pyref) + fp32
+attention with all host threads; when that byte code is absent, the numpy restatement under oracle/.
 """
 from __future__ import annotations
 
 import argparse
+import ctypes
 import json
 import math
 import os
@@ -34,39 +47,34 @@ ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 LOG2E = 1.4426950408889634
 P = 16
+SCALE = 1 / math.sqrt(128)
 
 WORKLOADS = {
-    # Llama-3.1-8B-shaped INT4 FlagRot decode: 32 q / 8 kv heads, d 128, batch 64, context 4096, 4 sinks + 128 window BF16
-    "cfg2": dict(kind="konlya", nb=4, B=64, L=4096, Hq=32, Hkv=8, S=4, W=128, center=False,
+    "cfg2": dict(path="decode", kind="konlya", nb=4, B=64, L=4096, Hq=32, Hkv=8, S=4, W=128, center=False, shard="replica",
                  name="llama-3.1-8b-shaped int4 konlya decode, batch 64 x ctx 4096, page 16, s4w128"),
-    # Qwen3-8B-shaped INT2 FlagRot decode, batch 256 x 8192 (per-GPU batch = 256 / n when sharded)
-    "cfg3": dict(kind="konlya2", nb=2, B=256, L=8192, Hq=32, Hkv=8, S=4, W=128, center=True,
+    "cfg3": dict(path="decode", kind="konlya2", nb=2, B=256, L=8192, Hq=32, Hkv=8, S=4, W=128, center=True, shard="batch",
                  name="qwen3-8b-shaped int2 konlya2 decode, batch 256 x ctx 8192, page 16, s4w128, centred keys"),
-    # one very long sequence, INT4 konlya, context 131072: the KV sequence is sharded over the ranks, every rank emits
-    # (o, m, l) rows (fr_attn_partial), an NCCL all-gather of 130 floats per (row, head) and the LSE merge finish the step
-    "cfg5b": dict(kind="konlya", nb=4, B=1, L=131072, Hq=32, Hkv=8, S=4, W=128, center=False, shard="kvseq",
+    "cfg4": dict(path="kivi", B=32, L=16384, Hq=64, Hkv=8, S=4, W=128, shard="kvhead",
+                 name="qwen-32b-shaped kivi2:32 decode, batch 32 x ctx 16384, 64 q / 8 kv heads, page 16, s4w128"),
+    "cfg5a": dict(path="prefill", kind="konlya", nb=4, B=4, new=512, L=32768, Hq=32, Hkv=8, shard="request",
+                  name="prefix-cached prefill, 4 requests x 512 new tokens over 32768 cached, 32 q / 8 kv heads, int4 konlya pages"),
+    "cfg5b": dict(path="decode", kind="konlya", nb=4, B=1, L=131072, Hq=32, Hkv=8, S=4, W=128, center=False, shard="kvseq",
                   name="int4 konlya decode, batch 1 x ctx 131072, page 16, s4w128, KV-sequence sharded"),
+    "writers": dict(path="writers", name="cache writers against the reference's own kernels, T = 64 and T = 65536, 8 kv heads"),
 }
 
 
-def algorithmic_bytes(w, B=None):
-    B = w["B"] if B is None else B
-    cell = 144 if w["nb"] == 4 else 80
-    pages = B * w["Hkv"] * cell * (w["L"] - w["W"] - w["S"])
-    tail = B * (w["S"] + w["W"]) * 2 * w["Hkv"] * 128 * 2
-    qo = B * w["Hq"] * 128 * 2 * 2
-    return pages + tail + qo
-
-
 def peaks():
+    """(hbm GB/s, dense bf16 TFLOP/s burst, sustained, source)"""
     f = ROOT / "MEASURED_PEAKS.json"
     if f.exists():
-        return float(json.loads(f.read_text())["hbm_gbs"]), "measured"
-    return 6650.0, "fallback"
+        d = json.loads(f.read_text())
+        return float(d["hbm_gbs"]), float(d["bf16_tflops"]), float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "measured"
+    return 6650.0, 1590.0, 1400.0, "fallback"
 
 
 class ClockSampler:
-    """samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+    """samples SM clock and throttle reasons with nvidia-smi while a timed region runs (query only)."""
 
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
@@ -76,22 +84,23 @@ class ClockSampler:
 
     def start(self):
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "50",
                                           "-i", str(self.idx)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=lambda: self.lines.extend(self.proc.stdout), daemon=True).start()
         except OSError:
             self.proc = None
+        return self
 
     def stop(self):
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.15)
+        time.sleep(0.1)
         self.proc.terminate()
         try:
             self.proc.wait(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
-        sm, mx, reasons = [], [], set()
+        sm, mx, pw, reasons = [], [], [], set()
         for ln in self.lines:
             f = [x.strip() for x in ln.split(",")]
             if len(f) < 9:
@@ -99,161 +108,18 @@ class ClockSampler:
             try:
                 sm.append(float(f[1]))
                 mx.append(float(f[2]))
+                pw.append(float(f[3]))
             except ValueError:
                 continue
             for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
                 if v.lower().startswith("active"):
                     reasons.add(name)
         return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+                "power_w_max": max(pw) if pw else None, "reasons": sorted(reasons), "samples": len(sm)}
 
 
-# ---------------------------------------------------------------------------------------------- workload state
-def make_state(w, B, dev, seed, ncopy, rank=0, world=1):
-    """synthetic inputs of the named shape and the quantised caches (written by the library's own dynamic writer, which
-    the parity tests hold bit-exact).  ncopy distinct pools (distinct random page tables over distinct memory) are cycled
-    so that no page is L2-resident between steps."""
-    from flagrot_releaser_b200 import kernels as K
-    g = torch.Generator().manual_seed(seed)
-    Hkv, Hq, L = w["Hkv"], w["Hq"], w["L"]
-    kvseq = w.get("shard") == "kvseq"
-    if kvseq:                                   # this rank's slice of the page tokens [0, L - W); window rows stay BF16
-        L = kvseq_local_len(w["L"], w["W"], world)
-    npages_seq = L // P
-    npool = B * npages_seq + 7
-    qs = torch.randn(Hkv, 512, 128, generator=g) * (torch.rand(Hkv, 1, 128, generator=g) + 0.5).sqrt()
-    Cq = (torch.einsum("hnd,hne->hde", qs, qs) / 512).contiguous()
-    co = torch.rand(Hkv, 128, generator=g) + 0.5
-    CT = Cq.transpose(1, 2).contiguous().to(dev)
-    cod = co.to(dev)
-    out_ch = torch.stack([torch.randperm(128, generator=g)[:6] for _ in range(Hkv)])          # 5 % of channels x10
-    kmu = None
-    offs = None
-    if w["center"]:
-        offs = torch.randn(Hkv, 128, generator=g) * math.sqrt(2.0)
-        kmu = offs.float().contiguous().to(dev)
-    chunk_b = K.cb_chunk_bytes(w["kind"], P)
-    pools, bts = [], []
-    rows_per = 64 * 1024
-    for c in range(ncopy):
-        pool = torch.randint(0, 256, (npool, Hkv, chunk_b), dtype=torch.uint8, generator=g).to(dev)
-        bt = torch.randperm(npool, generator=g)[:B * npages_seq].reshape(B, npages_seq).int()
-        pos = torch.arange(L)
-        slots = (bt.long()[:, pos // P] * P + pos % P).reshape(-1)
-        for r0 in range(0, B * L, rows_per):
-            n = min(rows_per, B * L - r0)
-            kv = torch.randn(n, 2 * Hkv, 128, generator=g)
-            for h in range(Hkv):
-                kv[:, h, out_ch[h]] *= 10
-            if offs is not None:
-                kv[:, :Hkv] += offs
-            K.cb_write(kv.bfloat16().to(dev), slots[r0:r0 + n].to(dev), CT, cod, w["kind"], pool, P, kmu=kmu)
-        torch.cuda.synchronize()
-        pools.append(pool)
-        bts.append(bt.to(dev))
-    T = w["S"] + w["W"]
-    ring = torch.randn(B, T, 2 * Hkv, 128, generator=g).bfloat16().to(dev)
-    st = dict(K=K, w=w, B=B, CT=CT, co=cod, kmu=kmu, pools=pools, bts=bts, ring=ring,
-              tail_len=torch.full((B,), T, dtype=torch.int32, device=dev),
-              seq=torch.full((B,), L - w["W"], dtype=torch.int32, device=dev),
-              q_host=torch.randn(B, Hq, 128, generator=g).bfloat16().pin_memory(),
-              kv_host=torch.randn(B, 2 * Hkv, 128, generator=g).bfloat16().pin_memory(),
-              out_host=torch.empty(B, Hq * 128, dtype=torch.bfloat16).pin_memory(),
-              out=torch.empty(B, Hq * 128, dtype=torch.bfloat16, device=dev))
-    st["q"] = st["q_host"].to(dev)
-    st["kv"] = st["kv_host"].to(dev)
-    st["Lloc"], st["rank"], st["world"] = L, rank, world
-    if kvseq:
-        st["part"] = torch.zeros(B, Hq, 130, dtype=torch.float32, device=dev)
-        st["parts"] = torch.zeros(world, B, Hq, 130, dtype=torch.float32, device=dev)
-    # the appended token of every sequence goes to position L - W - 1 of its row (a scattered slot per sequence)
-    st["slots"] = [(bt.long()[:, (L - w["W"] - 1) // P] * P + (L - w["W"] - 1) % P).contiguous() for bt in bts]
-    st["slots_host"] = [s.cpu().pin_memory() for s in st["slots"]]
-    return st
-
-
-def plan(st, nsplit):
-    K, w = st["K"], st["w"]
-    ns, ch = K.plan_cb(st["B"], st["Lloc"] - w["W"], w["Hkv"], P, w["kind"], nsplit)
-    st["plan"] = (ns, ch)
-    st["ws"] = K.Workspace(st["B"], w["Hkv"], st["B"] * w["Hkv"] * (ns + 1), st["pools"][0].device)
-
-
-def step(st, i, e2e=False):
-    """one pass of the hot path on pool copy i; returns nothing (asynchronous unless e2e reads the result back).
-    e2e: the step from pinned host buffers and back, replayed as one CUDA graph per pool copy (captured at first use)."""
-    K, w = st["K"], st["w"]
-    c = i % len(st["pools"])
-    if e2e and st.get("graphs", False):
-        gs = st.setdefault("_graphs", {})
-        if c not in gs:
-            from flagrot_releaser_b200.graphs import HostStep
-            step(st, c, e2e=False)                                      # first calls set kernel attributes
-            gs[c] = HostStep([(st["q"], st["q_host"]), (st["kv"], st["kv_host"]), (st["slots"][c], st["slots_host"][c])],
-                             lambda: step(st, c, e2e=False), [(st["out_host"], st["out"])])
-        gs[c].run()
-        return
-    pool, bt = st["pools"][c], st["bts"][c]
-    ns, ch = st["plan"]
-    if e2e:
-        st["q"].copy_(st["q_host"], non_blocking=True)
-        st["kv"].copy_(st["kv_host"], non_blocking=True)
-        st["slots"][c].copy_(st["slots_host"][c], non_blocking=True)
-    K.cb_write(st["kv"], st["slots"][c], st["CT"], st["co"], w["kind"], pool, P, kmu=st["kmu"])
-    ring = st["ring"]
-    K.cb_attn(st["q"], pool, bt, st["seq"], st["out"], ns, ch, st["ws"], LOG2E / math.sqrt(128), w["kind"], tail=ring,
-              tail_len=st["tail_len"], tail_idx=None, tail_bs=ring.stride(0), tail_ts=ring.stride(1), page=P, kv_start=w["S"])
-    if e2e:
-        st["out_host"].copy_(st["out"], non_blocking=True)
-        torch.cuda.current_stream().synchronize()
-
-
-def step_kvseq(st, i, e2e=False, dist=None):
-    """KV-sequence sharded step: the last rank appends the new token, every rank attends over its slice (rank 0 also over
-    the BF16 sink / window rows), partial rows are all-gathered (NCCL) and merged."""
-    K, w = st["K"], st["w"]
-    c = i % len(st["pools"])
-    pool, bt = st["pools"][c], st["bts"][c]
-    ns, ch = st["plan"]
-    first, last = st["rank"] == 0, st["rank"] == st["world"] - 1
-    if e2e:
-        st["q"].copy_(st["q_host"], non_blocking=True)
-        if last:
-            st["kv"].copy_(st["kv_host"], non_blocking=True)
-            st["slots"][c].copy_(st["slots_host"][c], non_blocking=True)
-    if last:
-        K.cb_write(st["kv"], st["slots"][c], st["CT"], st["co"], w["kind"], pool, P, kmu=st["kmu"])
-    ring = st["ring"]
-    tkw = dict(tail=ring, tail_len=st["tail_len"], tail_idx=None, tail_bs=ring.stride(0), tail_ts=ring.stride(1)) if first else {}
-    K.attn_partial(st["q"], pool, bt, st["seq"], st["part"], ns, ch, st["ws"], LOG2E / math.sqrt(128), w["kind"], page=P,
-                   kv_start=w["S"] if first else 0, **tkw)
-    if dist is not None:
-        dist.all_gather_into_tensor(st["parts"].view(-1, *st["part"].shape[1:]), st["part"])   # concatenated along dim 0
-        K.merge_partials_into(st["parts"], st["out"])
-    else:
-        K.merge_partials_into(st["part"][None], st["out"])
-    if e2e:
-        st["out_host"].copy_(st["out"], non_blocking=True)
-        torch.cuda.current_stream().synchronize()
-
-
-def decode_only(st, i):
-    K, w = st["K"], st["w"]
-    c = i % len(st["pools"])
-    ns, ch = st["plan"]
-    ring = st["ring"]
-    K.cb_attn(st["q"], st["pools"][c], st["bts"][c], st["seq"], st["out"], ns, ch, st["ws"], LOG2E / math.sqrt(128), w["kind"],
-              tail=ring, tail_len=st["tail_len"], tail_idx=None, tail_bs=ring.stride(0), tail_ts=ring.stride(1), page=P,
-              kv_start=w["S"])
-
-
-def kvseq_local_len(L, W, world):
-    """context length of one rank when the page tokens [0, L - W) of a sequence are split evenly over `world` ranks (every
-    rank keeps the W window rows in its count, as the single-GPU convention does)."""
-    return (L - W) // world + W
-
-
-def max_over_ranks(ms, dist, device):
+# ---------------------------------------------------------------------------------------------- timing
+def max_over_ranks(ms, dist, device="cuda"):
     """the slowest rank's time (all-reduce MAX), identical on every rank"""
     if dist is None:
         return ms
@@ -262,61 +128,695 @@ def max_over_ranks(ms, dist, device):
     return float(t.item())
 
 
-def timed(fn, steps, warmup, dist=None):
+def timed(fn, steps, warmup, dist=None, sustain_s=0.0):
+    """W warm-up steps (+ the same step repeated untimed for sustain_s seconds), then exactly `steps` steps between two
+    CUDA events on the launch stream, bracketed by barrier + synchronize; max over ranks.  Returns ms per step."""
     for i in range(warmup):
         fn(i)
     torch.cuda.synchronize()
+    n = warmup
+    if sustain_s > 0:
+        # the untimed load: a step count fixed from a short probe and agreed over the ranks (a step may hold a collective,
+        # so every rank has to run the same number of them)
+        t0 = time.perf_counter()
+        for _ in range(8):
+            fn(n)
+            n += 1
+        torch.cuda.synchronize()
+        est = max_over_ranks((time.perf_counter() - t0) * 1e3 / 8, dist)
+        for _ in range(min(200000, int(math.ceil(sustain_s * 1e3 / max(est, 1e-3))))):
+            fn(n)
+            n += 1
+        torch.cuda.synchronize()
     if dist is not None:
         dist.barrier()
         torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for i in range(steps):
-        fn(warmup + i)
+        fn(n + i)
     e1.record()
     torch.cuda.synchronize()
-    ms = e0.elapsed_time(e1)
+    ms = max_over_ranks(e0.elapsed_time(e1), dist)
     if dist is not None:
-        ms = max_over_ranks(ms, dist, "cuda")
         dist.barrier()
     return ms / steps
 
 
-# ---------------------------------------------------------------------------------------------- CPU arm
-def cpu_arm(w, steps, warmup, sample_rows=2):
-    """the reference's CPU path on a bounded sample: `sample_rows` rows of the batch, all kv heads, full context."""
-    from oracle import cpu_decode as C
-    from oracle import flagrot_oracle as O
+def sustained(fn, est_ms, seconds, gpu_index):
+    """a loop of at least `seconds` of back-to-back launches (count fixed beforehand from est_ms) timed by CUDA events, with
+    the SM clock sampled over the loop.  Returns (ms per launch, launches, clocks)."""
+    n = max(20, int(math.ceil(seconds * 1e3 / max(est_ms, 1e-3))))
+    for i in range(3):
+        fn(i)
+    torch.cuda.synchronize()
+    smp = ClockSampler(gpu_index).start()
+    time.sleep(0.15)                                     # the sampler's first line takes a moment
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(n):
+        fn(3 + i)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / n
+    return ms, n, smp.stop()
+
+
+def graph_of(fn):
+    """fn() captured as one CUDA graph (fn has run before: kernel attributes are set)"""
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        fn()
+    return g
+
+
+# ---------------------------------------------------------------------------------------------- FlagRot INT4 / INT2 decode
+def kvseq_local_len(L, W, world):
+    """context length of one rank when the page tokens [0, L - W) of a sequence are split evenly over `world` ranks (every
+    rank keeps the W window rows in its count, as the single-GPU convention does)."""
+    return (L - W) // world + W
+
+
+class DecodeWorkload:
+    """cfg2 / cfg3 / cfg5b: fr_cb_write (T = batch) + fr_cb_attn over konlya / konlya2 pages with BF16 sink + window rows."""
+
+    metric, unit, bound = "decode_attention_kv_gbps", "GB/s", "hbm"
+
+    def __init__(self, w, rank, world, dev, a):
+        from flagrot_releaser_b200 import kernels as K
+        self.K, self.w, self.rank, self.world, self.dev, self.a = K, w, rank, world, dev, a
+        self.kvseq = w["shard"] == "kvseq"
+        self.B = w["B"] // world if w["shard"] == "batch" else w["B"]
+        assert self.B >= 1 and (w["shard"] != "batch" or w["B"] % world == 0), "the batch must divide over the ranks"
+        self.cell = 144 if w["nb"] == 4 else 80
+        self.Lloc = kvseq_local_len(w["L"], w["W"], world) if self.kvseq else w["L"]
+        per_copy = self.B * self.Lloc * w["Hkv"] * self.cell
+        # pool copies cycled: an explicit --ncopy, else enough distinct memory that no page survives in L2 between steps
+        self.ncopy = a.ncopy if a.ncopy > 0 else min(64, max(1 if per_copy > (600 << 20) else 3, -(-(400 << 20) // per_copy)))
+        self.build(seed=1234 + rank)
+        ns, ch = K.plan_cb(self.B, self.Lloc - w["W"], w["Hkv"], P, w["kind"], a.nsplit or None)
+        self.plan = (ns, ch)
+        self.ws = K.Workspace(self.B, w["Hkv"], self.B * w["Hkv"] * (ns + 1), dev)
+        self.dist = None
+
+    def build(self, seed):
+        """synthetic inputs of the named shape and the quantised caches (written by the library's own dynamic writer, which
+        the parity tests hold bit-exact).  ncopy distinct pools (distinct random page tables over distinct memory) are cycled
+        so that no page is L2-resident between steps."""
+        K, w, dev, B, L = self.K, self.w, self.dev, self.B, self.Lloc
+        g = torch.Generator().manual_seed(seed)
+        Hkv, Hq = w["Hkv"], w["Hq"]
+        npages_seq = L // P
+        npool = B * npages_seq + 7
+        qs = torch.randn(Hkv, 512, 128, generator=g) * (torch.rand(Hkv, 1, 128, generator=g) + 0.5).sqrt()
+        Cq = (torch.einsum("hnd,hne->hde", qs, qs) / 512).contiguous()
+        self.CT = Cq.transpose(1, 2).contiguous().to(dev)
+        self.co = (torch.rand(Hkv, 128, generator=g) + 0.5).to(dev)
+        out_ch = torch.stack([torch.randperm(128, generator=g)[:6] for _ in range(Hkv)])          # 5 % of channels x10
+        self.kmu = offs = None
+        if w["center"]:
+            offs = torch.randn(Hkv, 128, generator=g) * math.sqrt(2.0)
+            self.kmu = offs.float().contiguous().to(dev)
+        chunk_b = K.cb_chunk_bytes(w["kind"], P)
+        self.pools, self.bts = [], []
+        rows_per = 64 * 1024
+        for _ in range(self.ncopy):
+            pool = torch.randint(0, 256, (npool, Hkv, chunk_b), dtype=torch.uint8, generator=g).to(dev)
+            bt = torch.randperm(npool, generator=g)[:B * npages_seq].reshape(B, npages_seq).int()
+            pos = torch.arange(L)
+            slots = (bt.long()[:, pos // P] * P + pos % P).reshape(-1)
+            for r0 in range(0, B * L, rows_per):
+                n = min(rows_per, B * L - r0)
+                kv = torch.randn(n, 2 * Hkv, 128, generator=g)
+                for h in range(Hkv):
+                    kv[:, h, out_ch[h]] *= 10
+                if offs is not None:
+                    kv[:, :Hkv] += offs
+                K.cb_write(kv.bfloat16().to(dev), slots[r0:r0 + n].to(dev), self.CT, self.co, w["kind"], pool, P, kmu=self.kmu)
+            torch.cuda.synchronize()
+            self.pools.append(pool)
+            self.bts.append(bt.to(dev))
+        T = w["S"] + w["W"]
+        self.ring = torch.randn(B, T, 2 * Hkv, 128, generator=g).bfloat16().to(dev)
+        self.tail_len = torch.full((B,), T, dtype=torch.int32, device=dev)
+        self.seq = torch.full((B,), L - w["W"], dtype=torch.int32, device=dev)
+        self.q_host = torch.randn(B, Hq, 128, generator=g).bfloat16().pin_memory()
+        self.kv_host = torch.randn(B, 2 * Hkv, 128, generator=g).bfloat16().pin_memory()
+        self.out_host = torch.empty(B, Hq * 128, dtype=torch.bfloat16).pin_memory()
+        self.out = torch.empty(B, Hq * 128, dtype=torch.bfloat16, device=dev)
+        self.q, self.kv = self.q_host.to(dev), self.kv_host.to(dev)
+        if self.kvseq:
+            self.part = torch.zeros(B, Hq, 130, dtype=torch.float32, device=dev)
+            self.parts = torch.zeros(self.world, B, Hq, 130, dtype=torch.float32, device=dev)
+        # the appended token of every sequence goes to position L - W - 1 of its row (a scattered slot per sequence)
+        self.slots = [(bt.long()[:, (L - w["W"] - 1) // P] * P + (L - w["W"] - 1) % P).contiguous() for bt in self.bts]
+        self.slots_host = [s.cpu().pin_memory() for s in self.slots]
+
+    # ---- the step
+    def _attn_args(self, c):
+        w, ring = self.w, self.ring
+        return dict(tail=ring, tail_len=self.tail_len, tail_idx=None, tail_bs=ring.stride(0), tail_ts=ring.stride(1))
+
+    def resident(self, c):
+        K, w = self.K, self.w
+        ns, ch = self.plan
+        if self.kvseq:
+            return self.resident_kvseq(c)
+        K.cb_write(self.kv, self.slots[c], self.CT, self.co, w["kind"], self.pools[c], P, kmu=self.kmu)
+        K.cb_attn(self.q, self.pools[c], self.bts[c], self.seq, self.out, ns, ch, self.ws, LOG2E * SCALE, w["kind"], page=P,
+                  kv_start=w["S"], **self._attn_args(c))
+
+    def resident_kvseq(self, c):
+        """the last rank appends the new token, every rank attends over its slice (rank 0 also over the BF16 sink / window
+        rows), partial rows are all-gathered (NCCL) and merged"""
+        K, w = self.K, self.w
+        ns, ch = self.plan
+        first, last = self.rank == 0, self.rank == self.world - 1
+        if last:
+            K.cb_write(self.kv, self.slots[c], self.CT, self.co, w["kind"], self.pools[c], P, kmu=self.kmu)
+        tkw = self._attn_args(c) if first else {}
+        K.attn_partial(self.q, self.pools[c], self.bts[c], self.seq, self.part, ns, ch, self.ws, LOG2E * SCALE, w["kind"], page=P,
+                       kv_start=w["S"] if first else 0, **tkw)
+        if self.dist is not None:
+            self.dist.all_gather_into_tensor(self.parts.view(-1, *self.part.shape[1:]), self.part)
+            K.merge_partials_into(self.parts, self.out)
+        else:
+            K.merge_partials_into(self.part[None], self.out)
+
+    def kernel(self, c):
+        K, w = self.K, self.w
+        ns, ch = self.plan
+        K.cb_attn(self.q, self.pools[c], self.bts[c], self.seq, self.out, ns, ch, self.ws, LOG2E * SCALE, w["kind"], page=P,
+                  kv_start=w["S"], **self._attn_args(c))
+
+    def e2e(self, c):
+        self.q.copy_(self.q_host, non_blocking=True)
+        if not self.kvseq or self.rank == self.world - 1:
+            self.kv.copy_(self.kv_host, non_blocking=True)
+            self.slots[c].copy_(self.slots_host[c], non_blocking=True)
+        g = getattr(self, "graphs", None)
+        if g is not None:
+            g[c].replay()
+        else:
+            self.resident(c)
+        self.out_host.copy_(self.out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    # ---- accounting
+    def job_units(self):
+        """algorithmic bytes of the decode read of the whole job (all ranks)"""
+        w = self.w
+        n = self.world if w["shard"] == "replica" else 1
+        return n * self._bytes(w["B"], w["L"])
+
+    def _bytes(self, B, L):
+        w = self.w
+        return (B * w["Hkv"] * self.cell * (L - w["W"] - w["S"]) + B * (w["S"] + w["W"]) * 2 * w["Hkv"] * 128 * 2
+                + B * w["Hq"] * 128 * 2 * 2)
+
+    def launch_units(self):
+        """algorithmic bytes of this rank's decode launch (kvseq: rank 0 carries the BF16 rows)"""
+        w = self.w
+        if self.kvseq:
+            return self._bytes(self.B, w["L"]) - self.B * w["Hkv"] * self.cell * (w["L"] - self.Lloc)
+        return self._bytes(self.B, w["L"])
+
+    def copies(self):
+        return int(self.q_host.numel() * 2 + self.kv_host.numel() * 2 + self.B * 8), int(self.out_host.numel() * 2)
+
+    launches = property(lambda self: 3 if self.kvseq else 2)    # append (keys + value rows, one launch), decode [, merge]
+    kernel_name = property(lambda self: f"k_decode<{self.w['nb']}, key-only>")
+
+    def config(self):
+        w, world = self.w, self.world
+        par = {"replica": f"batch replicas x{world}, no collective", "batch": f"batch-sharded x{world} ({self.B} rows per rank), no collective",
+               "kvseq": f"kv-sequence sharded x{world}, NCCL all-gather of (o, m, l) rows + LSE merge"}[w["shard"]]
+        return {"batch_per_gpu": self.B, "nsplit": self.plan[0], "chunk": self.plan[1],
+                "l2": f"{self.ncopy} distinct {self.pools[0].numel() >> 20} MiB pools cycled "
+                      f"({self.ncopy * self.pools[0].numel() >> 20} MiB in all, more than the 126 MB L2)",
+                "parallelism": par if world > 1 else "single gpu",
+                "step": ("fr_cb_write (last rank) + fr_attn_partial + all-gather + fr_merge_partials" if self.kvseq
+                         else "fr_cb_write (T = batch) + fr_cb_attn")}
+
+    def status(self):
+        return self.K.device_status()
+
+
+# ---------------------------------------------------------------------------------------------- KIVI decode
+class KiviWorkload:
+    """cfg4: kv_v_write (T = batch) + kv_attn over kivi2:32 pages; tensor parallel by kv head."""
+
+    metric, unit, bound = "decode_attention_kv_gbps", "GB/s", "hbm"
+    GRP, D = 32, 128
+
+    def __init__(self, w, rank, world, dev, a):
+        from flagrot_releaser_b200 import kivi as KV
+        self.KV, self.w, self.rank, self.world, self.dev, self.a = KV, w, rank, world, dev, a
+        assert w["Hkv"] % world == 0, "kv heads must divide over the ranks"
+        self.Hkv = w["Hkv"] // world                       # this rank's kv heads [rank Hkv, (rank + 1) Hkv) and their q heads
+        self.G = w["Hq"] // w["Hkv"]
+        self.B, self.L, self.S, self.W = w["B"], w["L"], w["S"], w["W"]
+        per_copy = self.B * (self.L // P) * self.Hkv * KV.chunk_bytes(self.D)
+        self.ncopy = a.ncopy if a.ncopy > 0 else min(64, max(2, -(-(400 << 20) // per_copy)))
+        self.build(seed=4321)
+        self.plan = KV.plan(self.B, self.L, self.Hkv) if not a.nsplit else (a.nsplit, max(256, -(-self.L // a.nsplit // 128) * 128))
+        self.ws = KV.Workspace(self.B * self.Hkv * (self.plan[0] + 1), self.G, self.D, dev)
+
+    def build(self, seed):
+        KV, dev, B, L, D, GRP, S = self.KV, self.dev, self.B, self.L, self.D, self.GRP, self.S
+        g = torch.Generator().manual_seed(seed)            # the same stream on every rank: the job's tensors, then sliced
+        Hall, h0, Hkv, G = self.w["Hkv"], self.rank * self.Hkv, self.Hkv, self.G
+        NQ = 64                                            # calibration queries per kv head (N(0, 0.3^2), log-normaliser 5.0)
+        sl = slice(h0, h0 + Hkv)
+        self.qs = (torch.randn(Hall, NQ, D, generator=g) * 0.3)[sl].contiguous().to(dev)
+        self.lz = torch.full((Hkv, NQ), 5.0, dtype=torch.float32, device=dev)
+        self.co = (torch.rand(Hall, D, generator=g) + 0.5)[sl].contiguous().to(dev)
+        out_ch = torch.stack([torch.randperm(D, generator=g)[:6] for _ in range(Hall)])[sl]
+        npg = L // P
+        self.pools, self.bts = [], []
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        self.us_v = self.us_k = 0.0
+        for _ in range(self.ncopy):
+            nb = B * npg + 3
+            pool = torch.zeros(nb, Hkv, KV.chunk_bytes(D), dtype=torch.uint8, device=dev)
+            bt = torch.randperm(nb - 3, generator=g).view(B, npg).int()
+            for b in range(B):
+                kv = torch.randn(L, 2 * Hkv, D, generator=g)
+                for h in range(Hkv):
+                    kv[:, h, out_ch[h]] *= 10
+                kv = kv.bfloat16().to(dev)
+                pos = torch.arange(L)
+                slots = (bt[b].long()[pos // P] * P + pos % P).to(dev)
+                gp = torch.arange(L).view(L // GRP, GRP)
+                sidx = torch.where(gp < S, torch.full_like(gp, -1), gp).contiguous().to(dev)
+                dslot = (bt[b].long()[gp // P] * P + gp % P).contiguous().to(dev)
+                ev[0].record()
+                KV.v_write(kv, slots, self.co, None, pool, Hkv, D)
+                ev[1].record()
+                KV.k_encode(kv, sidx, dslot, self.qs, self.lz, SCALE, pool, Hkv, D)
+                ev[2].record()
+                torch.cuda.synchronize()
+                self.us_v += ev[0].elapsed_time(ev[1]) * 1e3
+                self.us_k += ev[1].elapsed_time(ev[2]) * 1e3
+            self.pools.append(pool)
+            self.bts.append(bt.to(dev))
+        ntok = self.ncopy * B * L
+        self.us_v, self.us_k = self.us_v / ntok, self.us_k / ntok
+        T = self.S + self.W
+        Hq = Hkv * G
+        self.T = T
+        self.ring = torch.randn(B + 1, T, 2 * Hkv, D, generator=g).bfloat16().to(dev)
+        self.q_host = torch.randn(B, Hq, D, generator=g).bfloat16().pin_memory()
+        self.kv_host = torch.randn(B, 2 * Hkv, D, generator=g).bfloat16().pin_memory()
+        self.out_host = torch.empty(B, Hq * D, dtype=torch.bfloat16).pin_memory()
+        self.q, self.kv = self.q_host.to(dev), self.kv_host.to(dev)
+        self.out = torch.zeros(B, Hq * D, dtype=torch.bfloat16, device=dev)
+        self.cached = torch.full((B,), L - self.W, dtype=torch.int32, device=dev)
+        self.tl = torch.full((B,), T, dtype=torch.int32, device=dev)
+        self.ti = torch.arange(B, dtype=torch.int32, device=dev)
+        # the appended value row of every sequence lands at position L - W - 1 (keys are encoded per completed group)
+        self.slots = [(bt.long()[:, (L - self.W - 1) // P] * P + (L - self.W - 1) % P).contiguous() for bt in self.bts]
+        self.slots_host = [s.cpu().pin_memory() for s in self.slots]
+
+    def kernel(self, c):
+        ns, chunk = self.plan
+        self.KV.attn(self.q, self.pools[c], self.bts[c], self.cached, self.out, ns, chunk, self.ws, LOG2E * SCALE, self.S, self.G,
+                     ring=self.ring.view(-1, 2 * self.Hkv, self.D), tail_len=self.tl, tail_idx=self.ti, T=self.T)
+
+    def resident(self, c):
+        self.KV.v_write(self.kv, self.slots[c], self.co, None, self.pools[c], self.Hkv, self.D)
+        self.kernel(c)
+
+    def e2e(self, c):
+        self.q.copy_(self.q_host, non_blocking=True)
+        self.kv.copy_(self.kv_host, non_blocking=True)
+        self.slots[c].copy_(self.slots_host[c], non_blocking=True)
+        g = getattr(self, "graphs", None)
+        if g is not None:
+            g[c].replay()
+        else:
+            self.resident(c)
+        self.out_host.copy_(self.out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    def _bytes(self, Hkv):
+        cell = self.KV.cell_bytes(self.D)
+        return (self.B * Hkv * cell * (self.L - self.W - self.S) + self.B * self.T * 2 * Hkv * self.D * 2
+                + self.B * Hkv * self.G * self.D * 2 * 2)
+
+    def job_units(self):
+        return self._bytes(self.w["Hkv"])
+
+    def launch_units(self):
+        return self._bytes(self.Hkv)
+
+    def copies(self):
+        return int(self.q_host.numel() * 2 + self.kv_host.numel() * 2 + self.B * 8), int(self.out_host.numel() * 2)
+
+    launches = 3                                           # value append, page + window splits (one launch), split merge
+    kernel_name = "k_kv_attn_mma2 (page splits + BF16 window split) + k_kv_merge"
+
+    def config(self):
+        return {"batch_per_gpu": self.B, "kv_heads_per_gpu": self.Hkv, "nsplit": self.plan[0], "chunk": self.plan[1],
+                "l2": f"{self.ncopy} distinct {self.pools[0].numel() >> 20} MiB pools cycled",
+                "parallelism": (f"tensor parallel by kv head x{self.world} ({self.Hkv} kv heads + {self.Hkv * self.G} q heads per rank, "
+                                f"calibration rows sliced alike), no collective in the path") if self.world > 1 else "single gpu",
+                "step": "kv_v_write (T = batch) + kv_attn",
+                "writers_us_per_token": {"kv_v_write": self.us_v, "kv_k_encode": self.us_k}}
+
+    def status(self):
+        return 0
+
+    def race_reference(self):
+        """the reference's own kv_attn (kivi.cu built unmodified for sm_100a, oracle/_ref) on the same pools and plan: a bench
+        leg only, never the product path"""
+        p = ROOT / "oracle" / "_ref" / "libflagrot_kivi_ref.so"
+        if not p.exists():
+            return None
+        L = ctypes.CDLL(str(p))
+        PP, I, LL, F = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float
+        L.kv_attn.argtypes = [PP, LL, PP, PP, LL, PP, I, I, I, I, I, I, I, F, PP, PP, PP, I, PP, PP, PP, LL, I, PP]
+        L.kv_attn.restype = I
+        ns, chunk = self.plan
+        out2 = torch.zeros_like(self.out)
+        ring = self.ring.view(-1, 2 * self.Hkv, self.D)
+
+        def run(c):
+            rc = L.kv_attn(self.q.data_ptr(), self.q.stride(0), self.pools[c].data_ptr(), self.bts[c].data_ptr(), self.bts[c].stride(0),
+                           self.cached.data_ptr(), self.S, self.B, self.Hkv, self.G, self.D, ns, chunk, LOG2E * SCALE, ring.data_ptr(),
+                           self.tl.data_ptr(), self.ti.data_ptr(), self.T, self.ws.opart.data_ptr(), self.ws.ml.data_ptr(),
+                           out2.data_ptr(), out2.stride(0), 0, torch.cuda.current_stream().cuda_stream)
+            assert rc == 0, rc
+        ms = timed(lambda i: run(i % self.ncopy), 10, 3)
+        self.kernel(0)
+        run(0)
+        torch.cuda.synchronize()
+        diff = float((self.out.float() - out2.float()).abs().max())
+        return {"kernel": "reference kv_attn (k_attn3 + k_merge, mma.sync) at sm_100a", "us_per_launch": ms * 1e3,
+                "GB/s": self.launch_units() / (ms * 1e-3) / 1e9, "max_abs_diff_vs_ours": diff}
+
+
+# ---------------------------------------------------------------------------------------------- prefix-cached prefill
+class PrefillWorkload:
+    """cfg5a: frmq_prep_q + frmq_attn + frmq_merge over INT4 konlya pages; requests dealt over the ranks."""
+
+    metric, unit, bound = "mq_prefill_attention_tflops", "TFLOP/s", "tensor"
+
+    def __init__(self, w, rank, world, dev, a):
+        from flagrot_releaser_b200 import kernels as K
+        from flagrot_releaser_b200 import prefill_mq as MQ
+        self.K, self.MQ, self.w, self.rank, self.world, self.dev, self.a = K, MQ, w, rank, world, dev, a
+        assert w["B"] % world == 0, "the requests must divide over the ranks"
+        self.B, self.new, self.cached, self.Hq, self.Hkv = w["B"] // world, w["new"], w["L"], w["Hq"], w["Hkv"]
+        self.G = self.Hq // self.Hkv
+        self.konly = w["kind"].startswith("konlya")
+        self.build(seed=99 + rank)
+        self.plan = MQ.build_plan(self.reqs, self.G, self.Hkv, 0, dev)
+        self.out = torch.zeros(self.q.shape[0], self.Hq * 128, dtype=torch.bfloat16, device=dev)
+
+    def build(self, seed):
+        K, dev, w = self.K, self.dev, self.w
+        g = torch.Generator().manual_seed(seed)
+        L = self.cached + self.new
+        npg = -(-L // P)
+        total = self.B * npg + 3
+        pool = torch.zeros(total, self.Hkv, (80 if w["nb"] == 2 else 144) * P, dtype=torch.uint8, device=dev)
+        bt = torch.randperm(self.B * npg, generator=g).int().view(self.B, npg).contiguous()
+        A = torch.randn(self.Hkv, 128, 128, generator=g) / math.sqrt(128)
+        CT = (A @ A.transpose(1, 2) + 0.1 * torch.eye(128)).contiguous().to(dev)
+        co = torch.ones(self.Hkv, 128, device=dev)
+        out_ch = torch.randperm(128, generator=g)[:6]
+        for r in range(self.B):
+            for t0 in range(0, L, 8192):
+                n = min(8192, L - t0)
+                kv = torch.randn(n, 2 * self.Hkv, 128, generator=g)
+                kv[:, :self.Hkv, out_ch] *= 10
+                pos = torch.arange(t0, t0 + n)
+                sl = (bt[r].long()[pos // P] * P + pos % P).to(dev)
+                K.cb_write(kv.bfloat16().to(dev), sl, CT, co, w["kind"], pool, P)
+        self.pool, self.bt = pool, bt.to(dev)
+        self.q_host = torch.randn(self.B * self.new, self.Hq, 128, generator=g).bfloat16().pin_memory()
+        self.q = self.q_host.to(dev)
+        self.out_host = torch.empty(self.B * self.new, self.Hq * 128, dtype=torch.bfloat16).pin_memory()
+        self.reqs = [(r, r * self.new, (r + 1) * self.new, L, self.cached) for r in range(self.B)]
+
+    def resident(self, c):
+        MQ = self.MQ
+        self.q16 = MQ.prep_q(self.q, SCALE * MQ.LOG2E, self.G, idx=self.plan.idx)
+        self.opart, self.ml = MQ.attn(self.q16, self.pool, self.bt, self.plan, self.G, 0, konly=self.konly, int2=self.w["nb"] == 2)
+        MQ.merge(self.plan, self.opart, self.ml, self.G, out=self.out)
+
+    def kernel(self, c):
+        self.MQ.attn(self.q16, self.pool, self.bt, self.plan, self.G, 0, konly=self.konly, int2=self.w["nb"] == 2)
+
+    def e2e(self, c):
+        self.q.copy_(self.q_host, non_blocking=True)
+        self.resident(c)
+        self.out_host.copy_(self.out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    def _flops(self, B):
+        pairs = B * self.new * (self.cached + (self.new + 1) / 2)     # the causal triangle is counted exactly
+        return 4.0 * 128 * self.Hq * pairs
+
+    def job_units(self):
+        return self._flops(self.w["B"])
+
+    def launch_units(self):
+        return self._flops(self.B)
+
+    def copies(self):
+        return int(self.q_host.numel() * 2), int(self.out_host.numel() * 2)
+
+    launches = 3
+    kernel_name = "k_mq_tc<4, key-only> (tcgen05)"
+    ncopy = 1
+
+    def config(self):
+        return {"requests_per_gpu": self.B, "kernel": self.plan.kernel, "rows": self.plan.rows, "tiles": self.plan.ntiles,
+                "items": self.plan.nitems, "l2": f"one {self.pool.numel() >> 20} MiB pool (more than the 126 MB L2), read once per step",
+                "parallelism": f"requests dealt over {self.world} ranks, no collective" if self.world > 1 else "single gpu",
+                "step": "frmq_prep_q + frmq_attn + frmq_merge"}
+
+    def status(self):
+        return self.MQ.device_status()
+
+
+# ---------------------------------------------------------------------------------------------- writers vs the reference's kernels
+def writers_race(dev):
+    """our writers against the reference's own kernels built for sm_100a (oracle/_ref): a bench leg only.  Per entry and
+    T: microseconds per call (CUDA events, 10 calls after 3 warm-up calls), identical arguments and pools."""
+    from flagrot_releaser_b200 import kernels as K
+    from flagrot_releaser_b200 import kivi as KV
+    res = {}
+    PP, I, LL, F = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float
+    w3 = ROOT / "oracle" / "_ref" / "libflagrot_w3ref.so"
+    kr = ROOT / "oracle" / "_ref" / "libflagrot_kivi_ref.so"
+    Hkv = 8
+    g = torch.Generator().manual_seed(7)
+    qs = torch.randn(Hkv, 512, 128, generator=g)
+    Cq = (torch.einsum("hnd,hne->hde", qs, qs) / 512).contiguous()
+    CT, co = Cq.transpose(1, 2).contiguous().to(dev), (torch.rand(Hkv, 128, generator=g) + 0.5).to(dev)
+    mask = (torch.rand(2 * Hkv, 4, generator=g) < 0.5).to(torch.uint8).to(dev)
+    hfull = (torch.rand(2 * Hkv, generator=g) < 0.4).to(torch.uint8).to(dev)
+    st = lambda: torch.cuda.current_stream().cuda_stream  # noqa: E731
+    for T in (64, 65536):
+        kv = torch.randn(T, 2 * Hkv, 128, generator=g)
+        kv[:, :Hkv, :6] *= 10
+        kv = kv.bfloat16().to(dev)
+        npg = T // P + 64
+        slots = torch.randperm(npg * P, generator=g)[:T].to(torch.int64).to(dev)
+        pool = torch.zeros(npg, Hkv, 144 * P, dtype=torch.uint8, device=dev)
+        row = {"ours": {}, "reference": {}}
+        row["ours"]["fr_cb_write3 konlya"] = timed(lambda i: K.cb_write3(kv, slots, CT, co, None, None, "konlya", pool, P, split=False), 10, 3) * 1e3
+        row["ours"]["fr_w3_static_write int4a"] = timed(lambda i: K.w3_static_write(kv, slots, mask, hfull, pool, P, fmt="int4a"), 10, 3) * 1e3
+        if w3.exists():
+            R = ctypes.CDLL(str(w3))
+            R.fr_cb_write3.argtypes = [PP, LL, PP, I, I, I, I, PP, PP, PP, PP, PP, I, PP, I, I, PP, PP]
+            R.fr_w3_static_write.argtypes = [PP, LL, PP, I, I, I, PP, PP, I, PP, I, PP, PP]
+            sg = K.sign_words()
+            # the reference's ranking tables (kernels.py w3_calib) are optional inputs of its kernel: nullptr = exact path
+            row["reference"]["fr_cb_write3 konlya"] = timed(lambda i: R.fr_cb_write3(
+                kv.data_ptr(), kv.stride(0), slots.data_ptr(), 0, T, Hkv, P, CT.data_ptr(), co.data_ptr(), None, None, sg, 10,
+                pool.data_ptr(), 1, 1, st(), None), 10, 3) * 1e3
+            row["reference"]["fr_w3_static_write int4a"] = timed(lambda i: R.fr_w3_static_write(
+                kv.data_ptr(), kv.stride(0), slots.data_ptr(), T, Hkv, P, mask.data_ptr(), hfull.data_ptr(), 1, pool.data_ptr(), 0,
+                st(), None), 10, 3) * 1e3
+        # KIVI writers
+        D, GRP = 128, 32
+        kpool = torch.zeros(npg, Hkv, KV.chunk_bytes(D), dtype=torch.uint8, device=dev)
+        cqs = (torch.randn(Hkv, 64, D, generator=g) * 0.3).to(dev)
+        lz = torch.full((Hkv, 64), 5.0, device=dev)
+        ng = max(T // GRP, 1)
+        gp = torch.arange(ng * GRP).view(ng, GRP) % T
+        sidx = gp.contiguous().to(dev)
+        dslot = slots[gp.reshape(-1)].view(ng, GRP).contiguous()
+        row["ours"]["kv_v_write"] = timed(lambda i: KV.v_write(kv, slots, co, None, kpool, Hkv, D), 10, 3) * 1e3
+        row["ours"]["kv_k_encode"] = timed(lambda i: KV.k_encode(kv, sidx, dslot, cqs, lz, SCALE, kpool, Hkv, D), 10, 3) * 1e3
+        if kr.exists():
+            R = ctypes.CDLL(str(kr))
+            R.kv_v_write.argtypes = [PP, LL, I, I, I, PP, PP, PP, PP, I, PP, I, PP]
+            R.kv_k_encode.argtypes = [PP, LL, PP, LL, PP, PP, I, I, I, PP, PP, I, F, PP, I, PP, I, PP]
+            row["reference"]["kv_v_write"] = timed(lambda i: R.kv_v_write(kv.data_ptr(), kv.stride(0), T, Hkv, D, slots.data_ptr(),
+                                                                         co.data_ptr(), None, kpool.data_ptr(), 0, None, 0, st()), 10, 3) * 1e3
+            row["reference"]["kv_k_encode"] = timed(lambda i: R.kv_k_encode(kv.data_ptr(), kv.stride(0), None, 0, sidx.data_ptr(),
+                                                                           dslot.data_ptr(), ng, Hkv, D, cqs.data_ptr(), lz.data_ptr(), 64,
+                                                                           SCALE, kpool.data_ptr(), 0, None, 0, st()), 10, 3) * 1e3
+        res[f"T={T}"] = row
+    return res
+
+
+# ---------------------------------------------------------------------------------------------- the reference's CPU path
+def reference_front():
+    """the reference's own Python front ends (byte code built by oracle/build_ref.sh), or None"""
+    d = ROOT / "oracle" / "_ref" / "pyref"
+    if not (d / "vllm_flagrot" / "kernels.pyc").exists():
+        return None
+    os.environ.setdefault("FLAGROT_NO_REBUILD", "1")
+    sys.path.insert(0, str(d))
+    try:
+        import importlib
+        return importlib.import_module("vllm_flagrot.kernels"), importlib.import_module("vllm_flagrot.kivi")
+    except Exception:
+        return None
+    finally:
+        sys.path.remove(str(d))
+
+
+def _scale_words(rs, shape):
+    """sane scale words (positive fp16 around 2^-8 .. 2^-4) with random flag bits and zero points"""
+    return rs.randint(0x1C00, 0x2C00, shape).astype(np.uint16) | (rs.randint(0, 2, shape) << 15).astype(np.uint16)
+
+
+def cpu_arm(wname, w, steps, warmup):
+    """the reference's CPU implementation of the workload's attention on a bounded sample, all host threads.  Returns
+    (metric value scaled to the sample's work, seconds per step, cpu_baseline object)."""
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
     rs = np.random.RandomState(0)
-    Hkv, Hq, L = w["Hkv"], w["Hq"], w["L"]
-    nseq = sample_rows
-    npool = nseq * (L // P)
-    pool = rs.randint(0, 256, (npool, Hkv, O.chunk_bytes(w["nb"], P)), dtype=np.uint8)
-    # sane scale words (positive fp16 around 2^-8 .. 2^-4) with random flag bits and zero points, random codes
-    for off in ((128 * P, 144 * P) if w["nb"] == 4 else (64 * P, 80 * P)),:
-        words = (rs.randint(0x1C00, 0x2C00, (npool, Hkv, 8 * P)).astype(np.uint16) | (rs.randint(0, 2, (npool, Hkv, 8 * P)) << 15).astype(np.uint16))
-        pool[:, :, off[0]:off[1]] = words.view(np.uint8).reshape(npool, Hkv, 16 * P)
-    bt = rs.permutation(npool).reshape(nseq, L // P).astype(np.int32)
-    q = (rs.randn(nseq, Hq, 128).astype(np.float32).view(np.uint32) >> 16).astype(np.uint16)
-    T = w["S"] + w["W"]
-    ring = (rs.randn(nseq, T, 2 * Hkv, 128).astype(np.float32).view(np.uint32) >> 16).astype(np.uint16)
-    lens = np.full(nseq, L - w["W"], np.int32)
-    tl = np.full(nseq, T, np.int32)
+    ref = reference_front()
+    if w["path"] == "decode":
+        from oracle import flagrot_oracle as O
+        Hkv, Hq, L, nb = w["Hkv"], w["Hq"], min(w["L"], 16384), w["nb"]
+        nseq = 2 if w["L"] <= 16384 else 1
+        npool = nseq * (L // P)
+        pool = rs.randint(0, 256, (npool, Hkv, O.chunk_bytes(nb, P)), dtype=np.uint8)
+        off = (128 * P, 144 * P) if nb == 4 else (64 * P, 80 * P)
+        pool[:, :, off[0]:off[1]] = _scale_words(rs, (npool, Hkv, 8 * P)).view(np.uint8).reshape(npool, Hkv, 16 * P)
+        bt = rs.permutation(npool).reshape(nseq, L // P).astype(np.int32)
+        T = w["S"] + w["W"]
+        G = Hq // Hkv
+        unit_bytes = (nseq * Hkv * (144 if nb == 4 else 80) * (L - w["W"] - w["S"]) + nseq * T * 2 * Hkv * 128 * 2 + nseq * Hq * 128 * 4)
+        sample = f"{nseq} of {w['B']} batch rows, all {Hkv} kv heads, context {L}" + ("" if L == w["L"] else f" of {w['L']}")
+        if ref is not None:
+            RK = ref[0]
+            poolt, btt = torch.from_numpy(pool), torch.from_numpy(bt).long()
+            q = torch.randn(nseq, Hq, 128).bfloat16().float()
+            ring = torch.randn(nseq, T, 2 * Hkv, 128).bfloat16().float()
+
+            def step():
+                # kernels.py dequant_cb_pages (the plugin's PyTorch page parser) + fp32 attention over pages [S, L - W) and the BF16 rows
+                Kp, Vp = RK.dequant_cb_pages(poolt, P, w["kind"], torch.float32)
+                o = torch.empty(nseq, Hq, 128)
+                for b in range(nseq):
+                    k = torch.cat([Kp[btt[b]].reshape(L, Hkv, 128)[w["S"]:L - w["W"]], ring[b, :, :Hkv]])
+                    v = torch.cat([Vp[btt[b]].reshape(L, Hkv, 128)[w["S"]:L - w["W"]], ring[b, :, Hkv:]])
+                    s = torch.einsum("hgd,thd->hgt", q[b].view(Hkv, G, 128), k) * SCALE
+                    o[b] = torch.einsum("hgt,thd->hgd", torch.softmax(s, -1), v).reshape(Hq, 128)
+                return o
+            kind, how = "reference", "the reference's PyTorch page parser (kernels.py dequant_cb_pages) + fp32 einsum / softmax attention"
+        else:
+            from oracle import cpu_decode as C
+            qb = (rs.randn(nseq, Hq, 128).astype(np.float32).view(np.uint32) >> 16).astype(np.uint16)
+            ringb = (rs.randn(nseq, T, 2 * Hkv, 128).astype(np.float32).view(np.uint32) >> 16).astype(np.uint16)
+            lens, tl = np.full(nseq, L - w["W"], np.int32), np.full(nseq, T, np.int32)
+
+            def step():
+                return C.decode_rows_fp32(qb, pool, bt, lens, SCALE, nb, P, True, list(range(nseq)), tail=ringb, tail_len=tl, kv_start=w["S"])
+            kind, how = "port", "fp32 numpy restatement of the reference's page parser + attention (oracle/cpu_decode.py)"
+        to_metric = lambda sec: unit_bytes / sec / 1e9  # noqa: E731
+    elif w["path"] == "kivi":
+        from oracle import kivi_oracle as KO
+        Hkv, Hq, L, D = w["Hkv"], w["Hq"], w["L"], 128
+        G = Hq // Hkv
+        nseq = 1
+        npool = nseq * (L // P)
+        pool = rs.randint(0, 256, (npool, Hkv, KO.CB), dtype=np.uint8)
+        for lo, hi in ((KO.OFF_KM, KO.OFF_VC), (KO.OFF_VM, KO.OFF_VF)):       # finite fp16 (scale | flag, min) pairs
+            pool[:, :, lo:hi] = _scale_words(rs, (npool, Hkv, (hi - lo) // 2)).view(np.uint8).reshape(npool, Hkv, hi - lo)
+        bt = rs.permutation(npool).reshape(nseq, L // P).astype(np.int32)
+        T = w["S"] + w["W"]
+        unit_bytes = nseq * Hkv * 97 * (L - w["W"] - w["S"]) + nseq * T * 2 * Hkv * D * 2 + nseq * Hq * D * 4
+        sample = f"{nseq} of {w['B']} batch rows, all {Hkv} kv heads, context {L}"
+        if ref is not None:
+            RKV = ref[1]
+            poolt, btt = torch.from_numpy(pool), torch.from_numpy(bt).long()
+            q = torch.randn(nseq, Hq, D).bfloat16().float()
+            ring = torch.randn(nseq, T, 2 * Hkv, D).bfloat16().float()
+
+            def step():
+                o = torch.empty(nseq, Hq, D)
+                for b in range(nseq):
+                    k, v = RKV.dequant_groups(poolt[btt[b]], D)               # [L, Hkv, D] in the original basis
+                    k = torch.cat([k.float()[w["S"]:L - w["W"]], ring[b, :, :Hkv]])
+                    v = torch.cat([v.float()[w["S"]:L - w["W"]], ring[b, :, Hkv:]])
+                    s = torch.einsum("hgd,thd->hgt", q[b].view(Hkv, G, D), k) * SCALE
+                    o[b] = torch.einsum("hgt,thd->hgd", torch.softmax(s, -1), v).reshape(Hq, D)
+                return o
+            kind, how = "reference", "the reference's PyTorch page parser (kivi.py dequant_groups) + fp32 einsum / softmax attention"
+        else:
+            qb = (rs.randn(nseq, Hq, D).astype(np.float32).view(np.uint32) >> 16).astype(np.uint16)
+            ringb = (rs.randn(nseq, T, 2 * Hkv, D).astype(np.float32).view(np.uint32) >> 16).astype(np.uint16)
+
+            def step():
+                return KO.decode_reference(qb, pool, bt, np.full(nseq, L - w["W"], np.int32), SCALE, w["S"], G, ring=ringb,
+                                           tail_len=np.full(nseq, T, np.int32), tail_idx=np.arange(nseq))
+            kind, how = "port", "float64 numpy restatement of the reference's page parser + attention (oracle/kivi_oracle.py)"
+        to_metric = lambda sec: unit_bytes / sec / 1e9  # noqa: E731
+    else:   # prefill: one request, 64 of its 512 new tokens, all heads, over the cached keys
+        from oracle import flagrot_oracle as O
+        Hkv, Hq, L, nq = w["Hkv"], w["Hq"], w["L"], 64
+        G = Hq // Hkv
+        npool = (L + w["new"]) // P
+        pool = rs.randint(0, 256, (npool, Hkv, O.chunk_bytes(4, P)), dtype=np.uint8)
+        pool[:, :, 128 * P:144 * P] = _scale_words(rs, (npool, Hkv, 8 * P)).view(np.uint8).reshape(npool, Hkv, 16 * P)
+        flops = 4.0 * 128 * Hq * nq * (L + (nq + 1) / 2)
+        sample = f"1 of {w['B']} requests, {nq} of {w['new']} new tokens, all {Hq} q heads, {L} cached keys"
+        q = torch.randn(nq, Hq, 128).bfloat16().float()
+        if ref is not None:
+            RK = ref[0]
+            poolt = torch.from_numpy(pool)
+
+            def step():
+                Kp, Vp = RK.dequant_cb_pages(poolt, P, "konlya", torch.float32)
+                k, v = Kp.reshape(-1, Hkv, 128)[:L + nq], Vp.reshape(-1, Hkv, 128)[:L + nq]
+                s = torch.einsum("qhgd,thd->hgqt", q.view(nq, Hkv, G, 128), k) * SCALE
+                vis = torch.arange(L + nq)[None, :] <= (L + torch.arange(nq))[:, None]
+                s = s.masked_fill(~vis[None, None], float("-inf"))
+                return torch.einsum("hgqt,thd->qhgd", torch.softmax(s, -1), v)
+            kind, how = "reference", "the reference's PyTorch page parser (kernels.py dequant_cb_pages) + masked fp32 attention"
+        else:
+            from oracle import mq_oracle as MO
+            bt_row = np.arange(npool, dtype=np.int32)
+
+            def step():
+                kk, vv = MO.request_cache(pool, bt_row, L + nq, 4, True)
+                return MO.attention(q.numpy(), kk, vv, L + np.arange(nq), 0, SCALE)
+            kind, how = "port", "float64 numpy restatement (oracle/mq_oracle.py)"
+        to_metric = lambda sec: flops / sec / 1e12  # noqa: E731
     times = []
     for i in range(warmup + steps):
         t0 = time.perf_counter()
-        C.decode_rows_fp32(q, pool, bt, lens, 1 / math.sqrt(128), w["nb"], P, True, list(range(nseq)), tail=ring, tail_len=tl,
-                           kv_start=w["S"])
+        step()
         if i >= warmup:
             times.append(time.perf_counter() - t0)
-    if not times:                                  # --cpu-steps 0: no CPU leg
+    if not times:
         return None, None, None
     sec = float(np.mean(times))
-    gbs = algorithmic_bytes(w, nseq) / sec / 1e9
-    cores = os.cpu_count() or 1
-    return gbs, sec, dict(value=gbs, unit="GB/s", cores=cores, kind="port",
-                          sample=f"{nseq} of {w['B']} batch rows, all {Hkv} kv heads, full context {L}; fp32 numpy "
-                                 f"dequantise + attention, {cores} threads")
+    val = to_metric(sec)
+    unit = "TFLOP/s" if w["path"] == "prefill" else "GB/s"
+    return val, sec, dict(value=val, unit=unit, cores=cores, kind=kind, sample=f"{sample}; {how}, {cores} threads")
 
 
 # ---------------------------------------------------------------------------------------------- main
@@ -326,32 +826,38 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours")
-    ap.add_argument("--workload", default="cfg2")
+    ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS))
     ap.add_argument("--nsplit", type=int, default=0, help="force the split count (0: the planner's choice)")
-    ap.add_argument("--ncopy", type=int, default=3)
-    ap.add_argument("--cpu-steps", type=int, default=3)
+    ap.add_argument("--ncopy", type=int, default=0, help="pool copies cycled (0: enough to exceed L2 several times)")
+    ap.add_argument("--cpu-steps", type=int, default=3, help="steps of the cpu_baseline leg (0: skip it)")
+    ap.add_argument("--sustain-s", type=float, default=0.5, help="seconds of untimed load before the timed steps, and the least "
+                                                                  "length of the kernel-only loop behind the roofline figure")
     ap.add_argument("--no-step-graph", action="store_true", help="resident step: separate launches from Python instead of a CUDA graph")
-    ap.add_argument("--graph", action="store_true", help="e2e: one CUDA graph per step (flagrot_releaser_b200.graphs.HostStep) "
-                                                         "instead of separate launches from Python; measured equal within noise")
+    ap.add_argument("--race", action="store_true", help="also time the reference's own sm_100a-capable kernel on the same pools (cfg4)")
     a = ap.parse_args()
-    a.warmup = max(a.warmup, 3) if a.impl == "ours" else a.warmup
     w = WORKLOADS[a.workload]
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
+    metric = "mq_prefill_attention_tflops" if w["path"] == "prefill" else "decode_attention_kv_gbps"
+    unit = "TFLOP/s" if w["path"] == "prefill" else "GB/s"
 
     if a.impl == "reference":
         if rank != 0:
             return
-        gbs, sec, cb = cpu_arm(w, max(1, min(a.steps, 5)), min(a.warmup, 1))
-        print(json.dumps({"impl": "reference", "metric": "decode_attention_kv_gbps", "value": gbs, "unit": "GB/s",
-                          "n_gpus": a.gpus, "steps": max(1, min(a.steps, 5)), "warmup": min(a.warmup, 1),
-                          "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-                          "dtype": "u8", "data": "synthetic", "config": {"workload": w["name"]},
-                          "cpu_baseline": cb, "gpu_launches": 0,
-                          "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
+        if w["path"] == "writers":
+            print(json.dumps({"impl": "reference", "unavailable": "the writers workload races GPU kernels; it has no CPU arm"}))
+            return
+        steps, warm = max(1, a.steps), max(0, a.warmup)
+        val, sec, cb = cpu_arm(a.workload, w, steps, warm)
+        print(json.dumps({"impl": "reference", "metric": metric, "value": val, "unit": unit, "n_gpus": a.gpus, "steps": steps,
+                          "warmup": warm, "ms_per_step": sec * 1e3, "higher_is_better": True,
+                          "scaling": "weak" if w["shard"] == "replica" else "strong", "vs_baseline": None,
+                          "dtype": "f32", "data": "synthetic", "config": {"workload": w["name"]}, "cpu_baseline": cb, "gpu_launches": 0,
+                          "e2e": {"value": val, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
         return
 
+    a.warmup = max(a.warmup, 3)
     dist = None
     if world > 1:
         import torch.distributed as dist_mod
@@ -359,83 +865,83 @@ def main():
         dist_mod.init_process_group("nccl", device_id=torch.device("cuda", local))
         dist = dist_mod
     else:
+        local = 0
         torch.cuda.set_device(0)
-    dev = torch.device("cuda", local if world > 1 else 0)
-    B = w["B"]                                          # weak scaling: every rank runs the full per-GPU batch
-    kvseq = w.get("shard") == "kvseq"
-    if kvseq:                                           # strong scaling: the pools shrink with the rank count; keep the cycled set > L2
-        local = B * kvseq_local_len(w["L"], w["W"], world) * w["Hkv"] * (144 if w["nb"] == 4 else 80)
-        a.ncopy = max(a.ncopy, -(-(192 << 20) // local))
-    st = make_state(w, B, dev, seed=1234 + rank, ncopy=a.ncopy, rank=rank, world=world)
-    plan(st, a.nsplit or None)
-    st["graphs"] = a.graph
-    sampler = ClockSampler(local if world > 1 else 0)
-    if rank == 0:
-        sampler.start()
-    if kvseq:
-        ms = timed(lambda i: step_kvseq(st, i, dist=dist), a.steps, a.warmup, dist)
-        ms_e2e = timed(lambda i: step_kvseq(st, i, e2e=True, dist=dist), a.steps, a.warmup, dist)
-    else:
-        if a.no_step_graph:
-            ms = timed(lambda i: step(st, i), a.steps, a.warmup, dist)
-        else:
-            # the resident step (append + decode) is replayed as one CUDA graph per pool copy: the same two kernels, one launch
-            # from Python, so that the figure does not depend on how fast the host thread of a rank issues launches
-            vg = []
-            for c in range(len(st["pools"])):
-                step(st, c)                                             # first calls set kernel attributes
-                torch.cuda.synchronize()
-                g = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(g):
-                    step(st, c)
-                vg.append(g)
-            ms = timed(lambda i: vg[i % len(vg)].replay(), a.steps, a.warmup, dist)
-        ms_e2e = timed(lambda i: step(st, i, e2e=True), a.steps, a.warmup, dist)
-    ms_dec = timed(lambda i: decode_only(st, i), a.steps, a.warmup, None)
+    dev = torch.device("cuda", local)
+
+    if w["path"] == "writers":
+        res = writers_race(dev)
+        if rank == 0:
+            print(json.dumps({"metric": "writer_us_per_call", "unit": "us", "config": {"workload": w["name"]}, "data": "synthetic",
+                              "writers": res}))
+        return
+
+    wl = {"decode": DecodeWorkload, "kivi": KiviWorkload, "prefill": PrefillWorkload}[w["path"]](w, rank, world, dev, a)
+    if getattr(wl, "kvseq", False):
+        wl.dist = dist
+    nc = wl.ncopy
+    # the resident step replayed as one CUDA graph per pool copy: the same launches, one call from Python, so that the figure
+    # does not depend on how fast the host thread of a rank issues launches (prefill allocates its partials per step: eager)
+    graphs = None
+    if not a.no_step_graph and w["path"] != "prefill":
+        try:
+            for c in range(nc):
+                wl.resident(c)
+            graphs = [graph_of(lambda c=c: wl.resident(c)) for c in range(nc)]
+        except Exception as e:                              # e.g. a collective that cannot be captured here
+            if rank == 0:
+                print(f"bench: step graph unavailable ({type(e).__name__}: {e}); separate launches", file=sys.stderr)
+            graphs = None
+            torch.cuda.synchronize()
+    wl.graphs = graphs
+    run_res = (lambda i: graphs[i % nc].replay()) if graphs is not None else (lambda i: wl.resident(i % nc))
+    sampler = ClockSampler(local).start() if rank == 0 else None
+    ms = timed(run_res, a.steps, a.warmup, dist, a.sustain_s)
     clocks = sampler.stop() if rank == 0 else None
-    status = st["K"].device_status()
+    ms_e2e = timed(lambda i: wl.e2e(i % nc), a.steps, a.warmup, dist, min(a.sustain_s, 0.2))
+    wl.resident(0)                                          # (prefill: the kernel-only loop reuses the staged q)
+    ms_burst = timed(lambda i: wl.kernel(i % nc), a.steps, a.warmup, None)
+    ms_k, n_k, clk_k = sustained(lambda i: wl.kernel(i % nc), ms_burst, a.sustain_s, local)
+    ms_long, n_long, _ = sustained(run_res, ms, a.sustain_s, local) if dist is None else (None, 0, None)
+    status = wl.status()
+    race = wl.race_reference() if (a.race and hasattr(wl, "race_reference")) else None
     if rank != 0:
         if dist is not None:
             dist.destroy_process_group()
         return
-    nbytes = algorithmic_bytes(w)
-    peak, which = peaks()
-    nloc = nbytes
-    if kvseq:                                           # bytes of this rank's decode launch (rank 0 carries the BF16 rows)
-        cell = 144 if w["nb"] == 4 else 80
-        nloc = nbytes - B * w["Hkv"] * cell * (w["L"] - w["W"] - w["S"]) + B * w["Hkv"] * cell * (st["Lloc"] - w["W"] - w["S"])
-    ach = nloc / (ms_dec * 1e-3) / 1e9
-    nwork = nbytes if kvseq else world * nbytes          # strong scaling: the job is one sequence
+    hbm, tf_burst, tf_sus, which = peaks()
+    scale = 1e12 if wl.bound == "tensor" else 1e9
+    peak = tf_sus if wl.bound == "tensor" else hbm
+    ach = wl.launch_units() / (ms_k * 1e-3) / scale
     traffic = None
     tf = ROOT / "profiles" / "traffic.json"
     if tf.exists():
         traffic = json.loads(tf.read_text()).get(a.workload)
+    h2d, d2h = wl.copies()
+    cfg = {"workload": w["name"], **wl.config(), "device_status": status,
+           "timing": f"{a.warmup} warm-up steps + {a.sustain_s} s of the same step untimed, then {a.steps} timed steps (CUDA events)"}
     line = {
-        "metric": "decode_attention_kv_gbps", "value": nwork / (ms * 1e-3) / 1e9, "unit": "GB/s", "n_gpus": world,
-        "steps": a.steps, "warmup": a.warmup, "ms_per_step": ms, "higher_is_better": True,
-        "scaling": "strong" if kvseq else "weak",
-        "vs_baseline": None, "dtype": "u8", "data": "synthetic",
-        "config": {"workload": w["name"], "batch_per_gpu": B, "nsplit": st["plan"][0], "chunk": st["plan"][1],
-                   "l2": f"{a.ncopy} distinct {st['pools'][0].numel() >> 20} MiB pools cycled "
-                         f"({a.ncopy * st['pools'][0].numel() >> 20} MiB in all, more than the 126 MB L2)",
-                   "parallelism": ((f"kv-sequence sharded x{world}, NCCL all-gather of (o, m, l) rows + LSE merge" if kvseq
-                                    else f"batch-sharded x{world}") if world > 1 else "single gpu"),
-                   "step": ("fr_cb_write (last rank) + fr_attn_partial + all-gather + merge" if kvseq
-                            else "fr_cb_write (T = batch) + fr_cb_attn" + ("" if a.no_step_graph else ", replayed as one CUDA graph")),
-                   "device_status": status},
-        "e2e": {"value": nwork / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s",
-                "h2d_bytes_per_step": int(st["q_host"].numel() * 2 + st["kv_host"].numel() * 2 + B * 8),
-                "d2h_bytes_per_step": int(st["out_host"].numel() * 2), "ms_per_step": ms_e2e,
-                "launch": ("separate launches from Python" if (not a.graph or kvseq) else
-                           "one CUDA graph per step: 3 host-to-device copies, writer, decode, copy back")},
-        "gpu_launches": (3 if kvseq else 2) * a.steps,   # append (keys + value rows, one launch), decode [, merge]
-        "roofline": {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak, "traffic": traffic,
-                     "kernel": "k_decode<4, key-only>" if w["nb"] == 4 else "k_decode<2, key-only>", "peak_source": which,
-                     "us_per_launch": ms_dec * 1e3, "algorithmic_bytes": nloc, "frac_of_8000": ach / 8000.0},
+        "metric": metric, "value": wl.job_units() / (ms * 1e-3) / scale, "unit": unit, "n_gpus": world, "steps": a.steps,
+        "warmup": a.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak" if w["shard"] == "replica" else "strong",
+        "vs_baseline": None, "dtype": "f16" if wl.bound == "tensor" else "u8", "data": "synthetic", "config": cfg,
+        "e2e": {"value": wl.job_units() / (ms_e2e * 1e-3) / scale, "unit": unit, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "ms_per_step": ms_e2e, "launch": "copies from Python, the step as one CUDA graph" if graphs is not None
+                else "separate launches from Python"},
+        "gpu_launches": wl.launches * a.steps,
+        "roofline": {"bound": wl.bound, "achieved": ach, "peak": peak, "unit": unit, "frac": ach / peak, "traffic": traffic,
+                     "kernel": wl.kernel_name, "peak_source": which + (" (sustained dense bf16)" if wl.bound == "tensor" else " (copy)"),
+                     "us_per_launch": ms_k * 1e3, "launches_timed": n_k, "algorithmic_units": wl.launch_units(),
+                     "us_per_launch_burst": ms_burst * 1e3, "clocks": clk_k,
+                     "us_x_sm_mhz": (ms_k * 1e3 * clk_k["sm_mhz"]) if clk_k and clk_k.get("sm_mhz") else None,
+                     **({"frac_of_8000": ach / 8000.0} if wl.bound == "hbm" else {"frac_of_burst_peak": ach / tf_burst})},
         "clocks": clocks,
     }
-    if world == 1:
-        _, _, cb = cpu_arm(w, a.cpu_steps, 1)
+    if ms_long is not None:
+        line["sustained"] = {"ms_per_step": ms_long, "steps": n_long, "value": wl.job_units() / (ms_long * 1e-3) / scale}
+    if race is not None:
+        line["reference_kernel"] = race
+    if world == 1 and a.cpu_steps > 0:
+        _, _, cb = cpu_arm(a.workload, w, a.cpu_steps, 1)
         line["cpu_baseline"] = cb
     print(json.dumps(line))
     if dist is not None:

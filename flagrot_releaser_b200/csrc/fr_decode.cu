@@ -778,7 +778,12 @@ __global__ void __launch_bounds__(128, MINB) k_decode(const DecodeParams p) {
     if (tok0 < lo || tok0 + BLK > c1) process(st, tok0, std::true_type{});
     else process(st, tok0, std::false_type{});
   }
-  if (!wait_ok && lane == 0) atomicExch(&g_status, __LINE__);
+  if (!wait_ok) {
+    if (lane == 0) atomicExch(&g_status, __LINE__);
+    // copies still in flight must not land in shared memory that the next CTA on this SM owns: one more bounded wait on the
+    // last use of every stage before the warp goes on to the epilogue (the output of this launch is to be discarded)
+    for (int n = max(0, nmine - ST); n < nmine; ++n) mbar_wait(mb0 + 8 * (n % ST), (n / ST) & 1);
+  }
 
   // ---- warp epilogue: fold, reduce over the column's lanes, remove the zero points, park in shared memory
   fold(1.f);

@@ -195,6 +195,7 @@ __global__ void __launch_bounds__(128) k_dyn_keys(const DynParams p, const RowPa
   }
   if (STAGED) __syncthreads();
   bool staged = !STAGED;
+  bool stage_lost = false;             // the staging wait ran out: the sums read C_q^T from global memory instead
   for (int t0 = blockIdx.y * TG; t0 < p.T; t0 += gridDim.y * TG) {
   const int ntok = min(TG, p.T - t0);
 
@@ -213,7 +214,7 @@ __global__ void __launch_bounds__(128) k_dyn_keys(const DynParams p, const RowPa
     if (!staged) {                     // first use of C_q^T: the copy has had the loads and the Hadamard above to arrive
       staged = true;
       if (tc5::mbar_wait(wsmem_u32(&ctbar), 0)) CT = cts;
-      else if (i == 0) atomicExch(&g_wstatus, __LINE__);
+      else { stage_lost = true; if (i == 0) atomicExch(&g_wstatus, __LINE__); }
     }
 #pragma unroll
     for (int k = 0; k < 32; ++k) {   // fully unrolled: the 32 loads do not depend on the sum chain and go out together
@@ -316,6 +317,9 @@ __global__ void __launch_bounds__(128) k_dyn_keys(const DynParams p, const RowPa
   }
   __syncthreads();                     // the next group of tokens reuses the shared arrays
   }
+  // a bulk copy that is still in flight must not land in shared memory the next CTA on this SM already owns: give it one
+  // more bounded wait before the CTA leaves (the status word is set; the step's pages are to be rewritten by the caller)
+  if (STAGED && stage_lost) tc5::mbar_wait(wsmem_u32(&ctbar), 0);
 }
 
 // ------------------------------------------------------------------------------------------------ launchers

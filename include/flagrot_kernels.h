@@ -118,7 +118,9 @@ int fr_device_status(void);
  * built into the library (held by every GPU that loads it, until exit); inputs and outputs are still the caller's.
  * Needs 256-rounded 4 * B * Hkv + 32 * parts bytes plus 2048 * parts bytes, parts = B * Hkv * (nsplit + 1); a larger
  * request returns -9 and prints the sizes to stderr.  The call allocates nothing.  The first call on a device looks up
- * the array's device address: make that call before any stream capture.  All calls share the array, so two calls that
+ * the array's device address (this is also when the driver loads the module and sets the 16 MiB aside: on a device whose
+ * memory is already full that first call answers -1): make that call before any stream capture.  The array is chosen
+ * by the CURRENT device, so the current device must be the one `stream` belongs to.  All calls share the array, so two calls that
  * overlap on the GPU (two streams, or two host threads) corrupt each other: serialise them.  Each call clears its
  * tickets first; nothing else in the array is assumed. */
 int fr_cb_attn_noalloc(const void* q, long long q_bs, const uint8_t* pool, const int* block_table, int bt_stride,

@@ -451,11 +451,13 @@ def gather_cache(Kp: np.ndarray, Vp: np.ndarray, bt: np.ndarray, Lmax: int, P: i
 
 
 def decode_reference(q_bits, pool, bt, lens, scale, bits, P, key_only, kmask=None, vmask=None, tail=None, tail_len=None,
-                     tail_idx=None, kv_start=0):
+                     tail_idx=None, kv_start=0, bf16_operands=False):
     """decode attention of one step over a quantised pool, the way the reference tests build their expectation
     (integrations/vllm_flagrot/tests/test_kernels.py:119-150): dequantise the pages, float64 attention, BF16 tail rows
     treated identically.  Static formats: q and the tail are rotated into the stored basis by the block masks and the
-    output is rotated back.  q_bits uint16 [B, Hq, 128]; tail uint16 [R, W, 2 Hkv, 128].  Returns float64 [B, Hq, 128]."""
+    output is rotated back.  q_bits uint16 [B, Hq, 128]; tail uint16 [R, W, 2 Hkv, 128].  Returns float64 [B, Hq, 128].
+    bf16_operands: the same attention with q, K and V rounded to bf16 first, still in the stored basis (the yardstick of
+    the reference's own tolerance, sdpa_err in integrations/vllm_flagrot/tests/test_kernels.py:59-63)."""
     q = bf16_bits_to_f32(q_bits).astype(np.float64)
     B, Hq, _ = q.shape
     Hkv = pool.shape[1]
@@ -463,6 +465,7 @@ def decode_reference(q_bits, pool, bt, lens, scale, bits, P, key_only, kmask=Non
     Kp, Vp = dequant_pool(pool, bits, P, key_only)
     Lmax = int(max(max(lens), 1))
     Kc, Vc = gather_cache(Kp, Vp, bt, Lmax, P)
+    rnd = (lambda a: bf16_round(a.astype(np.float32)).astype(np.float64)) if bf16_operands else (lambda a: a)
     tails = None
     if tail is not None:
         tf = bf16_bits_to_f32(tail).astype(np.float64)
@@ -472,10 +475,15 @@ def decode_reference(q_bits, pool, bt, lens, scale, bits, P, key_only, kmask=Non
             n = min(int(tail_len[b]), 256)
             tails.append((tf[r, :n, :Hkv], tf[r, :n, Hkv:]))
     if key_only or (kmask is None and vmask is None):
-        return attention(q, Kc, Vc, lens, scale, tails, kv_start)
+        with np.errstate(invalid="ignore", over="ignore"):
+            return attention(q, rnd(Kc), rnd(Vc), lens, scale, tails, kv_start)
     km = np.zeros((Hkv, NG), bool) if kmask is None else np.asarray(kmask).astype(bool)
     vm = np.zeros((Hkv, NG), bool) if vmask is None else np.asarray(vmask).astype(bool)
     qr = sel_rot64(q.reshape(B, Hkv, G, D).transpose(0, 2, 1, 3), km).transpose(0, 2, 1, 3).reshape(B, Hq, D)
     tr = None if tails is None else [(sel_rot64(t[0], km), sel_rot64(t[1], vm)) for t in tails]
-    o = attention(qr, Kc, Vc, lens, scale, tr, kv_start)
+    if bf16_operands:
+        qr = rnd(qr)
+        tr = None if tr is None else [(rnd(a), rnd(b)) for a, b in tr]
+    with np.errstate(invalid="ignore", over="ignore"):
+        o = attention(qr, rnd(Kc), rnd(Vc), lens, scale, tr, kv_start)
     return sel_rot64(o.reshape(B, Hkv, G, D).transpose(0, 2, 1, 3), vm).transpose(0, 2, 1, 3).reshape(B, Hq, D)

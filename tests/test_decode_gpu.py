@@ -85,6 +85,7 @@ def run_case(K, fmt, lens, win=None, bt_shared=False, seed=0, G=4, Hkv=8, kv_sta
               tail_idx=None if tail is None else tail_idx.numpy(), kv_start=kv_start)
     with np.errstate(invalid="ignore", over="ignore"):
         ref = O.decode_reference(bits(q), pool_np, bt.numpy(), lens, scale, nb, P, key_only, km, vm, **kw)
+        ref_bf = O.decode_reference(bits(q), pool_np, bt.numpy(), lens, scale, nb, P, key_only, km, vm, bf16_operands=True, **kw)
     Lmax = max(max(lens), 1)
     ns, ch = (K.plan_cb(B, Lmax, Hkv, P, fmt, nsplit, G=G) if key_only else K.plan_v2(B, Lmax, Hkv, P, nsplit, fmt=fmt, G=G))
     NT = -(-G // 4)
@@ -113,20 +114,27 @@ def run_case(K, fmt, lens, win=None, bt_shared=False, seed=0, G=4, Hkv=8, kv_sta
     assert int(ws.counter.abs().sum()) == 0, "merge tickets must be left at zero"
     valid = np.array([lens[b] > min(kv_start, lens[b]) or (tail is not None and int(tail_len[b]) > 0) for b in range(B)])
     if not valid.any():
-        return 0.0, 0.0, 0.0
+        return 0.0, 0.0, 0.0, 0.0
     err = np.abs(got[valid] - ref[valid])
     assert not np.isnan(got[valid]).any()
     mx = np.abs(ref[valid]).max()
     rel_rms = float(np.sqrt((err ** 2).mean()) / max(np.sqrt((ref[valid] ** 2).mean()), 1e-30))
     # error of the same attention with bf16-rounded operands (the reference's yardstick)
-    return float(err.max()), rel_rms, float(err.max() / mx)
+    sd = float(np.abs(ref_bf[valid] - ref[valid]).max())
+    WORST[fmt] = max(WORST.get(fmt, 0.0), float(err.max()))
+    return float(err.max()), rel_rms, float(err.max() / mx), sd / mx
+
+
+WORST: dict = {}     # largest max-abs error seen per format in this session (printed by the last test of the file)
 
 
 def check(res, what):
-    e, rr, rel = res
+    """the baseline's bounds and the reference's own criterion (test_kernels.py:170-173):
+    max|err| / max|ref| <= max(2 x the error of the same attention on bf16-rounded operands, 4e-3)"""
+    e, rr, rel, sd_rel = res
     assert e <= 2e-2, (what, "max-abs", e)
     assert rr <= 1e-2, (what, "relative RMS", rr)
-    assert rel <= 8e-3, (what, "max|err| / max|ref|", rel)
+    assert rel <= max(2 * sd_rel, 4e-3), (what, "max|err| / max|ref|", rel, "limit", max(2 * sd_rel, 4e-3))
 
 
 LENS = ([1], [77], [300, 4101, 17], [1000] * 5, [0, 513, 64])
@@ -139,7 +147,7 @@ def test_decode_lengths_and_windows(K, fmt, win):
         check(run_case(K, fmt, lens, win=win, seed=10 * i + (0 if win is None else win[0])), (fmt, lens, win))
 
 
-@pytest.mark.parametrize("fmt", ["int4a", "konlya", "konlya2"])
+@pytest.mark.parametrize("fmt", ["int4a", "int2a", "konlya", "konlya2"])
 def test_decode_long_sequence(K, fmt):
     check(run_case(K, fmt, [33000], win=(256, 7), seed=3, Hkv=2), (fmt, 33000))
     check(run_case(K, fmt, [33000], seed=4, Hkv=2, nsplit=3), (fmt, 33000, "nsplit 3"))

@@ -106,8 +106,9 @@ CASES = [  # (requests [(L, nq)], shift W, sink S, G, Hkv)
 ]
 
 
-def build_case(K, mode, reqs, W, G, Hkv, seed):
-    """pool written by the library's writers; returns device tensors + the oracle's float64 caches per request"""
+def build_case(K, mode, reqs, W, G, Hkv, seed, gentle=False):
+    """pool written by the library's writers; returns device tensors + the oracle's float64 caches per request.
+    gentle: Gaussian keys and queries without the outlier channels (scores stay within about +-6)."""
     kind, nb, key_only = KINDS[mode]
     g = torch.Generator().manual_seed(seed)
     lens = [max(L - W, 1) for L, _ in reqs]
@@ -124,7 +125,7 @@ def build_case(K, mode, reqs, W, G, Hkv, seed):
     qs, mq, row = [], [], 0
     for i, (L, nq) in enumerate(reqs):
         n = lens[i]
-        kv = rand_kv(n, Hkv, g).bfloat16().to(DEV)
+        kv = (torch.randn(n, 2 * Hkv, 128, generator=g) if gentle else rand_kv(n, Hkv, g)).bfloat16().to(DEV)
         pos = torch.arange(n)
         sl = (bt[i].long()[pos // 16] * 16 + pos % 16).to(DEV)
         if key_only:
@@ -133,7 +134,7 @@ def build_case(K, mode, reqs, W, G, Hkv, seed):
             K.w3_static_write(kv, sl, mask.to(DEV), hfull.to(DEV), pool, 16, fmt=kind)
         else:
             K.v2_write(kv, sl, torch.zeros(2 * Hkv, 4, dtype=torch.uint8, device=DEV), 32, pool, 16, fmt=kind)
-        qs.append(rand_q(nq, Hkv * G, g))
+        qs.append(torch.randn(nq, Hkv * G, 128, generator=g).bfloat16() if gentle else rand_q(nq, Hkv * G, g))
         mq.append((i, row, row + nq, L, L - nq))
         row += nq
     torch.cuda.synchronize()
@@ -181,6 +182,40 @@ def test_request_mixes(libs, mode, kernel):
             got = ob[:n, :Hkv * G * 128].view(n, Hkv * G, 128)
             assert torch.equal(got, o.to(torch.bfloat16)), "bf16 rows must be the rounded fp32 rows"
             assert int(ob[n:].abs().sum()) == 0 and int(ob[:, Hkv * G * 128:].abs().sum()) == 0
+
+
+@pytest.mark.parametrize("mode", ["rtn", "flags", "konlya", "rtn2", "konlya2"])
+@pytest.mark.parametrize("kernel", [1, 3])
+def test_request_mixes_stated_bound(libs, mode, kernel):
+    """the same request mixes on inputs whose scores stay moderate (no outlier channels in q . k): here the absolute
+    bound the baseline states, max-abs <= 2e-2 and relative RMS <= 1e-2, is asserted as it stands"""
+    K, MQ = libs
+    kind, nb, key_only = KINDS[mode]
+    todo = CASES[::2] if mode in ("rtn", "konlya") else CASES[1::4]
+    for ci, (reqs, W, S, G, Hkv) in enumerate(todo):
+        pool, bt, btd, qall, mq, mask, hfull = build_case(K, mode, reqs, W, G, Hkv, 900 + 50 * ci + len(mode), gentle=True)
+        kf = hfull[:Hkv].to(DEV) if hfull is not None else None
+        km = mask[:Hkv].to(DEV) if mask is not None else None
+        _, _, _, o, lse = run_mq(MQ, qall.to(DEV), pool, btd, mq, G, W, S, key_only, nb == 2, kernel, kf, km)
+        ro, rl = oracle_case(pool, bt, qall, mq, W, S, G, nb, key_only, mask, hfull)
+        compare(o.double().cpu().numpy(), lse.double().cpu().numpy(), ro, rl, (mode, kernel, reqs, W, S, G, "gentle"), harsh=False)
+
+
+@pytest.mark.parametrize("mode", ["konlya", "rtn"])
+def test_long_prefix_sampled_rows(libs, mode):
+    """one request of the long-context prefill shape (512 new tokens over 32 768 cached, window shift 128, 4 sinks, 2 kv
+    heads): 64 sampled query tokens x all heads against the float64 oracle, stated bound"""
+    K, MQ = libs
+    kind, nb, key_only = KINDS[mode]
+    L, nq, W, S, G, Hkv = 32768 + 512, 512, 128, 4, 4, 2
+    pool, bt, btd, qall, mq, mask, hfull = build_case(K, mode, [(L, nq)], W, G, Hkv, 77, gentle=True)
+    _, _, _, o, lse = run_mq(MQ, qall.to(DEV), pool, btd, mq, G, W, S, key_only, nb == 2, 3)
+    pick = np.sort(np.random.RandomState(5).choice(nq, 64, replace=False))
+    pick[0], pick[-1] = 0, nq - 1
+    kk, vv = MO.request_cache(pool.cpu().numpy(), bt[0].numpy(), L - W, nb, key_only)
+    q = O.bf16_bits_to_f32(bits(qall))[pick]
+    ro, rl = MO.attention(q, kk, vv, (L - nq) + pick, W, SCALE, kmin=S)
+    compare(o.double().cpu().numpy()[pick], lse.double().cpu().numpy()[:, pick], ro, rl, (mode, "long prefix"), harsh=False)
 
 
 def test_ext_rows_and_many_items(libs):
