@@ -215,7 +215,7 @@ class DecodeWorkload:
         # pool copies cycled: an explicit --ncopy, else enough distinct memory that no page survives in L2 between steps
         self.ncopy = a.ncopy if a.ncopy > 0 else min(64, max(1 if per_copy > (600 << 20) else 3, -(-(400 << 20) // per_copy)))
         self.build(seed=1234 + rank)
-        ns, ch = K.plan_cb(self.B, self.Lloc - w["W"], w["Hkv"], P, w["kind"], a.nsplit or None)
+        ns, ch = K.plan_cb(self.B, self.Lloc - w["W"], w["Hkv"], P, w["kind"], a.nsplit or None, tail=True)
         self.plan = (ns, ch)
         self.ws = K.Workspace(self.B, w["Hkv"], self.B * w["Hkv"] * (ns + 1), dev)
         self.dist = None
@@ -631,15 +631,22 @@ def writers_race(dev):
         row = {"ours": {}, "reference": {}}
         row["ours"]["fr_cb_write3 konlya"] = timed(lambda i: K.cb_write3(kv, slots, CT, co, None, None, "konlya", pool, P, split=False), 10, 3) * 1e3
         row["ours"]["fr_w3_static_write int4a"] = timed(lambda i: K.w3_static_write(kv, slots, mask, hfull, pool, P, fmt="int4a"), 10, 3) * 1e3
+        rf = reference_front()
         if w3.exists():
             R = ctypes.CDLL(str(w3))
             R.fr_cb_write3.argtypes = [PP, LL, PP, I, I, I, I, PP, PP, PP, PP, PP, I, PP, I, I, PP, PP]
             R.fr_w3_static_write.argtypes = [PP, LL, PP, I, I, I, PP, PP, I, PP, I, PP, PP]
             sg = K.sign_words()
-            # the reference's ranking tables (kernels.py w3_calib) are optional inputs of its kernel: nullptr = exact path
-            row["reference"]["fr_cb_write3 konlya"] = timed(lambda i: R.fr_cb_write3(
-                kv.data_ptr(), kv.stride(0), slots.data_ptr(), 0, T, Hkv, P, CT.data_ptr(), co.data_ptr(), None, None, sg, 10,
-                pool.data_ptr(), 1, 1, st(), None), 10, 3) * 1e3
+            if rf is not None:
+                # the reference's kernel reads its ranking tables (C1, beta) unconditionally: they come from the reference's own
+                # host routine w3_calib(C_q), the persistent-grid sizes from its w3_nchunk, exactly as its cb_write3 wrapper does
+                RK = rf[0]
+                C1, beta = RK.w3_calib(Cq)
+                C1, beta = C1.to(dev), beta.to(dev)
+                nk, nv = RK.w3_nchunk(Hkv, RK.W3_CTAS_PER_SM), RK.w3_nchunk(Hkv, RK.W3_VCTAS_PER_SM)
+                row["reference"]["fr_cb_write3 konlya"] = timed(lambda i: R.fr_cb_write3(
+                    kv.data_ptr(), kv.stride(0), slots.data_ptr(), 0, T, Hkv, P, CT.data_ptr(), co.data_ptr(), C1.data_ptr(),
+                    beta.data_ptr(), sg, 10, pool.data_ptr(), nk, nv, st(), None), 10, 3) * 1e3
             row["reference"]["fr_w3_static_write int4a"] = timed(lambda i: R.fr_w3_static_write(
                 kv.data_ptr(), kv.stride(0), slots.data_ptr(), T, Hkv, P, mask.data_ptr(), hfull.data_ptr(), 1, pool.data_ptr(), 0,
                 st(), None), 10, 3) * 1e3
@@ -669,19 +676,14 @@ def writers_race(dev):
 
 # ---------------------------------------------------------------------------------------------- the reference's CPU path
 def reference_front():
-    """the reference's own Python front ends (byte code built by oracle/build_ref.sh), or None"""
-    d = ROOT / "oracle" / "_ref" / "pyref"
-    if not (d / "vllm_flagrot" / "kernels.pyc").exists():
-        return None
-    os.environ.setdefault("FLAGROT_NO_REBUILD", "1")
-    sys.path.insert(0, str(d))
+    """the reference's own Python front ends kernels.py and kivi.py (byte code built by oracle/build_ref.sh), or None"""
     try:
-        import importlib
-        return importlib.import_module("vllm_flagrot.kernels"), importlib.import_module("vllm_flagrot.kivi")
+        from oracle import pyref
+        if not pyref.available():
+            return None
+        return pyref.load("kernels"), pyref.load("kivi")
     except Exception:
         return None
-    finally:
-        sys.path.remove(str(d))
 
 
 def _scale_words(rs, shape):

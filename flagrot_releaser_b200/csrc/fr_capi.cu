@@ -181,6 +181,17 @@ int fr_attn_partial(int fmt, const void* q, long long q_bs, const uint8_t* pool,
                      nullptr, 0, tail, tail_len, tail_idx, tail_bs, tail_ts, stream, kv_start, part);
 }
 
+int fr_dequant_pages(int fmt, const uint8_t* pool, const int* bt_row, int start, int n, int Hkv, int page, const uint8_t* kmask,
+                     const uint8_t* vmask, const uint8_t* kfull, const uint8_t* vfull, void* ok, void* ov, int out_fp32,
+                     void* stream) {
+  int nb, ko;
+  if (!fmt_info(fmt, nb, ko)) return -4;
+  if (page != 16 && page != 32) return -5;
+  if (start < 0 || Hkv <= 0) return -3;
+  return fr::dequant_pages_launch(nb, ko, pool, bt_row, start, n, Hkv, page, ko ? nullptr : kmask, ko ? nullptr : vmask,
+                                  ko ? nullptr : kfull, ko ? nullptr : vfull, ok, ov, out_fp32, static_cast<cudaStream_t>(stream));
+}
+
 int fr_device_status() {
   const int d = fr::decode_status();
   return d != 0 ? d : fr::writer_status();

@@ -22,8 +22,11 @@
 //     1 KB of shared memory per warp and multiplied with the V^T code bytes (again the stored bytes are the A
 //     fragment); integer accumulators are folded into fp32 whenever the running maximum or the normaliser moves;
 //   * the 4 warps merge in shared memory; splits merge through the caller's workspace, last arriving CTA wins.
+#include <algorithm>
 #include <cmath>
+#include <functional>
 #include <type_traits>
+#include <vector>
 
 #include "fr_common.cuh"
 #include "fr_kernels.h"
@@ -96,11 +99,12 @@ FR_DEVI float2 h2x2f(uint32_t v) {   // two packed fp16 -> two fp32
   return __half22float2(h);
 }
 
-template <int NB> struct DLay {
-  static constexpr int P = 16;
-  static constexpr int CHUNK = Lay<NB>::CELL * P;             // 2304 | 1280
-  static constexpr int PG1 = CHUNK + 64;                      // second page of a stage (64-byte skew: bank spread)
-  static constexpr int STAGE = ((PG1 + CHUNK + 127) / 128) * 128;
+template <int NB, int PG> struct DLay {
+  static_assert(PG == 16 || PG == 32, "pages of 16 or 32 tokens");
+  static constexpr int P = PG;                                // tokens per page; a warp step is always 32 tokens = 32 / P pages
+  static constexpr int CHUNK = Lay<NB>::CELL * P;             // 2304 | 1280 (P 16), 4608 | 2560 (P 32)
+  static constexpr int PG1 = CHUNK + 64;                      // P 16: second page of a stage (64-byte skew: bank spread)
+  static constexpr int STAGE = P == 16 ? ((PG1 + CHUNK + 127) / 128) * 128 : ((CHUNK + 127) / 128) * 128;
   static constexpr int V_OFF = Lay<NB>::CBY * P, KS_OFF = 2 * Lay<NB>::CBY * P, VS_OFF = KS_OFF + 8 * P;
   static constexpr uint32_t ZM = NB == 4 ? 0xFu : 0x3u;
   // the tensor path reads the code fields in place, i.e. scaled by a power of two:
@@ -110,13 +114,16 @@ template <int NB> struct DLay {
   static constexpr float VF0 = NB == 4 ? 1.0f / 16.0f : 1.0f / 4.0f, VF1 = NB == 4 ? 1.0f / 16.0f : 1.0f / 64.0f;
 };
 constexpr int PBUF_WORDS = 4 * 72;  // P' exchange per warp: [head] stride 72 words (18 x 16 B), [c][hl][e][j]
+constexpr int KTAB_BYTES = 1024;    // K scale table per warp: [group pair][32 tokens] x (2 scales fp32, sign = H32 flag | 2 zero points)
+constexpr float TAU = 2.0f;         // the softmax reference only moves when a score exceeds it by more than TAU (log2): p <= 4
 
-// shared memory map (dynamic): ring | pbuf | q table | sums | page ids | merge scratch (aliases the ring)
-template <int NB, int NV> struct SMap {
+// shared memory map (dynamic): ring | pbuf | K scale tables | q table | sums | page ids | merge scratch (aliases the ring)
+template <int NB, int NV, int PG = 16> struct SMap {
   static constexpr int RING = 0;
-  static constexpr int RING_BYTES = NWARP * ST * DLay<NB>::STAGE;
+  static constexpr int RING_BYTES = NWARP * ST * DLay<NB, PG>::STAGE;
   static constexpr int PBUF = RING + RING_BYTES;
-  static constexpr int QT = PBUF + NWARP * PBUF_WORDS * 4;             // int16 [NV][4][128]
+  static constexpr int KTAB = PBUF + NWARP * PBUF_WORDS * 4;           // per warp: [2 group pairs][32 tokens] x 16 bytes
+  static constexpr int QT = KTAB + NWARP * KTAB_BYTES;                 // int16 [NV][4][128]
   static constexpr int SQ = QT + NV * 4 * 128 * 2;                      // int [NV][4][4]
   static constexpr int SF = SQ + NV * 16 * 4;                           // float [4]
   static constexpr int PIDX = SF + 16;                                  // int [MAXPG]
@@ -232,15 +239,18 @@ FR_DEVI void cta_finish(const DecodeParams& p, float* scr, int b, int kvh, int q
   const int slot = ((b * p.Hkv + kvh) * NT + qt) * nsp + part;
   *reinterpret_cast<float4*>(p.opart + static_cast<size_t>(slot) * 512 + w * 128 + 4 * lane) = make_float4(x[0], x[1], x[2], x[3]);
   if (lane == 0) *reinterpret_cast<float2*>(p.mlpart + slot * 8 + 2 * w) = make_float2(M, l);
-  __threadfence();
+  // publish: the CTA barrier orders every thread's stores before thread 0, whose fence (cumulative at device scope) and
+  // ticket make them visible to the last arriver; that CTA's thread 0 fences again before the barrier that releases its
+  // readers, which load through L2 (__ldcg).  One fence pair per CTA instead of one per thread.
   __syncthreads();
   if (tid == 0) {
+    __threadfence();
     const int old = atomicAdd(p.counter + b * p.Hkv + kvh, 1);
     *last_flag = old == nparts * NT - 1;
+    if (*last_flag) __threadfence();
   }
   __syncthreads();
   if (!*last_flag) return;
-  __threadfence();
   for (int t = 0; t < NT; ++t) {
     float y[4], Mo, Lo;
     merge_parts(p.opart, p.mlpart, ((b * p.Hkv + kvh) * NT + t) * nsp, nparts, w, lane, y, Mo, Lo);
@@ -428,12 +438,20 @@ FR_DEVI void q_prologue(const DecodeParams& p, int b, int kvh, int qt, int16_t* 
   if (lane == 0) sf[g] = p.qscale * step;
 }
 
+// pieces of row b: the first rows_wide rows are cut into nsplit - 1 pieces of chunk_w tokens, the others into nsplit pieces
+// of chunk tokens (both cover the same nominal length nsplit * chunk); returns the piece size, `np` = pieces of this row
+FR_DEVI int row_pieces(const DecodeParams& p, int b, int& np) {
+  const bool wide = b < p.rows_wide;
+  np = wide ? p.nsplit - 1 : p.nsplit;
+  return wide ? p.chunk_w : p.chunk;
+}
+
 // ------------------------------------------------------------------------------------------------ the kernel
-template <int NB, bool KO>
+template <int NB, bool KO, int PG>
 __global__ void __launch_bounds__(128, MINB) k_decode(const DecodeParams p) {
   constexpr int NV = KO ? 3 : 1;
-  using L = DLay<NB>;
-  using S = SMap<NB, NV>;
+  using L = DLay<NB, PG>;
+  using S = SMap<NB, NV, PG>;
   extern __shared__ __align__(128) uint8_t smem[];
   __shared__ int last_flag;
   const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5, gid = lane >> 2, tig = lane & 3;
@@ -447,7 +465,9 @@ __global__ void __launch_bounds__(128, MINB) k_decode(const DecodeParams p) {
   const int has_tail = p.tail != nullptr;
   const int nsp = p.nsplit + has_tail;
   const int len = p.seq_lens[b];
-  const int ns_b = len > 0 ? min(p.nsplit, max(1, (len + p.chunk - 1) / p.chunk)) : 0;
+  int np_b;
+  const int chunk_b = row_pieces(p, b, np_b);
+  const int ns_b = len > 0 ? min(np_b, max(1, (len + chunk_b - 1) / chunk_b)) : 0;
   const int nparts = ns_b + has_tail;
   float* scr = reinterpret_cast<float*>(smem + S::RING);
   constexpr int WS = 4 * 128 + 8;
@@ -463,7 +483,7 @@ __global__ void __launch_bounds__(128, MINB) k_decode(const DecodeParams p) {
   }
   if (split >= ns_b) return;
 
-  const int c0 = split * p.chunk, c1 = min(len, c0 + p.chunk);
+  const int c0 = split * chunk_b, c1 = min(len, c0 + chunk_b);
   const int lo = max(c0, p.kv_start);                                 // first attended token
   const int ntok = c1 - c0, nblk = (ntok + BLK - 1) / BLK;
   int16_t* qtab = reinterpret_cast<int16_t*>(smem + S::QT);
@@ -494,11 +514,16 @@ __global__ void __launch_bounds__(128, MINB) k_decode(const DecodeParams p) {
   auto issue = [&](int n) {
     const int blk = w + NWARP * n, s = n % ST;
     const int t0 = blk * BLK;
-    const int npages = (ntok - t0) > L::P ? 2 : 1;
-    mbar_expect(mb0 + 8 * s, npages * L::CHUNK);
-    bulk_g2s(ring + s * L::STAGE, poolh + static_cast<size_t>(pidx[2 * blk]) * pstride, L::CHUNK, mb0 + 8 * s);
-    if (npages == 2)
-      bulk_g2s(ring + s * L::STAGE + L::PG1, poolh + static_cast<size_t>(pidx[2 * blk + 1]) * pstride, L::CHUNK, mb0 + 8 * s);
+    if constexpr (L::P == 16) {
+      const int npages = (ntok - t0) > L::P ? 2 : 1;
+      mbar_expect(mb0 + 8 * s, npages * L::CHUNK);
+      bulk_g2s(ring + s * L::STAGE, poolh + static_cast<size_t>(pidx[2 * blk]) * pstride, L::CHUNK, mb0 + 8 * s);
+      if (npages == 2)
+        bulk_g2s(ring + s * L::STAGE + L::PG1, poolh + static_cast<size_t>(pidx[2 * blk + 1]) * pstride, L::CHUNK, mb0 + 8 * s);
+    } else {                          // one 32-token page per step
+      mbar_expect(mb0 + 8 * s, L::CHUNK);
+      bulk_g2s(ring + s * L::STAGE, poolh + static_cast<size_t>(pidx[blk]) * pstride, L::CHUNK, mb0 + 8 * s);
+    }
   };
   if (lane == 0)
     for (int n = 0; n < ST - 1 && n < nmine; ++n) issue(n);
@@ -506,7 +531,7 @@ __global__ void __launch_bounds__(128, MINB) k_decode(const DecodeParams p) {
   // ---- per-thread constants
   // q B fragments: column gid = (head gid >> 1, part gid & 1: hi / lo); k = 4 tig .. (b0), 16 + 4 tig .. (b1)
   uint32_t qf[NV][4][2];
-  int SQ[NV][4];   // per-group sums of the fixed-point q, pre-multiplied by the code scaling of the group (KF)
+  int SQ[NV][4];   // MINUS the per-group sums of the fixed-point q, pre-multiplied by the code scaling of the group (KF)
   {
     const int hd = gid >> 1, lo_part = gid & 1;
 #pragma unroll
@@ -524,28 +549,31 @@ __global__ void __launch_bounds__(128, MINB) k_decode(const DecodeParams p) {
           }
           qf[c][j][r] = word;
         }
-        SQ[c][j] = sqs[(c * 4 + tig) * 4 + j] * L::kf(j);
+        SQ[c][j] = -sqs[(c * 4 + tig) * 4 + j] * L::kf(j);
       }
   }
-  const float sfac = NB == 4 ? sfs[tig] * L::kfinv(0) : sfs[tig];
+  const float sfac = NB == 4 ? sfs[tig] * L::kfinv(0) : sfs[tig];      // (INT2: the table's scales carry 1 / KF(j))
   // tokens of this lane inside a block: tau_i = 8 c + 2 i + e, (c, e) = (gid >> 1, gid & 1)
   const int tc = gid >> 1, te = gid & 1;
-  const uint32_t tpoff = (tc >> 1) * L::PG1;                           // page of the block holding the lane's tokens
-  const int tpos0 = 8 * (tc & 1) + te;                                 // position in the page of token i = 0 (+ 2 i)
+  const uint32_t tpoff = L::P == 16 ? (tc >> 1) * L::PG1 : 0;          // page of the block holding the lane's tokens
+  const int tpos0 = (L::P == 16 ? 8 * (tc & 1) : 8 * tc) + te;         // position in the page of token i = 0 (+ 2 i)
   // P' exchange buffer: [head] 72 words, [part hi / lo] 36 words, [chunk c] 8 words, [e] 4 words, [j]
   const uint32_t pbuf = smem_u32(smem + S::PBUF) + w * PBUF_WORDS * 4;
   const uint32_t pw_dst = pbuf + 4 * (tig * 72 + tc * 8 + te * 4);               // + 144 bytes for the lo part
   const uint32_t pw_src = pbuf + 4 * ((gid >> 1) * 72 + (gid & 1) * 36 + tig * 8);   // 8 words: [e][j]
+  // K scale table of the warp: lane = token writes, every lane reads its four tokens 8 tc + 2 i + te
+  const uint32_t ktab = smem_u32(smem + S::KTAB) + w * KTAB_BYTES;
+  const uint32_t kt_dst = ktab + 16 * lane, kt_src = ktab + 16 * (8 * tc + te);   // + 32 i; groups 2, 3: 512 bytes further
+  const uint32_t kt_ld = L::P == 16 ? (lane >> 4) * L::PG1 + L::KS_OFF + 8 * (lane & 15)
+                                    : L::KS_OFF + 8 * lane;                       // the token's four K scale words in a stage
   // byte offsets of this lane's shared-memory reads inside a stage
-  const uint32_t ks_off = tpoff + L::KS_OFF + 8 * tpos0;               // + 16 i
-  const uint32_t vs_off = tpoff + L::VS_OFF + 2 * (8 * (tc & 1) + 4 * te);   // + 2 P j
-  uint32_t kc_off[4];
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const int pos = tpos0 + 2 * i;
-    kc_off[i] = tpoff + (NB == 4 ? 64 * pos + 16 * tig : 32 * (pos ^ ((pos >> 1) & 2)) + 8 * tig);
-  }
-  const uint32_t vc_off = (tig >> 1) * L::PG1 + L::V_OFF + (NB == 4 ? 16 : 8) * (gid * (L::P / 8) + (tig & 1));
+  const uint32_t vs_off = tpoff + L::VS_OFF + 2 * (8 * (L::P == 16 ? (tc & 1) : tc) + 4 * te);   // + 2 P j
+  // K code row of token i: INT4 rows are 64 bytes apart in token order; INT2 rows are 32 bytes apart with physical row
+  // pos ^ ((pos >> 1) & 2), which for pos = tpos0 + 2 i just swaps i = 2 and i = 3: a compile-time offset per i either way
+  const uint32_t kc_base = tpoff + (NB == 4 ? 64 * tpos0 + 16 * tig : 32 * tpos0 + 8 * tig);
+  auto kc_row = [](int i) { return NB == 4 ? 128 * i : 64 * (i < 2 ? i : 5 - i); };
+  const uint32_t vc_off = L::P == 16 ? (tig >> 1) * L::PG1 + L::V_OFF + (NB == 4 ? 16 : 8) * (gid * (L::P / 8) + (tig & 1))
+                                     : L::V_OFF + (NB == 4 ? 16 : 8) * (gid * (L::P / 8) + tig);
 
   // ---- running state (head tig)
   float m_run = NEG_INF, l_run = 0.f;
@@ -571,8 +599,8 @@ __global__ void __launch_bounds__(128, MINB) k_decode(const DecodeParams p) {
     for (int a = 0; a < 2; ++a)
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
-        Of[a][c][0] = (Of[a][c][0] + static_cast<float>(Oi[a][c][0] * 256 + Oi[a][c][1]) * (inrm * L::VF0)) * alpha;
-        Of[a][c][1] = (Of[a][c][1] + static_cast<float>(Oi[a][c][2] * 256 + Oi[a][c][3]) * (inrm * L::VF1)) * alpha;
+        Of[a][c][0] = (Of[a][c][0] + fmaf(static_cast<float>(Oi[a][c][0]), 256.f, static_cast<float>(Oi[a][c][1])) * (inrm * L::VF0)) * alpha;
+        Of[a][c][1] = (Of[a][c][1] + fmaf(static_cast<float>(Oi[a][c][2]), 256.f, static_cast<float>(Oi[a][c][3])) * (inrm * L::VF1)) * alpha;
 #pragma unroll
         for (int k = 0; k < 4; ++k) Oi[a][c][k] = 0;
       }
@@ -587,18 +615,24 @@ __global__ void __launch_bounds__(128, MINB) k_decode(const DecodeParams p) {
   // one 32-token block of this warp from stage memory `st`; PARTIAL: some tokens lie outside [lo, c1)
   auto process = [&](const uint32_t st, int tok0, auto partial_tag) {
     constexpr bool PARTIAL = decltype(partial_tag)::value;
-    // ---- scale words of the lane's 4 tokens: K (token i: groups 0 1 | 2 3), V (group j: tokens 0 1 | 2 3)
-    uint32_t ksw[4][2], vsw[4][2];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const uint2 t = lds64(st + ks_off + 16 * i);
-      ksw[i][0] = t.x; ksw[i][1] = t.y;
+    // ---- K scales of the block, decoded once per (token, group): lane = token converts its four words to fp32 (bit 15, the
+    // H32 flag of a key-only page, simply becomes the sign) and splits off the zero points; the lanes that share a token
+    // then read the same 16 + 16 bytes instead of decoding the words four times over
+    {
+      const uint2 t = lds64(st + kt_ld);
+      float2 f01 = h2x2f(t.x), f23 = h2x2f(t.y);
+      if (NB == 2) { f01.x *= L::kfinv(0); f01.y *= L::kfinv(1); f23.x *= L::kfinv(2); f23.y *= L::kfinv(3); }
+      sts128(kt_dst, __float_as_uint(f01.x), __float_as_uint(f01.y), t.x & L::ZM, (t.x >> 16) & L::ZM);         // groups 0, 1
+      sts128(kt_dst + 512, __float_as_uint(f23.x), __float_as_uint(f23.y), t.y & L::ZM, (t.y >> 16) & L::ZM);   // groups 2, 3
     }
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const uint2 t = lds64(st + vs_off + 2 * L::P * j);
-      vsw[j][0] = t.x; vsw[j][1] = t.y;
+    // ---- V scale words of the lane's 4 tokens (group j: tokens 0 1 | 2 3); group 0 now (it carries the whole-head flags
+    // of the keys), groups 1 - 3 after the scores
+    uint32_t vsw[4][2];
+    {
+      const uint2 t = lds64(st + vs_off);
+      vsw[0][0] = t.x; vsw[0][1] = t.y;
     }
+    __syncwarp();
     bool valid[4] = {true, true, true, true};
     [[maybe_unused]] bool ffl[4] = {false, false, false, false};
     if constexpr (KO) {   // whole-head flag of the key of token i: bit 15 of its V group-0 word
@@ -612,46 +646,36 @@ __global__ void __launch_bounds__(128, MINB) k_decode(const DecodeParams p) {
         const int pos = tok0 + 8 * tc + 2 * i + te;
         valid[i] = pos >= lo && pos < c1;
       }
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {   // garbage beyond the sequence must not reach the normaliser / P'
-        if (!valid[0]) vsw[j][0] &= 0xFFFF0000u;
-        if (!valid[1]) vsw[j][0] &= 0x0000FFFFu;
-        if (!valid[2]) vsw[j][1] &= 0xFFFF0000u;
-        if (!valid[3]) vsw[j][1] &= 0x0000FFFFu;
-      }
     }
     // ---- QK
     float sc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
     for (int u = 0; u < 2; ++u) {
+      float skp[2][2];     // table entries of the current group pair, rows 2 u and 2 u + 1
+      int kzp[2][2];
       uint32_t ka[2][4];   // code words of rows i = 2 u, 2 u + 1: INT4 4 words (group j), INT2 2 words (groups 2 jp, 2 jp + 1)
 #pragma unroll
       for (int r = 0; r < 2; ++r) {
         if (NB == 4) {
-          const uint4 t = lds128(st + kc_off[2 * u + r]);
+          const uint4 t = lds128(st + kc_base + kc_row(2 * u + r));
           ka[r][0] = t.x; ka[r][1] = t.y; ka[r][2] = t.z; ka[r][3] = t.w;
         } else {
-          const uint2 t = lds64(st + kc_off[2 * u + r]);
+          const uint2 t = lds64(st + kc_base + kc_row(2 * u + r));
           ka[r][0] = t.x; ka[r][1] = t.y; ka[r][2] = 0; ka[r][3] = 0;
-        }
-      }
-      float skf[2][4];     // group scales of the two rows
-      int nz[2][4];        // minus the zero points
-#pragma unroll
-      for (int r = 0; r < 2; ++r) {
-        const int i = 2 * u + r;
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          const uint32_t wv = ksw[i][h];
-          const float2 f = h2x2f(KO ? (wv & 0x7FFF7FFFu) : wv);
-          skf[r][2 * h] = f.x; skf[r][2 * h + 1] = f.y;
-          const uint32_t zz = wv & (L::ZM | (L::ZM << 16));
-          nz[r][2 * h] = -static_cast<int>(zz & 0xFFFFu);
-          nz[r][2 * h + 1] = -static_cast<int>(zz >> 16);
         }
       }
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
+        // group scale (key-only pages: negative = stored as H32 x) and zero point of the two rows: one 128-bit load per row
+        // and group pair
+        if ((j & 1) == 0) {
+#pragma unroll
+          for (int r = 0; r < 2; ++r) {
+            const uint4 e = lds128(kt_src + 32 * (2 * u + r) + 512 * (j >> 1));
+            skp[r][0] = __uint_as_float(e.x); skp[r][1] = __uint_as_float(e.y);
+            kzp[r][0] = static_cast<int>(e.z); kzp[r][1] = static_cast<int>(e.w);
+          }
+        }
         // A fragments: the code fields in place, scaled by KF(j) = 16 (INT4) | 4, 64 (INT2): no right shifts
         uint32_t a0, a1, a2, a3;
         if (NB == 4) {
@@ -668,15 +692,31 @@ __global__ void __launch_bounds__(128, MINB) k_decode(const DecodeParams p) {
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
           const int i = 2 * u + r;
-          int val = acc[0][2 * r] * 128 + acc[0][2 * r + 1] + nz[r][j] * SQ[0][j];
+          const float sk = skp[r][j & 1];
+          const int z = kzp[r][j & 1];
+          int val = acc[0][2 * r] * 128 + acc[0][2 * r + 1] + z * SQ[0][j];
           if constexpr (KO) {
-            const int vh = acc[1][2 * r] * 128 + acc[1][2 * r + 1] + nz[r][j] * SQ[1][j];
-            const int vf = acc[2][2 * r] * 128 + acc[2][2 * r + 1] + nz[r][j] * SQ[2][j];
-            const bool hfl = (j & 1) ? static_cast<int>(ksw[i][j >> 1]) < 0 : (ksw[i][j >> 1] & 0x8000u) != 0;
+            const int vh = acc[1][2 * r] * 128 + acc[1][2 * r + 1] + z * SQ[1][j];
+            const int vf = acc[2][2 * r] * 128 + acc[2][2 * r + 1] + z * SQ[2][j];
+            const bool hfl = __float_as_int(sk) < 0;
             val = ffl[i] ? vf : (hfl ? vh : val);
           }
-          sc[i] = fmaf(NB == 4 ? skf[r][j] : skf[r][j] * L::kfinv(j), static_cast<float>(val), sc[i]);
+          sc[i] = fmaf(KO ? fabsf(sk) : sk, static_cast<float>(val), sc[i]);
         }
+      }
+    }
+#pragma unroll
+    for (int j = 1; j < 4; ++j) {
+      const uint2 t = lds64(st + vs_off + 2 * L::P * j);
+      vsw[j][0] = t.x; vsw[j][1] = t.y;
+    }
+    if constexpr (PARTIAL) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {   // garbage beyond the sequence must not reach the normaliser / P'
+        if (!valid[0]) vsw[j][0] &= 0xFFFF0000u;
+        if (!valid[1]) vsw[j][0] &= 0x0000FFFFu;
+        if (!valid[2]) vsw[j][1] &= 0xFFFF0000u;
+        if (!valid[3]) vsw[j][1] &= 0x0000FFFFu;
       }
     }
     // ---- softmax step (head tig; the 8 lanes of a column hold the block's 32 tokens)
@@ -693,12 +733,15 @@ __global__ void __launch_bounds__(128, MINB) k_decode(const DecodeParams p) {
     uint32_t vm = __vmaxu2(__vmaxu2(__vmaxu2(vsw[0][0], vsw[0][1]), __vmaxu2(vsw[1][0], vsw[1][1])),
                            __vmaxu2(__vmaxu2(vsw[2][0], vsw[2][1]), __vmaxu2(vsw[3][0], vsw[3][1])));
     vm = max(vm & 0xFFFFu, vm >> 16);
-    if (__any_sync(FULLMASK, bm > m_run || vm > nmax16)) {
+    // the reference m_run is lazy: it moves only when a score exceeds it by more than TAU, so p <= 2^TAU and the 16-bit P~
+    // keeps two bits of headroom; every move folds the integer accumulators into fp32.  Without a move they cannot
+    // overflow: a warp sees at most MAXPG / 8 = 64 blocks, each adding at most 32 x 240 x 128 < 2^20 to an accumulator
+    if (__any_sync(FULLMASK, bm > m_run + TAU || vm > nmax16)) {
       uint32_t wm = vm;
       wm = max(wm, __shfl_xor_sync(FULLMASK, wm, 4));
       wm = max(wm, __shfl_xor_sync(FULLMASK, wm, 8));
       wm = max(wm, __shfl_xor_sync(FULLMASK, wm, 16));
-      const float mn = fmaxf(m_run, bm);
+      const float mn = bm > m_run + TAU ? bm : m_run;                  // (m_run = -inf: any finite score moves it)
       const float alpha = m_run == NEG_INF ? 0.f : (mn == m_run ? 1.f : ex2(m_run - mn));
       fold(alpha);
       m_run = mn;
@@ -728,7 +771,7 @@ __global__ void __launch_bounds__(128, MINB) k_decode(const DecodeParams p) {
       hiw[j] = prmt(x01, x23, 0x7531u);
       low[j] = prmt(x01, x23, 0x6420u);
       // zero-point sums with the same integers the tensor path sees: bytes (z0, z1, z2, z3)
-      const uint32_t zb = prmt(vsw[j][0] & (L::ZM | (L::ZM << 16)), vsw[j][1] & (L::ZM | (L::ZM << 16)), 0x6420u);
+      const uint32_t zb = prmt(vsw[j][0], vsw[j][1], 0x6420u) & (L::ZM * 0x01010101u);
       Zi[j] = __dp2a_hi(x23, zb, __dp2a_lo(x01, zb, static_cast<unsigned>(Zi[j])));
     }
     sts128(pw_dst, hiw[0], hiw[1], hiw[2], hiw[3]);
@@ -806,17 +849,94 @@ __global__ void __launch_bounds__(128, MINB) k_decode(const DecodeParams p) {
       scr[w * WS + tig * 128 + d + 8] = Of[mm][ww][1] - Zf[j];
     }
   if (gid == 0) { scr[w * WS + 512 + tig] = m_run; scr[w * WS + 516 + tig] = l_run; }
-  cta_finish(p, scr, b, kvh, qt, NT, split, nparts, nsp, &last_flag);
+  {
+    // the slot arithmetic is redone from the block index and the length (read again) rather than kept in registers
+    // across the main loop
+    const int len_e = __ldcg(p.seq_lens + b);
+    int np_e;
+    const int chunk_e = row_pieces(p, b, np_e);
+    const int nsb_e = len_e > 0 ? min(np_e, max(1, (len_e + chunk_e - 1) / chunk_e)) : 0;
+    cta_finish(p, scr, static_cast<int>(blockIdx.z), static_cast<int>(blockIdx.x) / NT, static_cast<int>(blockIdx.x) % NT, NT,
+               static_cast<int>(blockIdx.y), nsb_e + has_tail, p.nsplit + has_tail, &last_flag);
+  }
 }
 
-template <int NB, bool KO> int launch_k(const DecodeParams& p, cudaStream_t st) {
+// ---- host: wave packing.  A launch whose equal CTAs do not fill a whole number of waves of the GPU's resident CTA slots
+// ends with a partly empty wave.  The kernel may cut the first `rows_wide` rows into nsplit - 1 wider pieces instead of
+// nsplit (same nominal length; the workspace has room for nsplit pieces of every row), which gives two CTA sizes; CTAs are
+// dispatched in grid order (rows ascending), i.e. the wide ones first, and a free slot takes the next CTA.  pack_rows
+// simulates that dispatch (cost of a CTA = its tokens + a fixed part, window CTAs last) for a few values of rows_wide and
+// returns the one with the earliest finish.  Pure host arithmetic, cached for the last shape seen.
+constexpr int PACK_C0 = 640;      // fixed cost of a page CTA in token equivalents (q staging, pipeline fill, merge)
+constexpr int PACK_CW = 900;      // a BF16 window CTA (<= 256 rows of 512 bytes per kv head) in token equivalents
+
+long long pack_finish(int B, int X, int p, int chunk, int chunk_w, int rows_wide, int slots, bool tail, std::vector<long long>& heap) {
+  heap.assign(static_cast<size_t>(slots), 0);                       // min-heap of slot finish times (all equal: a valid heap)
+  auto run = [&](long long n, long long cost) {
+    for (long long i = 0; i < n; ++i) {
+      std::pop_heap(heap.begin(), heap.end(), std::greater<long long>());
+      heap.back() += cost;
+      std::push_heap(heap.begin(), heap.end(), std::greater<long long>());
+    }
+  };
+  run(static_cast<long long>(rows_wide) * X * (p - 1), chunk_w + PACK_C0);
+  run(static_cast<long long>(B - rows_wide) * X * p, chunk + PACK_C0);
+  if (tail) run(static_cast<long long>(B) * X, PACK_CW);
+  return *std::max_element(heap.begin(), heap.end());
+}
+
+int pack_rows(int B, int X, int p, int chunk, int slots, bool tail, int& chunk_w) {
+  chunk_w = 0;
+  if (p < 2 || slots < 1) return 0;
+  const long long nominal = static_cast<long long>(p) * chunk;
+  if (nominal % (p - 1) != 0) return 0;
+  const long long cw = nominal / (p - 1);
+  if (cw % BLK != 0 || cw > MAXPG * 16) return 0;               // pieces start on a 32-token block
+  if (static_cast<long long>(B) * X * p > 200000) return 0;        // keep the simulation cheap; such launches have many waves anyway
+  static struct { int B, X, p, chunk, slots, tail, rows, cw; } memo = {-1, 0, 0, 0, 0, 0, 0, 0};
+  if (memo.B == B && memo.X == X && memo.p == p && memo.chunk == chunk && memo.slots == slots && memo.tail == static_cast<int>(tail)) {
+    chunk_w = memo.cw;
+    return memo.rows;
+  }
+  std::vector<long long> heap;
+  int best = 0;
+  long long best_t = pack_finish(B, X, p, chunk, static_cast<int>(cw), 0, slots, tail, heap);
+  const int step = B > 32 ? B / 16 : 1;
+  for (int pass = 0; pass < 2; ++pass) {
+    const int lo = pass == 0 ? step : std::max(1, best - step + 1), hi = pass == 0 ? B : std::min(B, best + step - 1);
+    const int st = pass == 0 ? step : 1;
+    int cand_best = best;
+    for (int r = lo; r <= hi; r += st) {
+      const long long t = pack_finish(B, X, p, chunk, static_cast<int>(cw), r, slots, tail, heap);
+      if (t < best_t) { best_t = t; cand_best = r; }
+    }
+    best = cand_best;
+    if (step == 1) break;
+  }
+  memo = {B, X, p, chunk, slots, static_cast<int>(tail), best, static_cast<int>(cw)};
+  chunk_w = static_cast<int>(cw);
+  return best;
+}
+
+template <int NB, bool KO, int PG> int launch_k(DecodeParams p, cudaStream_t st) {
   constexpr int NV = KO ? 3 : 1;
-  constexpr int smem = SMap<NB, NV>::TOTAL > TAILM_BYTES ? SMap<NB, NV>::TOTAL : TAILM_BYTES;
+  constexpr int smem = SMap<NB, NV, PG>::TOTAL > TAILM_BYTES ? SMap<NB, NV, PG>::TOTAL : TAILM_BYTES;
   static unsigned long long ready = 0;
-  if (!smem_limit_ready(k_decode<NB, KO>, smem, ready)) return -2;
+  if (!smem_limit_ready(k_decode<NB, KO, PG>, smem, ready)) return -2;
+  static int slots_of[64];                   // resident CTAs of this instantiation per device ordinal (0: not asked yet)
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -1;
+  if (slots_of[dev] == 0) {
+    int sms = 0, occ = 0;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, k_decode<NB, KO, PG>, 128, smem) != cudaSuccess || occ < 1)
+      return -2;
+    slots_of[dev] = sms * occ;
+  }
   const int NT = (p.G + 3) / 4;
+  p.rows_wide = pack_rows(p.B, p.Hkv * NT, p.nsplit, p.chunk, slots_of[dev], p.tail != nullptr, p.chunk_w);
   const dim3 grid(p.Hkv * NT, p.nsplit, p.B * (p.tail != nullptr ? 2 : 1));
-  k_decode<NB, KO><<<grid, 128, smem, st>>>(p);
+  k_decode<NB, KO, PG><<<grid, 128, smem, st>>>(p);
   return cudaPeekAtLastError() == cudaSuccess ? 0 : -1;
 }
 
@@ -824,27 +944,31 @@ template <int NB, bool KO> int launch_k(const DecodeParams& p, cudaStream_t st) 
 
 int decode_launch(const DecodeParams& p, cudaStream_t st) {
   if (p.B <= 0) return 0;
-  if (p.page != 16) return -5;
+  if (p.page != 16 && p.page != 32) return -5;
   if (p.chunk <= 0 || p.chunk % 64 != 0 || p.chunk > MAXPG * 16 || p.nsplit < 1) return -3;
-  if (p.nb == 4) return p.key_only ? launch_k<4, true>(p, st) : launch_k<4, false>(p, st);
-  return p.key_only ? launch_k<2, true>(p, st) : launch_k<2, false>(p, st);
+  if (p.page == 32) {
+    if (p.nb == 4) return p.key_only ? launch_k<4, true, 32>(p, st) : launch_k<4, false, 32>(p, st);
+    return p.key_only ? launch_k<2, true, 32>(p, st) : launch_k<2, false, 32>(p, st);
+  }
+  if (p.nb == 4) return p.key_only ? launch_k<4, true, 16>(p, st) : launch_k<4, false, 16>(p, st);
+  return p.key_only ? launch_k<2, true, 16>(p, st) : launch_k<2, false, 16>(p, st);
 }
 
 int decode_occupancy(int nb, int key_only) {
   int n = 0;
   cudaError_t e;
   if (nb == 4 && key_only) {
-    cudaFuncSetAttribute(k_decode<4, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMap<4, 3>::TOTAL);
-    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, k_decode<4, true>, 128, SMap<4, 3>::TOTAL);
+    cudaFuncSetAttribute(k_decode<4, true, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMap<4, 3>::TOTAL);
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, k_decode<4, true, 16>, 128, SMap<4, 3>::TOTAL);
   } else if (nb == 4) {
-    cudaFuncSetAttribute(k_decode<4, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMap<4, 1>::TOTAL);
-    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, k_decode<4, false>, 128, SMap<4, 1>::TOTAL);
+    cudaFuncSetAttribute(k_decode<4, false, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMap<4, 1>::TOTAL);
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, k_decode<4, false, 16>, 128, SMap<4, 1>::TOTAL);
   } else if (key_only) {
-    cudaFuncSetAttribute(k_decode<2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMap<2, 3>::TOTAL);
-    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, k_decode<2, true>, 128, SMap<2, 3>::TOTAL);
+    cudaFuncSetAttribute(k_decode<2, true, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMap<2, 3>::TOTAL);
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, k_decode<2, true, 16>, 128, SMap<2, 3>::TOTAL);
   } else {
-    cudaFuncSetAttribute(k_decode<2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMap<2, 1>::TOTAL);
-    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, k_decode<2, false>, 128, SMap<2, 1>::TOTAL);
+    cudaFuncSetAttribute(k_decode<2, false, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMap<2, 1>::TOTAL);
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, k_decode<2, false, 16>, 128, SMap<2, 1>::TOTAL);
   }
   return e == cudaSuccess ? n : 0;
 }

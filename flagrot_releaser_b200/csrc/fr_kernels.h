@@ -14,6 +14,11 @@ int rows_launch(int nb, const void* kv, long long kv_ts, const long long* slots,
 int dyn_keys_launch(int nb, const void* kv, long long kv_ts, const long long* slots, int slot_ph, int T, int Hkv, int page,
                     const float* CT, const float* kmu, uint8_t* pool, cudaStream_t st, int with_values = 0);
 
+// positions [start, n) of one request's pages -> K / V rows in the original basis (fr_dequant.cu)
+int dequant_pages_launch(int nb, int key_only, const uint8_t* pool, const int* bt_row, int start, int n, int Hkv, int page,
+                         const uint8_t* kmask, const uint8_t* vmask, const uint8_t* kfull, const uint8_t* vfull, void* ok, void* ov,
+                         int fp32, cudaStream_t st);
+
 // paged decode attention (fr_decode.cu)
 struct DecodeParams {
   const void* q; long long q_bs;             // bf16 [B, G * Hkv, 128], row stride in elements
@@ -31,6 +36,7 @@ struct DecodeParams {
   int nb;                                    // code bits 4 | 2
   int key_only;                              // 1: per-token flags in the scale sign bits (konlya / konlya2)
   float* part_out;                           // optional: unmerged (m, l, o) of the whole row (extension entry)
+  int rows_wide, chunk_w;                    // set by decode_launch: rows [0, rows_wide) use nsplit - 1 pieces of chunk_w tokens
 };
 int decode_launch(const DecodeParams& p, cudaStream_t st);
 int decode_occupancy(int nb, int key_only);

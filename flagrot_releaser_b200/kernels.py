@@ -33,6 +33,7 @@ STAGES = 3
 MAX_CHUNK, MAX_SPLITS = 8192, 512
 # split planner constants for B200 (tokens-equivalent fixed cost per CTA, per merged part)
 PLAN_C0, PLAN_C1 = 640, 6
+PLAN_CW = 900              # a BF16 window CTA in token equivalents
 
 
 def _lib_path() -> Path:
@@ -73,9 +74,11 @@ def lib():
     L.fr_cb_attn_noalloc.argtypes = [P, LL, P, P, I, P, I, I, I, I, I, F, I, P, LL, P, P, P, LL, LL, P, I]
     L.fr_attn_partial.argtypes = [I, P, LL, P, P, I, P, I, I, I, I, I, F, P, P, P, P, P, P, P, P, P, LL, LL, P, I, I]
     L.fr_merge_partials.argtypes = [P, I, I, P, I, P]
+    L.fr_dequant_pages.argtypes = [I, P, P, I, I, I, I, P, P, P, P, P, P, I, P]
     for n in ("fr_v2_attn", "fr_v2_write", "fr_v2_occupancy", "fr_v2_chunk_bytes", "fr_cb_write", "fr_cb_attn",
               "fr_cb_occupancy", "fr_cb_chunk_bytes", "fr_cb_nsg", "fr_head_fwht", "fr_cb_write3",
-              "fr_w3_static_write", "fr_cb_write_smem", "fr_attn_partial", "fr_device_status", "fr_cb_attn_noalloc", "fr_merge_partials"):
+              "fr_w3_static_write", "fr_cb_write_smem", "fr_attn_partial", "fr_device_status", "fr_cb_attn_noalloc", "fr_merge_partials",
+              "fr_dequant_pages"):
         getattr(L, n).restype = I
     _LIB = L
     return L
@@ -152,38 +155,102 @@ def _slots_per_gpu(key, occ_fn) -> int:
     return _OCC[key] * _NUM_SMS
 
 
-def plan_splits(B: int, Lmax: int, ctas_per_row: int, slots: int, nsplit=None, gran: int = 64):
-    """(nsplit, chunk): chunk a multiple of 64 tokens, <= 8192, <= 512 splits.  Cost of a plan = resident waves of
-    B * ctas_per_row * nsplit CTAs on `slots` CTA slots, each wave costing chunk + C0 tokens, plus C1 per merged part.
-    Pure host arithmetic (usable without a GPU)."""
+def _dispatch_finish(classes, slots: int) -> int:
+    """finish time of `slots` CTA slots that take CTAs in the given order, a freed slot always taking the next CTA:
+    classes = [(count, cost), ...].  Slots with equal load are kept as groups, so the cost is per class, not per CTA."""
+    groups = [[0, slots]]                                    # [load, number of slots], ascending load
+    for n, c in classes:
+        while n > 0:
+            l0, k0 = groups[0]
+            if len(groups) > 1:
+                t = max(1, -(-(groups[1][0] - l0) // c))     # CTAs each slot of the lowest group takes before the next group is lower
+            else:
+                t = max(1, -(-n // k0))
+            if n >= k0 * t:
+                groups[0][0] = l0 + t * c
+                n -= k0 * t
+            else:
+                q, rem = divmod(n, k0)
+                groups[0] = [l0 + q * c, k0 - rem]
+                if rem:
+                    groups.append([l0 + (q + 1) * c, rem])
+                n = 0
+            groups.sort()
+            merged = []
+            for g in groups:                                 # equal loads become one group again
+                if g[1] <= 0:
+                    continue
+                if merged and merged[-1][0] == g[0]:
+                    merged[-1][1] += g[1]
+                else:
+                    merged.append(g)
+            groups = merged
+    return max(g[0] for g in groups)
+
+
+def packed_cost(B: int, ctas_per_row: int, nse: int, chunk: int, slots: int, tail: bool = False, Lmax: int | None = None):
+    """(finish time in token equivalents, rows_wide) of a launch with nse pieces of `chunk` tokens per row (rows of Lmax
+    tokens: the last piece is shorter) when the library may cut the first rows_wide rows into nse - 1 wider pieces (what
+    decode_launch does; csrc/fr_decode.cu pack_rows): wide CTAs first, then the narrow ones, the BF16 window CTAs last."""
+    Lmax = nse * chunk if Lmax is None else Lmax
+
+    def pieces(rows, n, size):
+        last = Lmax - (n - 1) * size
+        cl = [(rows * ctas_per_row * (n - 1), size + PLAN_C0)] if n > 1 else []
+        return cl + [(rows * ctas_per_row, max(last, 1) + PLAN_C0)]
+
+    def finish(r, cw):
+        cl = (pieces(r, nse - 1, cw) if r else []) + (pieces(B - r, nse, chunk) if B - r else [])
+        if tail:
+            cl.append((B * ctas_per_row, PLAN_CW))
+        return _dispatch_finish(cl, slots)
+    best = (finish(0, 0), 0)
+    if nse >= 2 and (nse * chunk) % (nse - 1) == 0:
+        cw = nse * chunk // (nse - 1)
+        if cw % 32 == 0 and cw <= MAX_CHUNK:
+            step = max(1, B // 16)
+            for r in sorted(set(list(range(step, B + 1, step)) + [B])):
+                best = min(best, (finish(r, cw), r))
+            for r in range(max(1, best[1] - step + 1), min(B, best[1] + step - 1) + 1):
+                best = min(best, (finish(r, cw), r))
+    return best
+
+
+def plan_splits(B: int, Lmax: int, ctas_per_row: int, slots: int, nsplit=None, gran: int = 64, tail: bool = False):
+    """(nsplit, chunk): chunk a multiple of 64 tokens, <= 8192, <= 512 splits.  Cost of a plan = the finish time of its CTAs
+    dispatched over `slots` resident CTA slots (packed_cost: a CTA costs its tokens + C0, the library may widen the pieces
+    of the first rows so that the last wave is full) plus C1 per merged part.  Pure host arithmetic (usable without a GPU)."""
     Lmax = max(1, int(Lmax))
     if nsplit is not None:
         chunk = min(MAX_CHUNK, math.ceil(Lmax / nsplit / gran) * gran)
         return math.ceil(Lmax / chunk), chunk
     best = None
-    for ns in range(max(1, math.ceil(Lmax / MAX_CHUNK)), min(MAX_SPLITS, math.ceil(Lmax / gran)) + 1):
-        chunk = math.ceil(Lmax / ns / gran) * gran
-        if chunk > MAX_CHUNK:
-            continue
-        nse = math.ceil(Lmax / chunk)
-        if best is not None and nse == best[1]:
-            continue
-        cost = math.ceil(B * ctas_per_row * nse / slots) * (chunk + PLAN_C0) + (PLAN_C1 * nse if nse > 1 else 0)
-        if best is None or cost < best[0] - 1e-9:
-            best = (cost, nse, chunk)
+    ns_hi = min(MAX_SPLITS, math.ceil(Lmax / gran))
+    if B * ctas_per_row >= slots:                            # several CTAs per slot already: a handful of splits is all balance needs
+        ns_hi = min(ns_hi, max(1, math.ceil(Lmax / MAX_CHUNK)) + 8)
+    for ns in range(max(1, math.ceil(Lmax / MAX_CHUNK)), ns_hi + 1):
+        for g in ((gran, gran * max(1, ns - 1)) if ns > 2 else (gran,)):         # also a chunk whose widened form is block-aligned
+            chunk = math.ceil(Lmax / ns / g) * g
+            if chunk > MAX_CHUNK:
+                continue
+            nse = math.ceil(Lmax / chunk)
+            cost = packed_cost(B, ctas_per_row, nse, chunk, slots, tail, Lmax)[0] + (PLAN_C1 * nse if nse > 1 else 0)
+            if best is None or cost < best[0] - 1e-9:
+                best = (cost, nse, chunk)
     return best[1], best[2]
 
 
-def plan_v2(B, Lmax, Hkv, page, nsplit=None, fmt="int4a", G=4, Dh=128):
+def plan_v2(B, Lmax, Hkv, page, nsplit=None, fmt="int4a", G=4, Dh=128, tail=False):
+    """tail: the launch also carries one BF16 window CTA per (row, kv head, q tile) (they run last and fill the final wave)."""
     s = _slots_per_gpu(("v2", fmt), lambda: lib().fr_v2_occupancy(V2_FMT[fmt], v2_variant(fmt, G, Dh), STAGES, page))
-    return plan_splits(B, Lmax, Hkv * -(-G // 4), s, nsplit, max(64, page))
+    return plan_splits(B, Lmax, Hkv * -(-G // 4), s, nsplit, max(64, page), tail)
 
 
-def plan_cb(B, Lmax, Hkv, page, kind, nsplit=None, G=4, Dh=128):
+def plan_cb(B, Lmax, Hkv, page, kind, nsplit=None, G=4, Dh=128, tail=False):
     if G != 4 or Dh != 128:
-        return plan_v2(B, Lmax, Hkv, page, nsplit, fmt=kind, G=G, Dh=Dh)
+        return plan_v2(B, Lmax, Hkv, page, nsplit, fmt=kind, G=G, Dh=Dh, tail=tail)
     s = _slots_per_gpu(("cb", kind), lambda: lib().fr_cb_occupancy(CB_KINDS[kind], 0, STAGES, page))
-    return plan_splits(B, Lmax, Hkv, s, nsplit, max(64, page))
+    return plan_splits(B, Lmax, Hkv, s, nsplit, max(64, page), tail)
 
 
 class Workspace:
@@ -404,6 +471,22 @@ def merge_partials_into(parts: torch.Tensor, out: torch.Tensor):
     _check(lib().fr_merge_partials(parts.data_ptr(), R, B * Hq, out.data_ptr(), int(out.dtype == torch.float32), _stream()),
            "fr_merge_partials")
     return out
+
+
+def dequant_pages(pool, bt_row, start, n, fmt, page=16, dtype=torch.bfloat16, kmask=None, vmask=None, kfull=None, vfull=None):
+    """K, V [n - start, Hkv, 128] (bf16 | fp32) of positions [start, n) of the request with block-table row bt_row, in the
+    original basis: the CUDA form of the "fa" prefill path's page dequantisation (reference backend.py:1744-1789).  Key-only
+    kinds read the per-token flags from the pages; static formats take the layer's block masks [Hkv, 4] and whole-head flags
+    [Hkv] (uint8)."""
+    Hkv = pool.shape[1]
+    assert bt_row.dtype == torch.int32 and bt_row.is_contiguous() and dtype in (torch.bfloat16, torch.float32)
+    k = torch.empty(max(n - start, 0), Hkv, D, dtype=dtype, device=pool.device)
+    v = torch.empty_like(k)
+    if n > start:
+        _check(lib().fr_dequant_pages(V2_FMT[fmt], pool.data_ptr(), bt_row.data_ptr(), int(start), int(n), Hkv, page, _ptr(kmask),
+                                      _ptr(vmask), _ptr(kfull), _ptr(vfull), k.data_ptr(), v.data_ptr(),
+                                      int(dtype == torch.float32), _stream()), "fr_dequant_pages")
+    return k, v
 
 
 def device_status() -> int:

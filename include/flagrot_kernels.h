@@ -109,6 +109,16 @@ int fr_attn_partial(int fmt, const void* q, long long q_bs, const uint8_t* pool,
  * [rows, 128] bf16 (or fp32 when out_fp32).  o = sum_r w_r l_r o_r / sum_r w_r l_r, w_r = 2^(m_r - max m). */
 int fr_merge_partials(const float* parts, int R, int rows, void* out, int out_fp32, void* stream);
 
+/* No counterpart in the reference's C ABI: the reference does this step of its "fa" prefill path in PyTorch
+ * (vllm_flagrot/attention/backend.py:1744-1789, kernels.py dequant_cb_pages / dequant_v2_pages + unrotate_cached).
+ * Positions [start, n) of the request whose block-table row is bt_row -> ok / ov [n - start, Hkv, 128] (bf16, or fp32 when
+ * out_fp32) in the ORIGINAL basis.  fmt as fr_v2_attn (5 int4a, 7 konlya, 8 int2a, 9 konlya2).  Key-only formats take the
+ * per-token flags from the pages; static formats take kmask / vmask uint8 [Hkv, 4] (block flags) and kfull / vfull uint8
+ * [Hkv] (whole-head flags: stored as bf16(H128 x / 16)), any of which may be null. */
+int fr_dequant_pages(int fmt, const uint8_t* pool, const int* bt_row, int start, int n, int Hkv, int page, const uint8_t* kmask,
+                     const uint8_t* vmask, const uint8_t* kfull, const uint8_t* vfull, void* ok, void* ov, int out_fp32,
+                     void* stream);
+
 /* 0, or the source line of a bounded device-side wait that gave up (sticky; synchronises the device). */
 int fr_device_status(void);
 

@@ -4,10 +4,10 @@
 #   libflagrot_w3ref.so    kernels/csrc/attn_cb_write3.cu + integrations/vllm_flagrot/csrc/flagrot_capi.cu
 #                          (+ ref_link_stubs.cu for the symbols of the wgmma translation units)
 #   libflagrot_kivi_ref.so integrations/vllm_flagrot/csrc/kivi.cu
-#   pyref/vllm_flagrot/*.pyc  byte code of the reference's three ctypes front ends (kernels.py, kivi.py, prefill_mq.py) and
-#                          the package __init__, compiled by py_compile from the sources where they lie: the boundary test
-#                          loads this repository's libraries through them, and bench.py --impl reference times their
-#                          PyTorch page parser + fp32 attention on the host cores
+#   pyref/*.bytecode       byte code of the reference's three ctypes front ends (kernels.py, kivi.py, prefill_mq.py),
+#                          compiled by py_compile from the sources where they lie and loaded by oracle/pyref.py: the
+#                          boundary test loads this repository's libraries through them, and bench.py --impl reference
+#                          times their PyTorch page parser + fp32 attention on the host cores
 # They are byte-for-byte GPU checkers for the writers / the KIVI library and the kernels to beat.  Test infrastructure:
 # the shipped libraries never load them.  Skips quietly when the reference tree is absent (the GPU box uses the
 # prebuilt files).
@@ -36,13 +36,13 @@ if newer "$OUT/libflagrot_kivi_ref.so" "$REF/integrations/vllm_flagrot/csrc/kivi
   "$NVCC" -shared "${ARCH[@]}" -cudart static -o "$OUT/libflagrot_kivi_ref.so" "$TMP/kivi.o"
   rm -rf "$TMP"
 fi
-PYREF="$OUT/pyref/vllm_flagrot"
+PYREF="$OUT/pyref"
 PYSRC="$REF/integrations/vllm_flagrot/vllm_flagrot"
-if newer "$PYREF/kernels.pyc" "$PYSRC/kernels.py" "$PYSRC/kivi.py" "$PYSRC/prefill_mq.py" "$PYSRC/__init__.py"; then
+if newer "$PYREF/kernels.bytecode" "$PYSRC/kernels.py" "$PYSRC/kivi.py" "$PYSRC/prefill_mq.py"; then
   mkdir -p "$PYREF"
-  for m in __init__ kernels kivi prefill_mq; do
+  for m in kernels kivi prefill_mq; do
     python -c "import py_compile, sys; py_compile.compile(sys.argv[1], cfile=sys.argv[2], dfile='vllm_flagrot/' + sys.argv[3] + '.py', doraise=True)" \
-      "$PYSRC/$m.py" "$PYREF/$m.pyc" "$m"
+      "$PYSRC/$m.py" "$PYREF/$m.bytecode" "$m"
   done
 fi
 ls -la "$OUT" "$PYREF"

@@ -29,7 +29,7 @@ def K():
     return kernels
 
 
-def alloc(lens, num_pages, g):
+def alloc(lens, num_pages, g, P=P):
     need = [(n + P - 1) // P for n in lens]
     ids = torch.randperm(num_pages, generator=g)[:sum(need)]
     bt = torch.zeros(len(lens), max(max(need), 1), dtype=torch.int32)
@@ -40,14 +40,14 @@ def alloc(lens, num_pages, g):
     return bt
 
 
-def run_case(K, fmt, lens, win=None, bt_shared=False, seed=0, G=4, Hkv=8, kv_start=0, nsplit=None, partial=False):
+def run_case(K, fmt, lens, win=None, bt_shared=False, seed=0, G=4, Hkv=8, kv_start=0, nsplit=None, partial=False, P=P):
     nb, key_only = FMT[fmt]
     g = torch.Generator().manual_seed(seed)
     B, Hq = len(lens), G * Hkv
     num_pages = (sum((n + P - 1) // P for n in lens) if not bt_shared else (max(lens) + P - 1) // P) + 7
     chunk_b = K.v2_chunk_bytes(P, 128, fmt)
     pool = torch.randint(0, 256, (num_pages, Hkv, chunk_b), dtype=torch.uint8, generator=g).to(DEV)   # garbage pool
-    bt = alloc(lens if not bt_shared else [max(lens)], num_pages, g)
+    bt = alloc(lens if not bt_shared else [max(lens)], num_pages, g, P)
     mask = (torch.rand(2 * Hkv, 4, generator=g) < 0.5).to(torch.uint8)
     Cq, co = calib(Hkv, g)
     CT = Cq.transpose(1, 2).contiguous().to(DEV)
@@ -87,7 +87,8 @@ def run_case(K, fmt, lens, win=None, bt_shared=False, seed=0, G=4, Hkv=8, kv_sta
         ref = O.decode_reference(bits(q), pool_np, bt.numpy(), lens, scale, nb, P, key_only, km, vm, **kw)
         ref_bf = O.decode_reference(bits(q), pool_np, bt.numpy(), lens, scale, nb, P, key_only, km, vm, bf16_operands=True, **kw)
     Lmax = max(max(lens), 1)
-    ns, ch = (K.plan_cb(B, Lmax, Hkv, P, fmt, nsplit, G=G) if key_only else K.plan_v2(B, Lmax, Hkv, P, nsplit, fmt=fmt, G=G))
+    ns, ch = (K.plan_cb(B, Lmax, Hkv, P, fmt, nsplit, G=G, tail=tail is not None) if key_only
+              else K.plan_v2(B, Lmax, Hkv, P, nsplit, fmt=fmt, G=G, tail=tail is not None))
     NT = -(-G // 4)
     ws = K.Workspace(B, Hkv * NT, B * Hkv * NT * (ns + 1), DEV, 4, 128)
     qd = q.to(DEV)
@@ -99,15 +100,15 @@ def run_case(K, fmt, lens, win=None, bt_shared=False, seed=0, G=4, Hkv=8, kv_sta
     if partial:
         part = torch.full((B, Hq, 130), float("nan"), dtype=torch.float32, device=DEV)
         K.attn_partial(qd, pool, btd, seq, part, ns, ch, ws, scale * LOG2E, fmt, None if key_only else mask[:Hkv].to(DEV),
-                       None if key_only else mask[Hkv:].to(DEV), kv_start=kv_start, **tkw)
+                       None if key_only else mask[Hkv:].to(DEV), kv_start=kv_start, page=P, **tkw)
         got = part[..., :128].double().cpu().numpy()
     else:
         out = torch.full((B, Hq * 128), float("nan"), dtype=torch.bfloat16, device=DEV)
         if key_only and G == 4:
-            K.cb_attn(qd, pool, btd, seq, out, ns, ch, ws, scale * LOG2E, fmt, kv_start=kv_start, **tkw)
+            K.cb_attn(qd, pool, btd, seq, out, ns, ch, ws, scale * LOG2E, fmt, kv_start=kv_start, page=P, **tkw)
         else:
             K.v2_attn(qd, pool, btd, seq, out, ns, ch, ws, scale * LOG2E, kmask=None if key_only else mask[:Hkv].to(DEV),
-                      vmask=None if key_only else mask[Hkv:].to(DEV), fmt=fmt, kv_start=kv_start, **tkw)
+                      vmask=None if key_only else mask[Hkv:].to(DEV), fmt=fmt, kv_start=kv_start, page=P, **tkw)
         got = out.view(B, Hq, 128).double().cpu().numpy()
     torch.cuda.synchronize()
     assert K.device_status() == 0
@@ -179,6 +180,15 @@ def test_decode_gqa_groups(K, fmt, G, Hkv):
 @pytest.mark.parametrize("nsplit", [1, 3])
 def test_decode_forced_splits(K, fmt, nsplit):
     check(run_case(K, fmt, [300, 4101, 17], win=(32, 9), nsplit=nsplit, seed=40), (fmt, nsplit))
+
+
+@pytest.mark.parametrize("fmt", ["int4a", "int2a", "konlya", "konlya2"])
+def test_decode_32_token_pages(K, fmt):
+    """pages of 32 tokens (one page per 32-token step of a warp; reference dispatch kernels/csrc/attn_decode_v2.cu:2018-2060)"""
+    for i, (lens, win, ks) in enumerate((([1], None, 0), ([77, 300, 4101, 17], (32, 9), 0), ([0, 513, 64], (256, 7), 0),
+                                          ([300, 4101, 54], (132, 9), 37))):
+        check(run_case(K, fmt, lens, win=win, kv_start=ks, seed=60 + i, P=32), (fmt, lens, win, ks, "page 32"))
+    check(run_case(K, fmt, [300, 4101, 17], win=(32, 9), nsplit=3, seed=64, P=32, G=8), (fmt, "page 32, G 8, 3 splits"))
 
 
 def test_decode_partial_rows_merge(K):

@@ -197,8 +197,12 @@ def test_writers_vs_reference_library(KV):
     assert np.array_equal(va[tok_ok], vb[tok_ok])
 
 
+@pytest.mark.parametrize("values", ["gauss", "offset"])
 @pytest.mark.parametrize("G", [4, 6, 8])
-def test_decode_attention(KV, G):
+def test_decode_attention(KV, G, values):
+    """values "gauss": V ~ N(0, 1) as the baseline configurations state, outputs of order one: the stated absolute bound
+    applies.  values "offset": V with per-channel offsets up to about 10 and outlier tokens (outputs up to about 20, where
+    the bf16 spacing of the output alone is 0.06 - 0.12): the bound is taken relative to the row's largest value."""
     g = torch.Generator().manual_seed(70 + G)
     Hkv, S, W = 4, 4, 128
     Ls = (1, 5, 100, 132, 133, 161, 300, 1000, 2077)
@@ -212,7 +216,7 @@ def test_decode_attention(KV, G):
     q = (torch.randn(B, Hkv * G, D, generator=g) * 0.5).bfloat16()
     for b, L in enumerate(Ls):
         k = keys(L, Hkv, g)
-        v = (keys(L, Hkv, g).float() * 0.3).bfloat16()
+        v = (keys(L, Hkv, g).float() * 0.3).bfloat16() if values == "offset" else torch.randn(L, Hkv, D, generator=g).bfloat16()
         kv = torch.cat([k, v], 1).contiguous()
         pos = torch.arange(L)
         slots = perm[b].long()[pos // PAGE] * PAGE + pos % PAGE
@@ -248,7 +252,7 @@ def test_decode_attention(KV, G):
                 ring=rd.view(-1, 2 * Hkv, D), tail_len=tld, tail_idx=tid, T=T)
         torch.cuda.synchronize()
         got = out.view(B, Hkv * G, D).double().cpu().numpy()
-        check_attn(got, ref, (G, ns_, ch_, "oracle"), Ls)
+        check_attn(got, ref, (G, ns_, ch_, "oracle"), Ls, values == "gauss")
         if L is not None:
             # the reference's own kv_attn (kivi.cu:1983-2060, built unmodified for sm_100a) on the same pool, plan and ring
             ws2 = KV.Workspace(B * Hkv * (ns_ + 1), G, D, DEV)
@@ -259,14 +263,15 @@ def test_decode_attention(KV, G):
                            torch.cuda.current_stream().cuda_stream)
             torch.cuda.synchronize()
             assert rc == 0, rc
-            check_attn(got, out2.view(B, Hkv * G, D).double().cpu().numpy(), (G, ns_, ch_, "reference kv_attn"), Ls)
+            check_attn(got, out2.view(B, Hkv * G, D).double().cpu().numpy(), (G, ns_, ch_, "reference kv_attn"), Ls, values == "gauss")
 
 
-def check_attn(got, ref, what, Ls):
-    """the stated bounds for attention outputs: max-abs <= 2e-2 and relative RMS <= 1e-2, plus the per-row bound relative
-    to the row's largest reference value that the earlier version of this test used"""
+def check_attn(got, ref, what, Ls, absolute=True):
+    """the stated bounds for attention outputs: max-abs <= 2e-2 (absolute: outputs of order one) and relative RMS <= 1e-2,
+    plus the per-row bound max|err| <= 1e-2 max|ref row|"""
     err = np.abs(got - ref)
-    assert err.max() <= 2e-2, (what, "max-abs", err.max())
+    if absolute:
+        assert err.max() <= 2e-2, (what, "max-abs", err.max())
     rms = math.sqrt((err ** 2).mean()) / max(math.sqrt((ref ** 2).mean()), 1e-30)
     assert rms <= 1e-2, (what, "relative RMS", rms)
     for b in range(got.shape[0]):

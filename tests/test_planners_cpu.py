@@ -6,8 +6,8 @@ from flagrot_releaser_b200 import kivi as KV
 
 
 def test_decode_planner_headline_shapes():
-    # 148 SMs x 3 resident CTAs; batch 64 x 3968 page tokens, 8 kv heads -> 2 splits of 1984 (measured best: 91 us)
-    assert K.plan_splits(64, 3968, 8, 444) == (2, 1984)
+    # 148 SMs x 3 resident CTAs; batch 64 x 3968 page tokens, 8 kv heads, window CTAs in the launch
+    assert K.plan_splits(64, 3968, 8, 444, tail=True) == (2, 1984)
     ns, ch = K.plan_splits(1, 131072 - 128, 8, 444)
     assert ns * ch >= 131072 - 128 and ch % 64 == 0 and ch <= K.MAX_CHUNK and 40 <= ns <= 64
     assert K.plan_splits(256, 8064, 8, 444)[0] == 1

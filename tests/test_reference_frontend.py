@@ -4,23 +4,21 @@ FLAGROT_LIB / FLAGROT_KIVI_LIB / FLAGROT_MQ_LIB / FLAGROT_NO_REBUILD; their lib(
 argtypes / restype line, so a missing or renamed symbol fails here before any kernel runs.
 
 The front ends are used as byte code compiled by oracle/build_ref.sh into oracle/_ref/pyref (git-ignored build output, like
-the reference libraries beside it); the tests skip when it was not built.  The CPU test loads the libraries only.  The GPU
+the reference libraries beside it) and loaded by oracle/pyref.py; the tests skip when it was not built.  The CPU test loads the libraries only.  The GPU
 tests run one writer + decode step, one KIVI step and one prefill step through the reference's modules and through this
 package's front end and compare the results byte for byte (same library, same launches: any difference is a marshalling
 difference)."""
 from __future__ import annotations
 
-import importlib
 import math
-import os
-import sys
 from pathlib import Path
 
 import pytest
 import torch
 
+from oracle import pyref
+
 ROOT = Path(__file__).resolve().parents[1]
-PYREF = ROOT / "oracle" / "_ref" / "pyref"
 LIBDIR = ROOT / "flagrot_releaser_b200" / "lib"
 ENV = {"FLAGROT_LIB": LIBDIR / "libflagrot_kernels.so", "FLAGROT_KIVI_LIB": LIBDIR / "libflagrot_kivi.so",
        "FLAGROT_MQ_LIB": LIBDIR / "libflagrot_mq.so"}
@@ -29,17 +27,11 @@ ENV = {"FLAGROT_LIB": LIBDIR / "libflagrot_kernels.so", "FLAGROT_KIVI_LIB": LIBD
 @pytest.fixture(scope="module")
 def ref_front():
     """(kernels, kivi, prefill_mq) of the reference, pointed at this repository's libraries"""
-    if not (PYREF / "vllm_flagrot" / "kernels.pyc").exists():
+    if not pyref.available():
         pytest.skip("oracle/_ref/pyref not built (oracle/build_ref.sh needs the reference checkout)")
-    for k, v in ENV.items():
+    for v in ENV.values():
         assert v.exists(), f"{v} missing: run python -m flagrot_releaser_b200._build"
-        os.environ[k] = str(v)
-    os.environ["FLAGROT_NO_REBUILD"] = "1"
-    sys.path.insert(0, str(PYREF))
-    try:
-        mods = tuple(importlib.import_module(f"vllm_flagrot.{m}") for m in ("kernels", "kivi", "prefill_mq"))
-    finally:
-        sys.path.remove(str(PYREF))
+    mods = tuple(pyref.load(m, ENV) for m in ("kernels", "kivi", "prefill_mq"))
     return mods
 
 

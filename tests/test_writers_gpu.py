@@ -104,6 +104,39 @@ def test_dynamic_writer_vs_oracle(K, kind, nb, T):
                 assert np.array_equal(got, exp), (how, smode, cen, int((got != exp).sum()))
 
 
+@pytest.mark.parametrize("T", [7, 257])
+def test_writers_32_token_pages_vs_oracle(K, T):
+    """pages of 32 tokens (the reference dispatches page 16 and 32: kernels/csrc/attn_decode_v2.cu:2018-2060): static and
+    dynamic writers, whole pools byte for byte against the oracle packed with P = 32"""
+    P32 = 32
+    g = torch.Generator().manual_seed(700 + T)
+    kvb = edge_rows(T, HKV, g)
+    kv = kvb.to(DEV)
+    npg = (T + P32 - 1) // P32 + 4
+    slots = torch.randperm(npg * P32, generator=g)[:T].to(torch.int64)
+    slots[::9] = -1
+    mask = (torch.rand(2 * HKV, 4, generator=g) < 0.5).to(torch.uint8)
+    hfull = (torch.rand(2 * HKV, generator=g) < 0.4).to(torch.uint8)
+    Cq, co = calib(HKV, g)
+    CT = Cq.transpose(1, 2).contiguous().to(DEV)
+    for fmt, kind, nb in (("int4a", "konlya", 4), ("int2a", "konlya2", 2)):
+        pool0 = torch.randint(0, 256, (npg, HKV, K.v2_chunk_bytes(P32, 128, fmt)), dtype=torch.uint8, generator=g)
+        codes, words = O.static_rows(bits(kvb), mask.numpy(), hfull.numpy(), nb, None, recip=True)
+        exp = pool0.numpy().copy()
+        O.write_pool(exp, slots.numpy(), codes, words, nb, P32)
+        pool = pool0.clone().to(DEV)
+        K.w3_static_write(kv, slots.to(DEV), mask.to(DEV), hfull.to(DEV), pool, P32, fmt=fmt)
+        torch.cuda.synchronize()
+        assert np.array_equal(pool.cpu().numpy(), exp), (fmt, int((pool.cpu().numpy() != exp).sum()))
+        codes, words, _ = O.dynamic_rows(bits(kvb), Cq.numpy(), nb, None, recip=True)
+        exp = pool0.numpy().copy()
+        O.write_pool(exp, slots.numpy(), codes, words, nb, P32)
+        pool = pool0.clone().to(DEV)
+        K.cb_write(kv, slots.to(DEV), CT, co.to(DEV), kind, pool, P32)
+        torch.cuda.synchronize()
+        assert np.array_equal(pool.cpu().numpy(), exp), (kind, int((pool.cpu().numpy() != exp).sum()))
+
+
 def test_writer_two_calls_commute(K):
     """value half before key half gives the same bytes (bit 15 of the V group-0 word belongs to the key half)."""
     g = torch.Generator().manual_seed(5)
