@@ -11,9 +11,11 @@
 // CUDA cores.
 //   * grid (Hkv * ceil(G / 4), nsplit, B [x 2 with BF16 rows: the window CTAs come last and fill the final wave]),
 //     128 threads; a CTA serves 4 q heads of one kv head;
-//   * each warp owns every 4th 32-token block (two pages) of the split and a private ring of bulk-copy stages:
-//     lane 0 issues one cp.async.bulk per page (one contiguous 2304 / 1280-byte chunk) completing on the stage's
-//     mbarrier; waits are bounded and report through a status word instead of spinning forever;
+//   * each warp owns every 4th 32-token block (two 16-token pages or one 32-token page) of the split and a private ring
+//     of three stages; all 32 lanes copy 16-byte pieces of the page chunks with cp.async (one commit group per block).
+//     A single lane issuing bulk copies was measured to stall its warp for about 460 cycles per block on the copy
+//     engine's issue path; spread over the lanes the issue costs ten instructions per lane and no waiting loop at all
+//     (cp.async.wait_group is a hardware wait);
 //   * QK: A = the code bytes as stored (the K row layout is the m16n8k32 A fragment: one 128-bit shared load per
 //     token gives all four groups), B = q in 15-bit fixed point split hi / lo, for key-only pages in three bases
 //     (identity, per-group H32, whole-head H128); per (token, group) the flags select the variant, the zero point is
@@ -30,7 +32,6 @@
 
 #include "fr_common.cuh"
 #include "fr_kernels.h"
-#include "fr_tc5.cuh"
 
 namespace fr {
 
@@ -43,21 +44,14 @@ constexpr int MINB = 3;            // resident CTAs per SM the register budget i
 constexpr int MAXPG = 512;         // pages per split (chunk <= 8192 tokens of 16)
 #define NEG_INF (-INFINITY)
 
-__device__ int g_status;           // != 0: a bounded wait gave up (value = line of the wait)
 
 FR_DEVI uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
-FR_DEVI void mbar_init(uint32_t a, int n) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(a), "r"(n)); }
-FR_DEVI void mbar_expect(uint32_t a, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(a), "r"(bytes) : "memory");
+// 16-byte asynchronous copy global -> shared (L2 only), tracked by per-thread commit groups
+FR_DEVI void cp16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src) : "memory");
 }
-FR_DEVI void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t mbar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(dst),
-               "l"(src), "r"(bytes), "r"(mbar)
-               : "memory");
-}
-FR_DEVI bool mbar_wait(uint32_t a, uint32_t parity) {  // bounded: false after about half a second of SM clock
-  return tc5::mbar_wait(a, parity);
-}
+FR_DEVI void cp_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N> FR_DEVI void cp_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
 // D = A * B with a zero accumulator (no register initialisation)
 FR_DEVI void mma_u8s8_z(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
   asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};\n"
@@ -127,8 +121,7 @@ template <int NB, int NV, int PG = 16> struct SMap {
   static constexpr int SQ = QT + NV * 4 * 128 * 2;                      // int [NV][4][4]
   static constexpr int SF = SQ + NV * 16 * 4;                           // float [4]
   static constexpr int PIDX = SF + 16;                                  // int [MAXPG]
-  static constexpr int MBAR = PIDX + MAXPG * 4;                         // u64 [NWARP][ST]
-  static constexpr int TOTAL = MBAR + NWARP * ST * 8;
+  static constexpr int TOTAL = PIDX + MAXPG * 4;
   static_assert(RING_BYTES >= NWARP * (4 * 128 + 8) * 4, "merge scratch aliases the ring");
 };
 
@@ -490,13 +483,7 @@ __global__ void __launch_bounds__(128, MINB) k_decode(const DecodeParams p) {
   int* sqs = reinterpret_cast<int*>(smem + S::SQ);
   float* sfs = reinterpret_cast<float*>(smem + S::SF);
   int* pidx = reinterpret_cast<int*>(smem + S::PIDX);
-  uint64_t* mbar = reinterpret_cast<uint64_t*>(smem + S::MBAR);
 
-  if (lane == 0) {
-#pragma unroll
-    for (int s = 0; s < ST; ++s) mbar_init(smem_u32(&mbar[w * ST + s]), 1);
-    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
-  }
   {
     const int* bt = p.block_table + static_cast<size_t>(b) * p.bt_stride + c0 / L::P;
     const int npg = (ntok + L::P - 1) / L::P;
@@ -505,28 +492,34 @@ __global__ void __launch_bounds__(128, MINB) k_decode(const DecodeParams p) {
   q_prologue<NV>(p, b, kvh, qt, qtab, sqs, sfs);
   __syncthreads();
 
-  const uint8_t* poolh = p.pool + static_cast<size_t>(kvh) * L::CHUNK;
+  // ---- page loads: every lane copies 16-byte pieces of the block's page chunks (cp.async, one commit group per block), so
+  // the issue is spread over the warp instead of stalling one lane on the copy engine
+  const uint8_t* poolh = p.pool + static_cast<size_t>(kvh) * L::CHUNK + 16 * lane;
   const size_t pstride = static_cast<size_t>(p.Hkv) * L::CHUNK;
   const uint32_t ring = smem_u32(smem + S::RING) + w * ST * L::STAGE;
-  const uint32_t mb0 = smem_u32(&mbar[w * ST]);
   // block n of this warp = CTA block w + 4 n
   const int nmine = nblk > w ? (nblk - w + NWARP - 1) / NWARP : 0;
-  auto issue = [&](int n) {
-    const int blk = w + NWARP * n, s = n % ST;
-    const int t0 = blk * BLK;
-    if constexpr (L::P == 16) {
-      const int npages = (ntok - t0) > L::P ? 2 : 1;
-      mbar_expect(mb0 + 8 * s, npages * L::CHUNK);
-      bulk_g2s(ring + s * L::STAGE, poolh + static_cast<size_t>(pidx[2 * blk]) * pstride, L::CHUNK, mb0 + 8 * s);
-      if (npages == 2)
-        bulk_g2s(ring + s * L::STAGE + L::PG1, poolh + static_cast<size_t>(pidx[2 * blk + 1]) * pstride, L::CHUNK, mb0 + 8 * s);
-    } else {                          // one 32-token page per step
-      mbar_expect(mb0 + 8 * s, L::CHUNK);
-      bulk_g2s(ring + s * L::STAGE, poolh + static_cast<size_t>(pidx[blk]) * pstride, L::CHUNK, mb0 + 8 * s);
-    }
+  auto copy_chunk = [&](uint32_t dst, const uint8_t* src) {
+    constexpr int NV16 = L::CHUNK / 16;                               // 144 | 80 (P 16), 288 | 160 (P 32)
+#pragma unroll
+    for (int v = 0; v < NV16 / 32; ++v) cp16(dst + 512 * v, src + 512 * v);
+    if (NV16 % 32 != 0 && lane < NV16 % 32) cp16(dst + 512 * (NV16 / 32), src + 512 * (NV16 / 32));
   };
-  if (lane == 0)
-    for (int n = 0; n < ST - 1 && n < nmine; ++n) issue(n);
+  auto issue = [&](int n) {                                           // all lanes; n may lie past the warp's last block
+    if (n < nmine) {
+      const int blk = w + NWARP * n;
+      const uint32_t dst = ring + (n % ST) * L::STAGE + 16 * lane;
+      if constexpr (L::P == 16) {
+        copy_chunk(dst, poolh + static_cast<size_t>(pidx[2 * blk]) * pstride);
+        if (ntok - blk * BLK > L::P) copy_chunk(dst + L::PG1, poolh + static_cast<size_t>(pidx[2 * blk + 1]) * pstride);
+      } else {                          // one 32-token page per step
+        copy_chunk(dst, poolh + static_cast<size_t>(pidx[blk]) * pstride);
+      }
+    }
+    cp_commit();                        // an empty group past the end keeps the group count in step with n
+  };
+#pragma unroll
+  for (int n = 0; n < ST - 1; ++n) issue(n);
 
   // ---- per-thread constants
   // q B fragments: column gid = (head gid >> 1, part gid & 1: hi / lo); k = 4 tig .. (b0), 16 + 4 tig .. (b1)
@@ -810,23 +803,18 @@ __global__ void __launch_bounds__(128, MINB) k_decode(const DecodeParams p) {
     }
   };
 
-  bool wait_ok = true;
   for (int n = 0; n < nmine; ++n) {
     const int blk = w + NWARP * n, s = n % ST;
-    __syncwarp();
-    if (lane == 0 && n + ST - 1 < nmine) issue(n + ST - 1);
-    if (!mbar_wait(mb0 + 8 * s, (n / ST) & 1)) wait_ok = false;
+    __syncwarp();                       // every lane is done with the stage that block n + ST - 1 overwrites
+    issue(n + ST - 1);
+    cp_wait<ST - 1>();                  // this lane's pieces of block n have landed ...
+    __syncwarp();                       // ... and so have everybody else's
     const uint32_t st = ring + s * L::STAGE;
     const int tok0 = c0 + blk * BLK;                                   // absolute position of the block's token 0
     if (tok0 < lo || tok0 + BLK > c1) process(st, tok0, std::true_type{});
     else process(st, tok0, std::false_type{});
   }
-  if (!wait_ok) {
-    if (lane == 0) atomicExch(&g_status, __LINE__);
-    // copies still in flight must not land in shared memory that the next CTA on this SM owns: one more bounded wait on the
-    // last use of every stage before the warp goes on to the epilogue (the output of this launch is to be discarded)
-    for (int n = max(0, nmine - ST); n < nmine; ++n) mbar_wait(mb0 + 8 * (n % ST), (n / ST) & 1);
-  }
+  cp_wait<0>();
 
   // ---- warp epilogue: fold, reduce over the column's lanes, remove the zero points, park in shared memory
   fold(1.f);
@@ -973,10 +961,6 @@ int decode_occupancy(int nb, int key_only) {
   return e == cudaSuccess ? n : 0;
 }
 
-int decode_status() {
-  int v = 0;
-  cudaMemcpyFromSymbol(&v, g_status, sizeof(int));
-  return v;
-}
+int decode_status() { return 0; }      // the decode kernel has no device-side wait loop (hardware copy groups only)
 
 }  // namespace fr

@@ -267,7 +267,7 @@ def test_decode_error_codes(K):
                                                             None, None, 32, 0, 0, variant, 3, a[0], a[0], a[0], a[0], 512,
                                                             None, None, None, 0, 0, None, 4, 0)
     assert common(4, 16, 64, 264) == -4          # symmetric INT4 pages are not built
-    assert common(5, 32, 64, 264) == -5          # decode reads pages of 16 tokens
+    assert common(5, 8, 64, 264) == -5           # pages of 16 or 32 tokens
     assert common(5, 16, 100, 264) == -3         # chunk must be a multiple of 64
     assert common(5, 16, 64, 264 | 4096) == -8   # head dim 256
     assert L.fr_cb_attn(a[0], 512, a[1], a[2], 1, a[3], 1, 1, 16, 1, 64, 1.0, K.sign_words(), 3, 0, 3, a[0], a[0], a[0], a[0],
