@@ -896,7 +896,9 @@ def main():
             graphs = None
             torch.cuda.synchronize()
     wl.graphs = graphs
-    run_res = (lambda i: graphs[i % nc].replay()) if graphs is not None else (lambda i: wl.resident(i % nc))
+    run_res = (lambda i: wl.graphs[i % nc].replay()) if graphs is not None else (lambda i: wl.resident(i % nc))
+    use_graph = graphs is not None
+    del graphs
     sampler = ClockSampler(local).start() if rank == 0 else None
     ms = timed(run_res, a.steps, a.warmup, dist, a.sustain_s)
     clocks = sampler.stop() if rank == 0 else None
@@ -907,9 +909,20 @@ def main():
     ms_long, n_long, _ = sustained(run_res, ms, a.sustain_s, local) if dist is None else (None, 0, None)
     status = wl.status()
     race = wl.race_reference() if (a.race and hasattr(wl, "race_reference")) else None
+
+    def leave():
+        """captured graphs that hold collectives go before the process group does; a rank that still cannot tear its
+        communicator down must not keep the job (and the GPUs) waiting: the results are out, so it exits at once"""
+        if dist is None:
+            return
+        wl.graphs = None
+        torch.cuda.synchronize()
+        dist.barrier()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
     if rank != 0:
-        if dist is not None:
-            dist.destroy_process_group()
+        leave()
         return
     hbm, tf_burst, tf_sus, which = peaks()
     scale = 1e12 if wl.bound == "tensor" else 1e9
@@ -927,7 +940,7 @@ def main():
         "warmup": a.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak" if w["shard"] == "replica" else "strong",
         "vs_baseline": None, "dtype": "f16" if wl.bound == "tensor" else "u8", "data": "synthetic", "config": cfg,
         "e2e": {"value": wl.job_units() / (ms_e2e * 1e-3) / scale, "unit": unit, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                "ms_per_step": ms_e2e, "launch": "copies from Python, the step as one CUDA graph" if graphs is not None
+                "ms_per_step": ms_e2e, "launch": "copies from Python, the step as one CUDA graph" if use_graph
                 else "separate launches from Python"},
         "gpu_launches": wl.launches * a.steps,
         "roofline": {"bound": wl.bound, "achieved": ach, "peak": peak, "unit": unit, "frac": ach / peak, "traffic": traffic,
@@ -946,8 +959,7 @@ def main():
         _, _, cb = cpu_arm(a.workload, w, a.cpu_steps, 1)
         line["cpu_baseline"] = cb
     print(json.dumps(line))
-    if dist is not None:
-        dist.destroy_process_group()
+    leave()
 
 
 if __name__ == "__main__":
