@@ -835,9 +835,14 @@ def main():
     ap.add_argument("--sustain-s", type=float, default=0.5, help="seconds of untimed load before the timed steps, and the least "
                                                                   "length of the kernel-only loop behind the roofline figure")
     ap.add_argument("--no-step-graph", action="store_true", help="resident step: separate launches from Python instead of a CUDA graph")
+    ap.add_argument("--batch", type=int, default=0, help="override the workload's batch (requests for cfg5a): smaller cases for "
+                                                         "profiler captures; the line's config names the batch actually run")
     ap.add_argument("--race", action="store_true", help="also time the reference's own sm_100a-capable kernel on the same pools (cfg4)")
     a = ap.parse_args()
-    w = WORKLOADS[a.workload]
+    w = dict(WORKLOADS[a.workload])
+    if a.batch > 0 and "B" in w:
+        w["name"] += f" [batch overridden: {a.batch} instead of {w['B']}]"
+        w["B"] = a.batch
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))

@@ -100,21 +100,11 @@ struct RowParams {
   int shared15;
 };
 
+// codes and scale word of row hr of token t (row mapping: lane l holds d = 4 l .. 4 l + 3): bf16 -> fp32, whole-head H128 / 16
+// rounded to bf16, key centering, H32 of the flagged 32-blocks, stored-form quantiser
 template <int NB>
-FR_DEVI void rows_block(const RowParams& p, long long block) {
-  const int lane = threadIdx.x & 31;
-  const long long item = block * 4 + (threadIdx.x >> 5);
-  if (item >= static_cast<long long>(p.T) * p.nrow) return;
-  const int t = static_cast<int>(item / p.nrow), hr = p.row0 + static_cast<int>(item % p.nrow);
+FR_DEVI void row_codes(const RowParams& p, int t, int hr, int lane, unsigned (&code)[4], unsigned& word) {
   const bool isv = hr >= p.Hkv;
-  const int head = isv ? hr - p.Hkv : hr;
-  const long long slot = p.slot_ph ? p.slots[static_cast<long long>(t) * p.Hkv + head] : p.slots[t];
-  if (slot < 0) return;
-  const int P = p.page;
-  const long long page = slot / P;
-  const int pos = static_cast<int>(slot % P);
-  uint8_t* chunk = p.pool + (page * p.Hkv + head) * static_cast<long long>(Lay<NB>::chunk(P));
-
   const uint2 raw = *reinterpret_cast<const uint2*>(p.kv + t * p.kv_ts + hr * HD + 4 * lane);
   float v[4] = {bf16_lo(raw.x), bf16_hi(raw.x), bf16_lo(raw.y), bf16_hi(raw.y)};
   if (p.hfull != nullptr && p.hfull[hr]) {   // whole-head H128 x / 16, rounded to bf16 once
@@ -139,15 +129,99 @@ FR_DEVI void rows_block(const RowParams& p, long long block) {
   }
   const float mn = group_min8(fminf(fminf(v[0], v[1]), fminf(v[2], v[3])));
   const float mx = group_max8(fmaxf(fmaxf(v[0], v[1]), fmaxf(v[2], v[3])));
-  unsigned code[4], word = 0;
+  word = 0;
 #pragma unroll
   for (int i = 0; i < 4; ++i) quant_store<NB>(v[i], mn, mx, code[i], word);
+}
+
+// one (token, row) of a warp: quantise and store at `slot` (the whole warp takes part; slot < 0: nothing is written)
+template <int NB>
+FR_DEVI void row_write(const RowParams& p, int t, int hr, long long slot, int lane) {
+  if (slot < 0) return;
+  const bool isv = hr >= p.Hkv;
+  const int head = isv ? hr - p.Hkv : hr;
+  const int P = p.page;
+  const long long page = slot / P;
+  const int pos = static_cast<int>(slot % P);
+  uint8_t* chunk = p.pool + (page * p.Hkv + head) * static_cast<long long>(Lay<NB>::chunk(P));
+  unsigned code[4], word;
+  row_codes<NB>(p, t, hr, lane, code, word);
   if (!isv) store_k_row<NB>(chunk, P, pos, lane, code, word);
   else store_v_row<NB>(chunk, P, pos, lane, code, word, p.shared15 != 0);
 }
 
 template <int NB>
+FR_DEVI void rows_block(const RowParams& p, long long block) {
+  const int lane = threadIdx.x & 31;
+  const long long item = block * 4 + (threadIdx.x >> 5);
+  if (item >= static_cast<long long>(p.T) * p.nrow) return;
+  const int t = static_cast<int>(item / p.nrow), hr = p.row0 + static_cast<int>(item % p.nrow);
+  const int head = hr >= p.Hkv ? hr - p.Hkv : hr;
+  row_write<NB>(p, t, hr, p.slot_ph ? p.slots[static_cast<long long>(t) * p.Hkv + head] : p.slots[t], lane);
+}
+
+template <int NB>
 __global__ void __launch_bounds__(128) k_rows(const RowParams p) { rows_block<NB>(p, blockIdx.x); }
+
+// Bulk writes: warp = (8 consecutive tokens, row).  A V^T code word holds ONE dim of the 8 tokens of an aligned 8-slot run of
+// a page (INT2: two dims), so when the group's slots are such a run the warp assembles whole words in registers and stores
+// them plainly (4 words per lane and 16 bytes of scale words per 32-group) instead of flipping 128 four-bit fields per token
+// with atomics.  Any other group (ragged end, holes, scattered slots) and every K row take the per-token path.
+template <int NB>
+__global__ void __launch_bounds__(128) k_rows8(const RowParams p) {
+  const int lane = threadIdx.x & 31;
+  const long long item = static_cast<long long>(blockIdx.x) * 4 + (threadIdx.x >> 5);
+  const int groups = (p.T + 7) >> 3;
+  if (item >= static_cast<long long>(groups) * p.nrow) return;
+  const int g = static_cast<int>(item / p.nrow), hr = p.row0 + static_cast<int>(item % p.nrow);
+  const bool isv = hr >= p.Hkv;
+  const int head = isv ? hr - p.Hkv : hr;
+  const int t0 = 8 * g, nt = min(8, p.T - t0);
+  long long sl = -1;
+  if (lane < nt) sl = p.slot_ph ? p.slots[static_cast<long long>(t0 + lane) * p.Hkv + head] : p.slots[t0 + lane];
+  const long long s0 = __shfl_sync(FULLMASK, sl, 0);
+  const bool run = nt == 8 && s0 >= 0 && (s0 & 7) == 0 && __all_sync(FULLMASK, lane >= 8 || sl == s0 + lane);
+  if (!isv || !run) {
+    for (int i = 0; i < nt; ++i) row_write<NB>(p, t0 + i, hr, __shfl_sync(FULLMASK, sl, i), lane);
+    return;
+  }
+  const int P = p.page;
+  const int pos0 = static_cast<int>(s0 % P), c8 = pos0 >> 3;
+  uint8_t* chunk = p.pool + ((s0 / P) * p.Hkv + head) * static_cast<long long>(Lay<NB>::chunk(P));
+  unsigned acc[4] = {0u, 0u, 0u, 0u};       // per dim of the lane: the 8 tokens' codes (byte i >> 1, field i & 1)
+  unsigned sw[4] = {0u, 0u, 0u, 0u};        // the 8 scale words of the lane's 32-group in page order (tokens 0 2 4 6 1 3 5 7)
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    unsigned code[4], word;
+    row_codes<NB>(p, t0 + i, hr, lane, code, word);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) acc[k] |= code[k] << (8 * (i >> 1) + NB * (i & 1));
+    const int idx = (i & 1) ? 4 + (i >> 1) : (i >> 1);
+    sw[idx >> 1] |= (word & 0xFFFFu) << (16 * (idx & 1));
+  }
+  const int w = (lane & 15) >> 2, r8 = (lane & 3) >> 1, m = lane >> 4;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const int gid = 4 * (lane & 1) + k;
+    const int e = (w * 8 + gid) * (P >> 3) + c8;
+    if (NB == 4) {
+      *reinterpret_cast<uint32_t*>(chunk + Lay<4>::v_off(P) + 16 * e + 4 * (2 * m + r8)) = acc[k];
+    } else {                                  // dims d (r8 = 0, this lane) and d + 8 (lane + 2) share the word
+      const unsigned hi = __shfl_down_sync(FULLMASK, acc[k], 2);
+      if (r8 == 0) *reinterpret_cast<uint32_t*>(chunk + Lay<2>::v_off(P) + 8 * e + 4 * m) = acc[k] | (hi << 4);
+    }
+  }
+  if ((lane & 7) == 0) {
+    const int j = lane >> 3;
+    const int off = Lay<NB>::vs_off(P) + 2 * (j * P + 8 * c8);
+    if (p.shared15 && j == 0) {               // bit 15 of these words belongs to the key writer
+#pragma unroll
+      for (int x = 0; x < 8; ++x) put_word_low15(chunk, off + 2 * x, (sw[x >> 1] >> (16 * (x & 1))) & 0xFFFFu);
+    } else {
+      *reinterpret_cast<uint4*>(chunk + off) = make_uint4(sw[0], sw[1], sw[2], sw[3]);
+    }
+  }
+}
 
 // ------------------------------------------------------------------------------------------------ dynamic key writer
 struct DynParams {
@@ -340,6 +414,13 @@ int rows_launch(int nb, const void* kv, long long kv_ts, const long long* slots,
   if (T <= 0 || nrow <= 0) return 0;
   RowParams p{static_cast<const __nv_bfloat16*>(kv), kv_ts, slots, slot_ph, T, Hkv, page, mask, hfull, kmu, pool, row0,
               nrow, shared15};
+  if (T >= 256) {                              // bulk write: groups of 8 tokens, whole V^T words where the slots allow
+    const long long items = static_cast<long long>((T + 7) / 8) * nrow;
+    const unsigned blocks = static_cast<unsigned>((items + 3) / 4);
+    if (nb == 4) k_rows8<4><<<blocks, 128, 0, st>>>(p);
+    else k_rows8<2><<<blocks, 128, 0, st>>>(p);
+    return check_launch();
+  }
   const long long items = static_cast<long long>(T) * nrow;
   const unsigned blocks = static_cast<unsigned>((items + 3) / 4);
   if (nb == 4) k_rows<4><<<blocks, 128, 0, st>>>(p);

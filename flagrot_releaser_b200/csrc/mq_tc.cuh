@@ -1,17 +1,18 @@
 // Prefix-cached multi-query prefill attention on the 5th-generation tensor cores: S = Q K^T and O += P V as tcgen05.mma
 // with the accumulators, the Q operand and the P operand in tensor memory.  Included by mq_capi.cu inside its anonymous
-// namespace (kernel 3 of frmq_attn); same work list, partial layout and numerics contract as the mma.sync kernel above.
+// namespace (every plan kernel of frmq_attn runs it); work list, partial layout and numerics contract of the reference's kernels.
 //
 // CTA = (item, kv head): up to 128 query rows (the M tile; plans with 64-row tiles leave the upper half empty) x the item's
-// 64-key blocks; 24 warps (80 registers each) with fixed roles:
-//   warps 0-3   softmax: thread r owns query row r = tensor-memory lane r.  Per block two passes over the 64 scores (they
-//               are read from tensor memory twice rather than kept in registers): row maximum, then p = 2^(s - ref) into
-//               the P operand columns and the row sum.  The reference is lazy: it only moves when the maximum grew by
+// 64-key blocks; 26 warps (72 registers each) with fixed roles:
+//   warps 0-3, 20-23  softmax: two threads per query row r = tensor-memory lane r (warps w and 20 + w reach the same 32
+//               lanes), each with 32 of the block's 64 score columns, read once and kept in registers: half-row maximum,
+//               exchange with the partner through shared memory (a 64-thread named barrier), p = 2^(s - ref) into its half
+//               of the P operand columns, and the row sum.  The reference is lazy: it only moves when the maximum grew by
 //               more than 2^8 (p stays <= 256), so the O accumulator is rescaled a few times per item, not per block;
 //   warps 4-19  conversion: raw page chunks -> FP16 operand tiles in shared memory (128-byte swizzle, K-major):
 //               K [64 keys][128 dims] as (code - zero point) * scale, exact in FP16, one rounding; V^T [128 dims][64 keys];
-//   warp 20     issues the MMAs (lane 0; the whole warp waits) and owns the tensor-memory allocation;
-//   warp 21     bulk-copies the four page chunks of a block into a 3-stage ring (warps 22, 23 idle).
+//   warp 24     issues the MMAs (lane 0; the whole warp waits) and owns the tensor-memory allocation;
+//   warp 25     bulk-copies the four page chunks of a block into a 3-stage ring.
 // Key-only pages (per-token rotation flags) are not rotated back per token: the kernel keeps Q in three bases (identity,
 // per-group H32, whole-head H128) in tensor memory, the conversion drops each (key, group) into the operand tile of its
 // base and zeros into the other two, and S accumulates the three products - three times the QK tensor work, which the
@@ -21,10 +22,11 @@
 // which every wait returns at once and the CTA runs to its end (results are garbage, the status says so).
 #pragma once
 
-constexpr int TQ_THREADS = 768;
-constexpr int TQ_SOFT = 128;          // softmax threads (warps 0 .. 3): one per query row
+constexpr int TQ_THREADS = 832;       // 26 warps
+constexpr int TQ_SOFT = 128;          // query rows = softmax threads per column half
 constexpr int TQ_CONV = 512;          // conversion threads (warps 4 .. 19)
-constexpr int TQ_WMMA = 20, TQ_WLOAD = 21;
+constexpr int TQ_WSOFTB = 20;         // warps 20 .. 23: the second softmax thread of every row (warps 0 .. 3: the first)
+constexpr int TQ_WMMA = 24, TQ_WLOAD = 25;
 constexpr int TQ_RAWST = 3;
 __device__ int g_mq_status;
 
@@ -36,9 +38,10 @@ template <int NB, int NBASE> struct TQMap {
   static constexpr int RAW = VT + 2 * 16384;                     // [3][4 pages][CHUNK]
   static constexpr int RAW_STAGE = PPB * CHUNK;
   static constexpr int BAR = RAW + TQ_RAWST * RAW_STAGE;         // mbarriers
-  static constexpr int NBAR = 3 + 3 + 2 + 2 + 2 + 2 + 2 + 2 + 1 + 1;
+  static constexpr int NBAR = 3 + 3 + 2 + 2 + 2 + 2 + 2 + 2 + 1 + 1 + 1;
   static constexpr int MISC = BAR + NBAR * 8;
-  static constexpr int TOTAL = MISC + 16 + 1024;                 // + slack for the 1024-byte alignment of the tiles
+  static constexpr int XCH = MISC + 16;                          // softmax pair exchange: float [2][2][128] maxima, [128] sums
+  static constexpr int TOTAL = XCH + 5 * 128 * 4 + 1024;         // + slack for the 1024-byte alignment of the tiles
   static constexpr int QSTAGE_STRIDE = 272;                      // prologue: q rows staged over the K / V tiles
   static_assert(NBASE * 128 * QSTAGE_STRIDE <= RAW, "q staging fits in the tile region");
   static_assert(RAW % 16 == 0 && RAW_STAGE % 16 == 0 && BAR % 8 == 0, "alignment");
@@ -230,7 +233,7 @@ __global__ void __launch_bounds__(TQ_THREADS, 1) k_mq_tc(const MqParams p) {
   // ---- barriers, tensor memory
   const uint32_t bar = sb + S::BAR;
   const uint32_t b_rawf = bar, b_rawe = bar + 24, b_kf = bar + 48, b_ke = bar + 64, b_vf = bar + 80, b_ve = bar + 96;
-  const uint32_t b_sf = bar + 112, b_pf = bar + 128, b_od = bar + 144, b_q = bar + 152;
+  const uint32_t b_sf = bar + 112, b_pf = bar + 128, b_od = bar + 144, b_q = bar + 152, b_fin = bar + 160;
   volatile uint32_t* misc = reinterpret_cast<volatile uint32_t*>(smem + S::MISC);
   volatile uint32_t* abortf = misc + 1;
   if (tid == 0) {
@@ -238,10 +241,11 @@ __global__ void __launch_bounds__(TQ_THREADS, 1) k_mq_tc(const MqParams p) {
     for (int i = 0; i < 2; ++i) {
       tc5::mbar_init(b_kf + 8 * i, TQ_CONV); tc5::mbar_init(b_ke + 8 * i, 1);
       tc5::mbar_init(b_vf + 8 * i, TQ_CONV); tc5::mbar_init(b_ve + 8 * i, 1);
-      tc5::mbar_init(b_sf + 8 * i, 1); tc5::mbar_init(b_pf + 8 * i, TQ_SOFT);
+      tc5::mbar_init(b_sf + 8 * i, 1); tc5::mbar_init(b_pf + 8 * i, 2 * TQ_SOFT);
     }
     tc5::mbar_init(b_od, 1);
-    tc5::mbar_init(b_q, TQ_SOFT);
+    tc5::mbar_init(b_fin, 1);
+    tc5::mbar_init(b_q, 2 * TQ_SOFT);
     misc[1] = 0;
     tc5::mbar_init_fence();
   }
@@ -280,56 +284,61 @@ __global__ void __launch_bounds__(TQ_THREADS, 1) k_mq_tc(const MqParams p) {
   const uint8_t* poolh = p.pool + static_cast<long long>(h) * L::CHUNK;
   const int* bt = p.bt + static_cast<long long>(req) * p.bt_stride;
 
-  if (warp < TQ_SOFT / 32) {
-    // =========================================================================== softmax warps (thread = query row)
-    const int r = tid, t = r / G;
-    const uint32_t lanebase = static_cast<uint32_t>(warp * 32) << 16;
+  if (warp < 4 || (warp >= TQ_WSOFTB && warp < TQ_WSOFTB + 4)) {
+    // =========================================================================== softmax warps
+    // Two threads per query row: warps w and TQ_WSOFTB + w own the same 32 tensor-memory lanes (a warp reaches lanes
+    // 32 (warp % 4) ..) and split the 64 key columns of a block (hf = 0 | 1).  Per block each reads its 32 scores once
+    // (they stay in registers for both passes), the pair exchanges its two half-row maxima through shared memory
+    // across a 64-thread named barrier, and each writes its half of the P operand; row sums stay per thread until the end.
+    const int hf = warp >= TQ_WSOFTB ? 1 : 0;
+    const int r = (warp & 3) * 32 + lane, t = r / G;
+    const uint32_t lanebase = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const int pairbar = 1 + (warp & 3);
+    volatile float* xmax = reinterpret_cast<volatile float*>(smem + S::XCH);          // [parity][half][128 rows]
+    volatile float* xsum = xmax + 4 * 128;                                             // [128 rows]
     const bool rval = r < TQr * G && t < ntok;
     const int lim = min(kend - 1, max(pos0 + t - p.shift, ext));
-    // Q operand: this thread's row of every base -> tensor memory (64 packed columns per base)
+    // Q operand: this thread's half row of every base -> tensor memory (64 packed columns per base)
 #pragma unroll
-    for (int b = 0; b < NBASE; ++b)
+    for (int b = 0; b < NBASE; ++b) {
+      uint32_t v[32];
 #pragma unroll
-      for (int c0 = 0; c0 < 64; c0 += 32) {
-        uint32_t v[32];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const uint4 x = lds128(sb + (b * 128 + r) * S::QSTAGE_STRIDE + (c0 + 4 * i) * 4);
-          v[4 * i] = x.x; v[4 * i + 1] = x.y; v[4 * i + 2] = x.z; v[4 * i + 3] = x.w;
-        }
-        tc5::tmem_st32(tbase + TQ_Q + b * 64 + c0 + lanebase, v);
+      for (int i = 0; i < 8; ++i) {
+        const uint4 x = lds128(sb + (b * 128 + r) * S::QSTAGE_STRIDE + (32 * hf + 4 * i) * 4);
+        v[4 * i] = x.x; v[4 * i + 1] = x.y; v[4 * i + 2] = x.z; v[4 * i + 3] = x.w;
       }
+      tc5::tmem_st32(tbase + TQ_Q + b * 64 + 32 * hf + lanebase, v);
+    }
     tc5::tmem_st_wait();
     tc5::fence_before_sync();
     tc5::mbar_arrive(b_q);
 
     float mref = MQ_NEG_INF, lsum = 0.f;
     for (int j = 0; j < nblk; ++j) {
-      const int sbuf = j & 1, j0 = (kblk0 + j) * BN;
+      const int sbuf = j & 1, j0 = (kblk0 + j) * BN + 32 * hf;
       tq_wait(b_sf + 8 * sbuf, (j >> 1) & 1, abortf);
       tc5::fence_after_sync();
-      const bool full = rval && j0 >= p.kmin && j0 + BN - 1 <= lim;
-      const uint32_t ts = tbase + TQ_S + sbuf * 64 + lanebase;
-      // pass 1: row maximum (four independent chains)
+      const bool full = rval && j0 >= p.kmin && j0 + 31 <= lim;
+      uint32_t sv[32];
+      tc5::tmem_ld32(tbase + TQ_S + sbuf * 64 + 32 * hf + lanebase, sv);
+      tc5::tmem_ld_wait();
+      if (!full) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int key = j0 + i;
+          if (!(rval && key >= p.kmin && key <= lim)) sv[i] = __float_as_uint(MQ_NEG_INF);
+        }
+      }
+      // pass 1: maximum of the half row (four independent chains), then of the row
       float m4[4] = {MQ_NEG_INF, MQ_NEG_INF, MQ_NEG_INF, MQ_NEG_INF};
 #pragma unroll
-      for (int hf = 0; hf < 2; ++hf) {
-        uint32_t sv[32];
-        tc5::tmem_ld32(ts + 32 * hf, sv);
-        tc5::tmem_ld_wait();
-        if (!full) {
+      for (int i = 0; i < 32; i += 8)
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const int key = j0 + 32 * hf + i;
-            if (!(rval && key >= p.kmin && key <= lim)) sv[i] = __float_as_uint(MQ_NEG_INF);
-          }
-        }
-#pragma unroll
-        for (int i = 0; i < 32; i += 8)
-#pragma unroll
-          for (int c = 0; c < 4; ++c) m4[c] = fmaxf(m4[c], fmaxf(__uint_as_float(sv[i + 2 * c]), __uint_as_float(sv[i + 2 * c + 1])));
-      }
-      const float mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+        for (int c = 0; c < 4; ++c) m4[c] = fmaxf(m4[c], fmaxf(__uint_as_float(sv[i + 2 * c]), __uint_as_float(sv[i + 2 * c + 1])));
+      const float mxh = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+      xmax[((j & 1) * 2 + hf) * 128 + r] = mxh;
+      asm volatile("bar.sync %0, 64;\n" ::"r"(pairbar) : "memory");
+      const float mx = fmaxf(mxh, xmax[((j & 1) * 2 + (hf ^ 1)) * 128 + r]);
       float alpha = 1.f;
       const bool moved = mx > mref + 8.f || (mref == MQ_NEG_INF && mx > MQ_NEG_INF);
       if (moved) {
@@ -337,37 +346,24 @@ __global__ void __launch_bounds__(TQ_THREADS, 1) k_mq_tc(const MqParams p) {
         mref = mx;
       }
       const float base = mref == MQ_NEG_INF ? 0.f : mref;
-      // pass 2: p = 2^(s - ref) as packed FP16 straight into the P operand columns; row sum of the rounded values in fp32
+      // pass 2: p = 2^(s - ref) as packed FP16 straight into this half of the P operand; sum of the values in fp32
       float s4[4] = {0.f, 0.f, 0.f, 0.f};
+      uint32_t pk[16];
 #pragma unroll
-      for (int hf = 0; hf < 2; ++hf) {
-        uint32_t sv[32];
-        tc5::tmem_ld32(ts + 32 * hf, sv);
-        tc5::tmem_ld_wait();
-        if (!full) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const int key = j0 + 32 * hf + i;
-            if (!(rval && key >= p.kmin && key <= lim)) sv[i] = __float_as_uint(MQ_NEG_INF);
-          }
-        }
-        uint32_t pk[16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const float x0 = __uint_as_float(sv[2 * i]) - base, x1 = __uint_as_float(sv[2 * i + 1]) - base;
-          const float p0 = ex2(x0), p1 = ex2(x1);
-          s4[i & 3] += p0 + p1;
-          pk[i] = pack_h2_rn(p0, p1);
-        }
-        tc5::tmem_st16(tbase + TQ_P + sbuf * 32 + 16 * hf + lanebase, pk);
+      for (int i = 0; i < 16; ++i) {
+        const float p0 = ex2(__uint_as_float(sv[2 * i]) - base), p1 = ex2(__uint_as_float(sv[2 * i + 1]) - base);
+        s4[i & 3] += p0 + p1;
+        pk[i] = pack_h2_rn(p0, p1);
       }
+      tc5::tmem_st16(tbase + TQ_P + sbuf * 32 + 16 * hf + lanebase, pk);
       lsum = lsum * alpha + ((s4[0] + s4[1]) + (s4[2] + s4[3]));
-      // rescale of O (warp-collective) before P is released: the PV of the previous block must have landed
+      // rescale of O (warp-collective; each thread of the pair takes 64 of the 128 columns) before P is released: the PV
+      // of the previous block must have landed.  Both warps of a pair see the same `moved` for their rows.
       if (j > 0 && __any_sync(FULLMASK, moved)) {
         tq_wait(b_od, (j - 1) & 1, abortf);
         tc5::fence_after_sync();
 #pragma unroll
-        for (int c0 = 0; c0 < 128; c0 += 32) {
+        for (int c0 = 64 * hf; c0 < 64 * hf + 64; c0 += 32) {
           uint32_t o[32];
           tc5::tmem_ld32(tbase + TQ_O + c0 + lanebase, o);
           tc5::tmem_ld_wait();
@@ -381,15 +377,16 @@ __global__ void __launch_bounds__(TQ_THREADS, 1) k_mq_tc(const MqParams p) {
       tc5::mbar_arrive(b_pf + 8 * sbuf);
     }
     // ---- partials: unnormalised O (relative to the reference), the reference (log2 units), the row sum
-    // a parity wait can only tell the phase in flight from the one before it: at this point PV(nblk - 2) may still be
-    // pending, so its phase is waited for first, then the last one
-    if (nblk > 1) tq_wait(b_od, (nblk - 2) & 1, abortf);
-    tq_wait(b_od, (nblk - 1) & 1, abortf);
+    // the last PV completes a barrier of its own: a parity wait on b_od can only tell the phase in flight from the one
+    // before it, and here two of its phases (PV(nblk - 2), PV(nblk - 1)) may or may not have completed already
+    tq_wait(b_fin, 0, abortf);
     tc5::fence_after_sync();
+    if (hf == 1) xsum[r] = lsum;
+    asm volatile("bar.sync %0, 64;\n" ::"r"(pairbar) : "memory");
     {
       float* op = p.opart + (pbase + r) * D;
 #pragma unroll
-      for (int c0 = 0; c0 < 128; c0 += 32) {    // the loads are warp-collective: rows without a query take part, only the stores are predicated
+      for (int c0 = 64 * hf; c0 < 64 * hf + 64; c0 += 32) {    // the loads are warp-collective: rows without a query take part, only the stores are predicated
         uint32_t o[32];
         tc5::tmem_ld32(tbase + TQ_O + c0 + lanebase, o);
         tc5::tmem_ld_wait();
@@ -400,10 +397,10 @@ __global__ void __launch_bounds__(TQ_THREADS, 1) k_mq_tc(const MqParams p) {
                                                                   __uint_as_float(o[i + 2]), __uint_as_float(o[i + 3]));
         }
       }
-      if (rval) *reinterpret_cast<float2*>(p.ml + (pbase + r) * 2) = make_float2(mref, lsum);
+      if (rval && hf == 0) *reinterpret_cast<float2*>(p.ml + (pbase + r) * 2) = make_float2(mref, lsum + xsum[r]);
     }
     tc5::fence_before_sync();
-  } else if (warp < (TQ_SOFT + TQ_CONV) / 32) {
+  } else if (warp >= 4 && warp < 4 + TQ_CONV / 32) {
     // =========================================================================== conversion warps
     const int ctid = tid - TQ_SOFT;
     tq_wait_relaxed(b_q, 0, abortf);          // the q staging (which lies over the operand tiles) has been read
@@ -447,6 +444,7 @@ __global__ void __launch_bounds__(TQ_THREADS, 1) k_mq_tc(const MqParams p) {
           tc5::mma_f16_ts(tbase + TQ_O, tbase + TQ_P + buf * 32 + kk * 8, tc5::desc_sw128(vt + kk * 32, 1024), id_pv, (i | kk) > 0);
         tc5::mma_commit(b_ve + 8 * buf);
         tc5::mma_commit(b_od);
+        if (i == nblk - 1) tc5::mma_commit(b_fin);
       }
       __syncwarp();
     };

@@ -28,7 +28,7 @@ LOG2E = 1.4426950408889634
 ABI = 7
 KERNEL = int(os.environ.get("FLAGROT_MQ_KERNEL", "3"))
 KROWS = {1: 64, 2: 128, 3: 128}       # query rows per tile
-KCTAS = {1: 3, 2: 2, 3: 1}            # resident CTAs per SM of this build's kernels (shared / tensor memory, registers)
+KCTAS = {1: 1, 2: 1, 3: 1}            # resident CTAs per SM: every plan kernel runs the one tcgen05 kernel (shared / tensor memory)
 WAVES = float(os.environ.get("FLAGROT_MQ_WAVES", "2"))
 MIN_BLOCKS = int(os.environ.get("FLAGROT_MQ_MIN_BLOCKS", "4"))
 NO_EXT = -(1 << 30)
