@@ -408,23 +408,26 @@ int head_fwht_launch(const void* x, long long x_ts, void* out, long long o_ts, i
   return check_launch();
 }
 
+// quantise-and-pack of whole rows: token groups of 8 for a bulk write, one warp per row for an append
+template <int NB>
+static void rows_kernel_launch(const RowParams& p, cudaStream_t st) {
+  if (p.T >= 256) {                            // bulk write: groups of 8 tokens, whole V^T words where the slots allow
+    const long long items = static_cast<long long>((p.T + 7) / 8) * p.nrow;
+    k_rows8<NB><<<static_cast<unsigned>((items + 3) / 4), 128, 0, st>>>(p);
+  } else {
+    const long long items = static_cast<long long>(p.T) * p.nrow;
+    k_rows<NB><<<static_cast<unsigned>((items + 3) / 4), 128, 0, st>>>(p);
+  }
+}
+
 int rows_launch(int nb, const void* kv, long long kv_ts, const long long* slots, int slot_ph, int T, int Hkv, int page,
                 const uint8_t* mask, const uint8_t* hfull, const float* kmu, uint8_t* pool, int row0, int nrow,
                 int shared15, cudaStream_t st) {
   if (T <= 0 || nrow <= 0) return 0;
   RowParams p{static_cast<const __nv_bfloat16*>(kv), kv_ts, slots, slot_ph, T, Hkv, page, mask, hfull, kmu, pool, row0,
               nrow, shared15};
-  if (T >= 256) {                              // bulk write: groups of 8 tokens, whole V^T words where the slots allow
-    const long long items = static_cast<long long>((T + 7) / 8) * nrow;
-    const unsigned blocks = static_cast<unsigned>((items + 3) / 4);
-    if (nb == 4) k_rows8<4><<<blocks, 128, 0, st>>>(p);
-    else k_rows8<2><<<blocks, 128, 0, st>>>(p);
-    return check_launch();
-  }
-  const long long items = static_cast<long long>(T) * nrow;
-  const unsigned blocks = static_cast<unsigned>((items + 3) / 4);
-  if (nb == 4) k_rows<4><<<blocks, 128, 0, st>>>(p);
-  else k_rows<2><<<blocks, 128, 0, st>>>(p);
+  if (nb == 4) rows_kernel_launch<4>(p, st);
+  else rows_kernel_launch<2>(p, st);
   return check_launch();
 }
 
@@ -463,10 +466,7 @@ static int dyn_keys_nb(const DynParams& p, const RowParams& rows, cudaStream_t s
     const int rc = items <= 256 ? dyn_keys_staged<NB, 1>(p, rows, st) : dyn_keys_staged<NB, 2>(p, rows, st);
     if (rc != 1) return rc;
   }
-  if (rows.T > 0) {
-    const unsigned blocks = static_cast<unsigned>((static_cast<long long>(rows.T) * rows.nrow + 3) / 4);
-    k_rows<NB><<<blocks, 128, 0, st>>>(rows);
-  }
+  if (rows.T > 0) rows_kernel_launch<NB>(rows, st);
   RowParams none = rows;
   none.T = 0;
   // many tokens: C_q^T through L1 / L2 (coalesced rows), more resident CTAs, groups of up to 4 tokens share every value read
