@@ -56,6 +56,8 @@ WORKLOADS = {
                  name="qwen3-8b-shaped int2 konlya2 decode, batch 256 x ctx 8192, page 16, s4w128, centred keys"),
     "cfg4": dict(path="kivi", B=32, L=16384, Hq=64, Hkv=8, S=4, W=128, shard="kvhead",
                  name="qwen-32b-shaped kivi2:32 decode, batch 32 x ctx 16384, 64 q / 8 kv heads, page 16, s4w128"),
+    "cfg4p8": dict(path="kivi", B=32, L=16384, Hq=64, Hkv=8, S=4, W=128, shard="kvhead", f8=True,
+                   name="qwen-32b-shaped kivi2p8 (FP8 scale / min, 2.5 bits) decode, batch 32 x ctx 16384, 64 q / 8 kv heads, page 16, s4w128"),
     "cfg5a": dict(path="prefill", kind="konlya", nb=4, B=4, new=512, L=32768, Hq=32, Hkv=8, shard="request",
                   name="prefix-cached prefill, 4 requests x 512 new tokens over 32768 cached, 32 q / 8 kv heads, int4 konlya pages"),
     "cfg5b": dict(path="decode", kind="konlya", nb=4, B=1, L=131072, Hq=32, Hkv=8, S=4, W=128, center=False, shard="kvseq",
@@ -377,7 +379,8 @@ class KiviWorkload:
         self.Hkv = w["Hkv"] // world                       # this rank's kv heads [rank Hkv, (rank + 1) Hkv) and their q heads
         self.G = w["Hq"] // w["Hkv"]
         self.B, self.L, self.S, self.W = w["B"], w["L"], w["S"], w["W"]
-        per_copy = self.B * (self.L // P) * self.Hkv * KV.chunk_bytes(self.D)
+        self.f8 = bool(w.get("f8", False))                 # kivi2p8 pages
+        per_copy = self.B * (self.L // P) * self.Hkv * KV.chunk_bytes(self.D, self.f8)
         self.ncopy = a.ncopy if a.ncopy > 0 else min(64, max(2, -(-(400 << 20) // per_copy)))
         self.build(seed=4321)
         self.plan = KV.plan(self.B, self.L, self.Hkv) if not a.nsplit else (a.nsplit, max(256, -(-self.L // a.nsplit // 128) * 128))
@@ -399,7 +402,7 @@ class KiviWorkload:
         self.us_v = self.us_k = 0.0
         for _ in range(self.ncopy):
             nb = B * npg + 3
-            pool = torch.zeros(nb, Hkv, KV.chunk_bytes(D), dtype=torch.uint8, device=dev)
+            pool = torch.zeros(nb, Hkv, KV.chunk_bytes(D, self.f8), dtype=torch.uint8, device=dev)
             bt = torch.randperm(nb - 3, generator=g).view(B, npg).int()
             for b in range(B):
                 kv = torch.randn(L, 2 * Hkv, D, generator=g)
@@ -412,9 +415,9 @@ class KiviWorkload:
                 sidx = torch.where(gp < S, torch.full_like(gp, -1), gp).contiguous().to(dev)
                 dslot = (bt[b].long()[gp // P] * P + gp % P).contiguous().to(dev)
                 ev[0].record()
-                KV.v_write(kv, slots, self.co, None, pool, Hkv, D)
+                KV.v_write(kv, slots, self.co, None, pool, Hkv, D, f8=self.f8)
                 ev[1].record()
-                KV.k_encode(kv, sidx, dslot, self.qs, self.lz, SCALE, pool, Hkv, D)
+                KV.k_encode(kv, sidx, dslot, self.qs, self.lz, SCALE, pool, Hkv, D, f8=self.f8)
                 ev[2].record()
                 torch.cuda.synchronize()
                 self.us_v += ev[0].elapsed_time(ev[1]) * 1e3
@@ -442,10 +445,10 @@ class KiviWorkload:
     def kernel(self, c):
         ns, chunk = self.plan
         self.KV.attn(self.q, self.pools[c], self.bts[c], self.cached, self.out, ns, chunk, self.ws, LOG2E * SCALE, self.S, self.G,
-                     ring=self.ring.view(-1, 2 * self.Hkv, self.D), tail_len=self.tl, tail_idx=self.ti, T=self.T)
+                     ring=self.ring.view(-1, 2 * self.Hkv, self.D), tail_len=self.tl, tail_idx=self.ti, T=self.T, f8=self.f8)
 
     def resident(self, c):
-        self.KV.v_write(self.kv, self.slots[c], self.co, None, self.pools[c], self.Hkv, self.D)
+        self.KV.v_write(self.kv, self.slots[c], self.co, None, self.pools[c], self.Hkv, self.D, f8=self.f8)
         self.kernel(c)
 
     def e2e(self, c):
@@ -461,7 +464,7 @@ class KiviWorkload:
         torch.cuda.current_stream().synchronize()
 
     def _bytes(self, Hkv):
-        cell = self.KV.cell_bytes(self.D)
+        cell = self.KV.cell_bytes(self.D, self.f8)
         return (self.B * Hkv * cell * (self.L - self.W - self.S) + self.B * self.T * 2 * Hkv * self.D * 2
                 + self.B * Hkv * self.G * self.D * 2 * 2)
 
@@ -502,19 +505,24 @@ class KiviWorkload:
         out2 = torch.zeros_like(self.out)
         ring = self.ring.view(-1, 2 * self.Hkv, self.D)
 
+        f8 = 0
+
         def run(c):
             rc = L.kv_attn(self.q.data_ptr(), self.q.stride(0), self.pools[c].data_ptr(), self.bts[c].data_ptr(), self.bts[c].stride(0),
                            self.cached.data_ptr(), self.S, self.B, self.Hkv, self.G, self.D, ns, chunk, LOG2E * SCALE, ring.data_ptr(),
                            self.tl.data_ptr(), self.ti.data_ptr(), self.T, self.ws.opart.data_ptr(), self.ws.ml.data_ptr(),
-                           out2.data_ptr(), out2.stride(0), 0, torch.cuda.current_stream().cuda_stream)
+                           out2.data_ptr(), out2.stride(0), f8, torch.cuda.current_stream().cuda_stream)
             assert rc == 0, rc
-        ms = timed(lambda i: run(i % self.ncopy), 10, 3)
-        self.kernel(0)
-        run(0)
-        torch.cuda.synchronize()
-        diff = float((self.out.float() - out2.float()).abs().max())
-        return {"kernel": "reference kv_attn (k_attn3 + k_merge, mma.sync) at sm_100a", "us_per_launch": ms * 1e3,
-                "GB/s": self.launch_units() / (ms * 1e-3) / 1e9, "max_abs_diff_vs_ours": diff}
+        res = {}
+        for name, f8 in (("plain", int(self.f8)),) + ((("fast", 3),) if self.f8 else ()):    # kivi2p8 also has the reference's "fast" variant
+            ms = timed(lambda i: run(i % self.ncopy), 10, 3)
+            self.kernel(0)
+            run(0)
+            torch.cuda.synchronize()
+            diff = float((self.out.float() - out2.float()).abs().max())
+            res[name] = {"kernel": "reference kv_attn (k_attn3 + k_merge, mma.sync) at sm_100a" + (", fast variant" if f8 & 2 else ""),
+                         "us_per_launch": ms * 1e3, "GB/s": self.launch_units() / (ms * 1e-3) / 1e9, "max_abs_diff_vs_ours": diff}
+        return res["plain"] if len(res) == 1 else res
 
 
 # ---------------------------------------------------------------------------------------------- prefix-cached prefill
@@ -744,12 +752,18 @@ def cpu_arm(wname, w, steps, warmup):
         G = Hq // Hkv
         nseq = 1
         npool = nseq * (L // P)
-        pool = rs.randint(0, 256, (npool, Hkv, KO.CB), dtype=np.uint8)
-        for lo, hi in ((KO.OFF_KM, KO.OFF_VC), (KO.OFF_VM, KO.OFF_VF)):       # finite fp16 (scale | flag, min) pairs
-            pool[:, :, lo:hi] = _scale_words(rs, (npool, Hkv, (hi - lo) // 2)).view(np.uint8).reshape(npool, Hkv, hi - lo)
+        f8 = bool(w.get("f8", False))
+        pool = rs.randint(0, 256, (npool, Hkv, KO.CB8 if f8 else KO.CB), dtype=np.uint8)
+        if f8:                                                                 # finite FP8 (scale | flag, min) pairs
+            for lo, hi in ((KO.OFF_KM8, KO.OFF_VC8), (KO.OFF_VM8, KO.CB8)):
+                m = pool[:, :, lo:hi]
+                m[(m & 0x7F) > 0x50] &= 0xCF
+        else:
+            for lo, hi in ((KO.OFF_KM, KO.OFF_VC), (KO.OFF_VM, KO.OFF_VF)):   # finite fp16 (scale | flag, min) pairs
+                pool[:, :, lo:hi] = _scale_words(rs, (npool, Hkv, (hi - lo) // 2)).view(np.uint8).reshape(npool, Hkv, hi - lo)
         bt = rs.permutation(npool).reshape(nseq, L // P).astype(np.int32)
         T = w["S"] + w["W"]
-        unit_bytes = nseq * Hkv * 97 * (L - w["W"] - w["S"]) + nseq * T * 2 * Hkv * D * 2 + nseq * Hq * D * 4
+        unit_bytes = nseq * Hkv * (80 if f8 else 97) * (L - w["W"] - w["S"]) + nseq * T * 2 * Hkv * D * 2 + nseq * Hq * D * 4
         sample = f"{nseq} of {w['B']} batch rows, all {Hkv} kv heads, context {L}"
         if ref is not None:
             RKV = ref[1]
@@ -760,7 +774,7 @@ def cpu_arm(wname, w, steps, warmup):
             def step():
                 o = torch.empty(nseq, Hq, D)
                 for b in range(nseq):
-                    k, v = RKV.dequant_groups(poolt[btt[b]], D)               # [L, Hkv, D] in the original basis
+                    k, v = RKV.dequant_groups(poolt[btt[b]], D, f8=f8)        # [L, Hkv, D] in the original basis
                     k = torch.cat([k.float()[w["S"]:L - w["W"]], ring[b, :, :Hkv]])
                     v = torch.cat([v.float()[w["S"]:L - w["W"]], ring[b, :, Hkv:]])
                     s = torch.einsum("hgd,thd->hgt", q[b].view(Hkv, G, D), k) * SCALE
@@ -773,7 +787,7 @@ def cpu_arm(wname, w, steps, warmup):
 
             def step():
                 return KO.decode_reference(qb, pool, bt, np.full(nseq, L - w["W"], np.int32), SCALE, w["S"], G, ring=ringb,
-                                           tail_len=np.full(nseq, T, np.int32), tail_idx=np.arange(nseq))
+                                           tail_len=np.full(nseq, T, np.int32), tail_idx=np.arange(nseq), f8=f8)
             kind, how = "port", "float64 numpy restatement of the reference's page parser + attention (oracle/kivi_oracle.py)"
         to_metric = lambda sec: unit_bytes / sec / 1e9  # noqa: E731
     else:   # prefill: one request, 64 of its 512 new tokens, all heads, over the cached keys

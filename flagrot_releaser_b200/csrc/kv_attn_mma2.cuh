@@ -16,7 +16,7 @@ constexpr int P_BYTES = 4 * 8 * P_HSTR * 2;                // p of the step: [gr
 constexpr int SMEM2 = QB_BYTES + 4 * WARP_SMEM + P_BYTES + 256;   // + [4][8] group maxima, [4] flags
 static_assert(3 * (SMEM2 + 1024) <= 227 * 1024, "three CTAs per SM");
 
-template <int G>
+template <int G, bool F8>
 __global__ void __launch_bounds__(128, 3) k_kv_attn_mma2(const __nv_bfloat16* __restrict__ q, long long q_rs,
                                                           const uint8_t* __restrict__ pool, const int* __restrict__ bt, long long bt_rs,
                                                           const int* __restrict__ cached, int kv_start, int Hkv, int NS, int chunk,
@@ -24,6 +24,7 @@ __global__ void __launch_bounds__(128, 3) k_kv_attn_mma2(const __nv_bfloat16* __
                                                           const int* __restrict__ tail_len, const int* __restrict__ tail_idx, int T,
                                                           int B, float* __restrict__ opart, float* __restrict__ ml) {
   static_assert(G <= 8, "one M tile of q heads");
+  using L = KLay<F8>;                            // kivi2p8 pages are read as stored: their FP8 pairs are converted at use
   extern __shared__ __align__(16) uint8_t smraw[];
   if (static_cast<int>(blockIdx.z) >= B) {       // the BF16 sink / window splits come last in the grid
     if (blockIdx.y == 0) kv_tail_mma<G>(smraw, blockIdx.x, static_cast<int>(blockIdx.z) - B, q, q_rs, Hkv, NS, qscale, ring, tail_len,
@@ -73,10 +74,10 @@ __global__ void __launch_bounds__(128, 3) k_kv_attn_mma2(const __nv_bfloat16* __
   const int* btb = bt + static_cast<long long>(b) * bt_rs;
   const int gfirst = t0 / GRP, gend = (t1 + GRP - 1) / GRP;
   auto load_group = [&](int g32, int buf) {
-    const uint8_t* chA = pool + (static_cast<long long>(btb[2 * g32]) * Hkv + h) * CB;
-    const uint8_t* chB = pool + (static_cast<long long>(btb[2 * g32 + 1]) * Hkv + h) * CB;
+    const uint8_t* chA = pool + (static_cast<long long>(btb[2 * g32]) * Hkv + h) * L::CB;
+    const uint8_t* chB = pool + (static_cast<long long>(btb[2 * g32 + 1]) * Hkv + h) * L::CB;
     const uint32_t dst = wraw + buf * RAW_GROUP;
-    for (int i = lane; i < CB / 16; i += 32) {
+    for (int i = lane; i < L::CB / 16; i += 32) {
       cp16(dst + 16 * i, chA + 16 * i);
       cp16(dst + RAW_PAGE + 16 * i, chB + 16 * i);
     }
@@ -110,11 +111,16 @@ __global__ void __launch_bounds__(128, 3) k_kv_attn_mma2(const __nv_bfloat16* __
     if (have) {
       // ---- group flags
       uint32_t lmask = 0;
-      {
-        const uint4 m0 = lds128(rA + OFF_KM);
+      bool useF;
+      if (F8) {                                      // sign of slot 0 of cells 0 .. 3 | of cell 4
+        const uint4 m0 = lds128(rA + L::KM), m1 = lds128(rA + L::KM + 16);
+        lmask = ((m0.x >> 7) & 1u) | (((m0.z >> 7) & 1u) << 1) | (((m1.x >> 7) & 1u) << 2) | (((m1.z >> 7) & 1u) << 3);
+        useF = ((lds32(rA + L::KM + 32) >> 7) & 1u) != 0;
+      } else {
+        const uint4 m0 = lds128(rA + L::KM);
         lmask = ((m0.x >> 15) & 1u) | (((m0.y >> 15) & 1u) << 1) | (((m0.z >> 15) & 1u) << 2) | (((m0.w >> 15) & 1u) << 3);
+        useF = ((lds32(rA + L::KM + 16) >> 15) & 1u) != 0;
       }
-      const bool useF = ((lds32(rA + OFF_KM + 16) >> 15) & 1u) != 0;
       // ---- A fragments of QK: lane (head g8, c4) holds channels 16 kk + 2 c4 + {0, 1, 8, 9}
       uint32_t qa[8][2];
       float bias = 0.f, bias8 = 0.f;                 // bias8: the terms of channels 8 - 15 of every 16 (q there is 2^-8 small)
@@ -122,10 +128,17 @@ __global__ void __launch_bounds__(128, 3) k_kv_attn_mma2(const __nv_bfloat16* __
       for (int kk = 0; kk < 8; ++kk) {
         const int which = useF ? 2 : static_cast<int>((lmask >> (kk >> 1)) & 1u);
         const int c0 = 16 * kk + 2 * c4;
-        const uint32_t mp = (kk < 4 ? rA : rB) + OFF_KM + ((4 * kk + (c4 >> 1)) & 15) * 16 + 8 * (c4 & 1);
-        const uint2 ma = lds64(mp), mb = lds64(mp + 32);                       // channels c0, c0 + 1 | c0 + 8, c0 + 9
+        const uint32_t mp = (kk < 4 ? rA : rB) + L::KM + ((4 * kk + (c4 >> 1)) & 15) * L::MCELL + (L::MCELL / 2) * (c4 & 1);
+        float2 a0, a1, b0, b1;                                                 // (scale | flag, min) of channels c0, c0 + 1 | c0 + 8, c0 + 9
+        if (F8) {
+          const uint32_t wa = lds32(mp), wb = lds32(mp + 2 * L::MCELL);
+          a0 = e4m3x2_val(static_cast<uint16_t>(wa & 0xFF7Fu)); a1 = e4m3x2_val(static_cast<uint16_t>((wa >> 16) & 0xFF7Fu));
+          b0 = e4m3x2_val(static_cast<uint16_t>(wb & 0xFF7Fu)); b1 = e4m3x2_val(static_cast<uint16_t>((wb >> 16) & 0xFF7Fu));
+        } else {
+          const uint2 ma = lds64(mp), mb = lds64(mp + 2 * L::MCELL);
+          a0 = unpack_h2(ma.x); a1 = unpack_h2(ma.y); b0 = unpack_h2(mb.x); b1 = unpack_h2(mb.y);
+        }
         const uint2 qx = lds64(qbs + ((which * 8 + g8) * QSTR + c0) * 4), qy = lds64(qbs + ((which * 8 + g8) * QSTR + c0 + 8) * 4);
-        const float2 a0 = unpack_h2(ma.x), a1 = unpack_h2(ma.y), b0 = unpack_h2(mb.x), b1 = unpack_h2(mb.y);   // (scale | flag, min)
         const float q0 = __uint_as_float(qx.x), q1 = __uint_as_float(qx.y), q2 = __uint_as_float(qy.x), q3 = __uint_as_float(qy.y);
         qa[kk][0] = pack_h2(q0 * fabsf(a0.x), q1 * fabsf(a1.x));      // q is stored times qscale * 16 | qscale / 16
         qa[kk][1] = pack_h2(q2 * fabsf(b0.x), q3 * fabsf(b1.x));
@@ -166,7 +179,7 @@ __global__ void __launch_bounds__(128, 3) k_kv_attn_mma2(const __nv_bfloat16* __
       // (fields 0 - 4) or where one shift by 10 puts it (fields 5 - 7): mantissa bits 2 i' .. 2 i' + 1, i' = i mod 5, i.e.
       // code * 2^(2 i' - 24); the power of two of a tile column is taken out once, in the epilogue
       {
-        const uint32_t vp = (lane < 16 ? rA : rB) + OFF_VC + (lane & 15) * 32;
+        const uint32_t vp = (lane < 16 ? rA : rB) + L::VC + (lane & 15) * 32;
         const uint4 w0 = lds128(vp), w1 = lds128(vp + 16);
         const uint32_t wd[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
 #pragma unroll
@@ -182,16 +195,29 @@ __global__ void __launch_bounds__(128, 3) k_kv_attn_mma2(const __nv_bfloat16* __
       // (16 bytes), then [block][token]: whole-head scale, min (8 bytes); it goes over the group's consumed raw pages
       {
         const uint32_t pg = lane < 16 ? rA : rB;
-        const uint4 vm = lds128(pg + OFF_VM + (lane & 15) * 16);
-        const bool fF = ((lds32(pg + OFF_VF + (lane & 12)) >> (8 * (lane & 3))) & 0xFFu) != 0u;
+        float2 smj[4];                              // (scale, min) of the token's four blocks
+        uint32_t hbits = 0;                         // bit j: block j is stored as H32 x
+        bool fF;
+        if (F8) {
+          const uint2 vm = lds64(pg + L::VM + (lane & 15) * L::MCELL);
+          const uint32_t pr[4] = {vm.x & 0xFFFFu, vm.x >> 16, vm.y & 0xFFFFu, vm.y >> 16};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) { smj[j] = e4m3x2_val(static_cast<uint16_t>(pr[j] & 0xFF7Fu)); hbits |= ((pr[j] >> 7) & 1u) << j; }
+          fF = ((lds32(pg + L::KM + (lane & 15) * L::MCELL + 4) >> 23) & 1u) != 0u;    // bit 7 of the cell's slot-3 key scale
+        } else {
+          const uint4 vm = lds128(pg + L::VM + (lane & 15) * L::MCELL);
+          const uint32_t wv[4] = {vm.x, vm.y, vm.z, vm.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) { smj[j] = unpack_h2(wv[j]); hbits |= ((wv[j] >> 15) & 1u) << j; }
+          fF = ((lds32(pg + L::VF + (lane & 12)) >> (8 * (lane & 3))) & 0xFFu) != 0u;
+        }
         anyF = __any_sync(FULLMASK, fF);
-        const uint32_t wv[4] = {vm.x, vm.y, vm.z, vm.w};
         __syncwarp();                               // every lane has read what it needs of the raw pages
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          const float2 sm = unpack_h2(wv[j]);
+          const float2 sm = smj[j];
           const float sc = fabsf(sm.x) * 16.f;
-          const bool fH = !fF && signbit(sm.x), fI = !fF && !fH;
+          const bool fH = !fF && ((hbits >> j) & 1u), fI = !fF && !fH;
           sts128(rA + (j * 32 + lane) * 16, __float_as_uint(fI ? sc : 0.f), __float_as_uint(fH ? sc : 0.f),
                  __float_as_uint(fI ? sm.y : 0.f), __float_as_uint(fH ? sm.y : 0.f));
           asm volatile("st.shared.v2.u32 [%0], {%1,%2};\n" ::"r"(rA + 2048 + (j * 32 + lane) * 8), "r"(__float_as_uint(fF ? sc : 0.f)),

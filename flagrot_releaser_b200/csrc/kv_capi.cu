@@ -11,13 +11,21 @@
 //
 // Kernels: k_v_write (warp per (token, head)), k_k_encode (CTA per (group, head); fp32 CUDA cores: the selection is
 // defined by fp32 sums), kvm::k_kv_attn_mma2 (kv_attn_mma2.cuh: page splits and the BF16 sink / window split on the tensor
-// cores, GQA groups <= 8, one launch), k_kv_merge, k_kv_dequant, k_kv_lse_merge.  Head dim 128; the FP8-metadata pages
-// (f8) and head dim 256 answer code 2 with a message, as the reference does for unsupported shapes.
+// cores, GQA groups <= 8, one launch), k_kv_merge, k_kv_dequant, k_kv_lse_merge.
+//
+// kivi2p8 pages (f8 bit 0 of every entry; reference kivi.cu:28-35, 83-88): scale and minimum stored as FP8 E4M3 (round to
+// nearest even, saturating at +-448), the codes computed from the STORED values; chunk of 10 D bytes:
+//   KC [16][D/4] | KM [16][D/32][2] u8 (s8 | flag << 7, m8) of the GROUP | VC [16][D/4] | VM [16][D/32][2] u8 (s8 | H32 << 7, m8).
+// Flags sit in the sign bits of the non-negative scales: key sub-vector j -> cell j slot 0, key whole head -> cell 4 slot 0,
+// the VALUE whole-head flag of the token in cell i -> key scale of cell i slot 3 (set by the value writer, kept by the key
+// encoder).  Every kernel is templated on the page kind; f8 bit 1 (the reference's "fast" kernel variants, same values)
+// selects nothing here.  Head dim 256 and the matrix-weighted value selection answer code 2 with a message.
 #include <cmath>
 #include <cstdint>
 #include <cstdio>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
+#include <cuda_fp8.h>
 #include <cuda_runtime.h>
 
 #include "fr_common.cuh"
@@ -27,7 +35,12 @@ namespace {
 
 using fr::FULLMASK;
 constexpr int D = 128, NV = 4, PAGE = 16, GRP = 32;
-constexpr int CB = 12 * D + 16, OFF_KM = 4 * D, OFF_VC = 6 * D, OFF_VM = 10 * D, OFF_VF = 12 * D;
+template <bool F8> struct KLay {              // byte offsets inside a (page, kv head) chunk
+  static constexpr int CB = F8 ? 10 * D : 12 * D + 16;
+  static constexpr int KM = 4 * D, VC = F8 ? 5 * D : 6 * D, VM = F8 ? 9 * D : 10 * D;
+  static constexpr int VF = 12 * D;           // kivi2 only
+  static constexpr int MCELL = F8 ? 2 * NV : 4 * NV;   // bytes of (scale, min) pairs per cell
+};
 #define KV_NEG_INF (-INFINITY)
 
 char g_err[512];
@@ -51,6 +64,20 @@ FR_DEVI int kivi_code(float x, float mn, float s) {
   return static_cast<int>(rintf(fminf(fmaxf(__fdiv_rn(__fsub_rn(x, mn), d), 0.f), 3.f)));
 }
 FR_DEVI float kivi_rec(int code, float mn, float s) { return __fadd_rn(__fmul_rn(static_cast<float>(code), s), mn); }
+// FP8 E4M3, round to nearest even, saturating at +-448 (reference kivi.cu:110-119)
+FR_DEVI uint8_t e4m3_bits(float x) {
+  return static_cast<uint8_t>(__nv_cvt_float_to_fp8(fminf(fmaxf(x, -448.f), 448.f), __NV_SATFINITE, __NV_E4M3));
+}
+FR_DEVI float e4m3_val(uint8_t b) { return __half2float(__half(__nv_cvt_fp8_to_halfraw(b, __NV_E4M3))); }
+FR_DEVI float2 e4m3x2_val(uint16_t pair) {    // (low byte, high byte)
+  return __half22float2(__half2(__nv_cvt_fp8x2_to_halfraw2(pair, __NV_E4M3)));
+}
+// (scale, min) the quantizer works with: fp32 for kivi2, the stored E4M3 values for kivi2p8 (reference kivi.cu:120-125)
+template <bool F8> FR_DEVI void qparams(float mn, float mx, float& s, float& m) {
+  s = kivi_scale(mn, mx);
+  m = mn;
+  if (F8) { s = e4m3_val(e4m3_bits(s)); m = e4m3_val(e4m3_bits(mn)); }
+}
 // orthonormal H_n (n = 32 | 128) of a row held 4 elements per lane
 FR_DEVI void hada_row(float (&v)[4], int lane, int n) {
   fr::fwht_row_stages(v, lane, n);
@@ -60,6 +87,7 @@ FR_DEVI void hada_row(float (&v)[4], int lane, int n) {
 }
 
 // ------------------------------------------------------------------------------------------------ value writer
+template <bool F8>
 __global__ void __launch_bounds__(128) k_v_write(const __nv_bfloat16* __restrict__ kv, long long kv_rs, int n, int Hkv,
                                                  const long long* __restrict__ slots, const float* __restrict__ co,
                                                  uint8_t* __restrict__ pool, int ident, const int* __restrict__ vfix) {
@@ -80,10 +108,11 @@ __global__ void __launch_bounds__(128) k_v_write(const __nv_bfloat16* __restrict
     if (c > 0) hada_row(y, lane, c == 1 ? 32 : 128);
     const float mn = fr::group_min8(fminf(fminf(y[0], y[1]), fminf(y[2], y[3])));
     const float mx = fr::group_max8(fmaxf(fmaxf(y[0], y[1]), fmaxf(y[2], y[3])));
-    const float s = kivi_scale(mn, mx);
-    sc[c] = s; mnv[c] = mn;
+    float s, m0;
+    qparams<F8>(mn, mx, s, m0);
+    sc[c] = s; mnv[c] = m0;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) { code[c][i] = kivi_code(y[i], mn, s); y[i] = kivi_rec(code[c][i], mn, s); }
+    for (int i = 0; i < 4; ++i) { code[c][i] = kivi_code(y[i], m0, s); y[i] = kivi_rec(code[c][i], m0, s); }
     if (c > 0) hada_row(y, lane, c == 1 ? 32 : 128);
 #pragma unroll
     for (int i = 0; i < 4; ++i) rec[c][i] = y[i];
@@ -120,25 +149,37 @@ __global__ void __launch_bounds__(128) k_v_write(const __nv_bfloat16* __restrict
   }
   const long long blk = slot / PAGE;
   const int off = static_cast<int>(slot % PAGE);
-  uint8_t* chunk = pool + (blk * Hkv + h) * static_cast<long long>(CB);
+  using L = KLay<F8>;
+  uint8_t* chunk = pool + (blk * Hkv + h) * static_cast<long long>(L::CB);
   int cc[4];
   float s_, m_;
   if (cand == 0) { cc[0] = code[0][0]; cc[1] = code[0][1]; cc[2] = code[0][2]; cc[3] = code[0][3]; s_ = sc[0]; m_ = mnv[0]; }
   else if (cand == 1) { cc[0] = code[1][0]; cc[1] = code[1][1]; cc[2] = code[1][2]; cc[3] = code[1][3]; s_ = sc[1]; m_ = mnv[1]; }
   else { cc[0] = code[2][0]; cc[1] = code[2][1]; cc[2] = code[2][2]; cc[3] = code[2][3]; s_ = sc[2]; m_ = mnv[2]; }
-  chunk[OFF_VC + off * (D / 4) + lane] = static_cast<uint8_t>((cc[0] & 3) | ((cc[1] & 3) << 2) | ((cc[2] & 3) << 4) | ((cc[3] & 3) << 6));
+  chunk[L::VC + off * (D / 4) + lane] = static_cast<uint8_t>((cc[0] & 3) | ((cc[1] & 3) << 2) | ((cc[2] & 3) << 4) | ((cc[3] & 3) << 6));
+  if (F8) {
+    if ((lane & 7) == 0)
+      *reinterpret_cast<uint16_t*>(chunk + L::VM + off * L::MCELL + 2 * (lane >> 3)) =
+          static_cast<uint16_t>((e4m3_bits(s_) & 0x7F) | (cand == 1 ? 0x80 : 0) | (e4m3_bits(m_) << 8));
+    if (lane == 0) {                                 // the token's whole-head flag: bit 7 of its cell's slot-3 key scale
+      uint8_t* kb = chunk + L::KM + off * L::MCELL + 2 * (NV - 1);
+      *kb = static_cast<uint8_t>((*kb & 0x7F) | (useF ? 0x80 : 0));
+    }
+    return;
+  }
   if ((lane & 7) == 0) {
     __half sh = __float2half_rn(s_);
     if (cand == 1) sh = __hneg(__habs(sh));          // sign bit = this sub-vector is stored as H32 x
-    reinterpret_cast<__half2*>(chunk + OFF_VM + off * (D / 8))[lane >> 3] = __halves2half2(sh, __float2half_rn(m_));
+    reinterpret_cast<__half2*>(chunk + L::VM + off * (D / 8))[lane >> 3] = __halves2half2(sh, __float2half_rn(m_));
   }
-  if (lane == 0) chunk[OFF_VF + off] = useF ? 1 : 0;
+  if (lane == 0) chunk[L::VF + off] = useF ? 1 : 0;
 }
 
 // ------------------------------------------------------------------------------------------------ key group encoder
 constexpr int LD = D + 4, QT = 64;
 constexpr size_t KENC_SMEM = sizeof(float) * (32 * LD + 3 * 32 * LD + QT * LD + QT);
 
+template <bool F8>
 __global__ void __launch_bounds__(256) k_k_encode(const __nv_bfloat16* __restrict__ src, long long src_rs,
                                                   const __nv_bfloat16* __restrict__ src2, long long src2_rs,
                                                   const long long* __restrict__ sidx, const long long* __restrict__ dslot,
@@ -171,8 +212,7 @@ __global__ void __launch_bounds__(256) k_k_encode(const __nv_bfloat16* __restric
       float mn = INFINITY, mx = -INFINITY;
       for (int t = 0; t < 32; ++t)
         if (s_valid[t]) { const float v = xs[t * LD + c]; mn = fminf(mn, v); mx = fmaxf(mx, v); }
-      s_par[0][0][c] = mn;
-      s_par[0][1][c] = kivi_scale(mn, mx);
+      qparams<F8>(mn, mx, s_par[0][1][c], s_par[0][0][c]);
     }
     if (tid <= NV) s_choice[tid] = 0;
     __syncthreads();
@@ -196,11 +236,12 @@ __global__ void __launch_bounds__(256) k_k_encode(const __nv_bfloat16* __restric
       float mn = INFINITY, mx = -INFINITY;
       for (int t = 0; t < 32; ++t)
         if (s_valid[t]) { const float v = col[t * LD]; mn = fminf(mn, v); mx = fmaxf(mx, v); }
-      const float s = kivi_scale(mn, mx);
-      s_par[c3][0][c] = mn;
+      float s, m0;
+      qparams<F8>(mn, mx, s, m0);
+      s_par[c3][0][c] = m0;
       s_par[c3][1][c] = s;
       for (int t = 0; t < 32; ++t)
-        if (s_valid[t]) col[t * LD] = kivi_rec(kivi_code(col[t * LD], mn, s), mn, s);
+        if (s_valid[t]) col[t * LD] = kivi_rec(kivi_code(col[t * LD], m0, s), m0, s);
     }
     __syncthreads();
     if (kfix != nullptr) {
@@ -329,7 +370,7 @@ __global__ void __launch_bounds__(256) k_k_encode(const __nv_bfloat16* __restric
     hada_row(yf, lane, 128);
     const int cand = useF ? 2 : s_choice[lane >> 3];
     const long long slot = ds[t];
-    uint8_t* chunk = pool + ((slot / PAGE) * Hkv + h) * static_cast<long long>(CB);
+    uint8_t* chunk = pool + ((slot / PAGE) * Hkv + h) * static_cast<long long>(KLay<F8>::CB);
     const int off = static_cast<int>(slot % PAGE);
     uint32_t word = 0;
 #pragma unroll
@@ -342,6 +383,20 @@ __global__ void __launch_bounds__(256) k_k_encode(const __nv_bfloat16* __restric
     word |= __shfl_xor_sync(FULLMASK, word, 2);
     if ((lane & 3) == 0) reinterpret_cast<uint32_t*>(chunk + off * (D / 4))[lane >> 2] = word;
   }
+  if constexpr (F8) {     // (s8 | flag << 7, m8) byte pairs; bit 7 of a cell's slot-3 scale is the value writer's and stays
+    for (int c = tid; c < D; c += 256) {
+      const int cand = useF ? 2 : s_choice[c / 32];
+      const int cell = c / NV, k = c % NV;
+      const bool neg = k == 0 && (cell < NV ? (!useF && s_choice[cell] != 0) : (cell == NV && useF));
+      const long long slot = ds[cell];
+      uint8_t* km = pool + ((slot / PAGE) * Hkv + h) * static_cast<long long>(KLay<true>::CB) + KLay<true>::KM +
+                    static_cast<int>(slot % PAGE) * KLay<true>::MCELL + 2 * k;
+      uint8_t sb = static_cast<uint8_t>((e4m3_bits(s_par[cand][1][c]) & 0x7F) | (neg ? 0x80 : 0));
+      if (k == NV - 1) sb = static_cast<uint8_t>((sb & 0x7F) | (km[0] & 0x80));
+      km[0] = sb;
+      km[1] = e4m3_bits(s_par[cand][0][c]);
+    }
+  } else {
   for (int c = tid; c < D; c += 256) {
     const int cand = useF ? 2 : s_choice[c / 32];
     __half sh = __float2half_rn(s_par[cand][1][c]);
@@ -349,9 +404,10 @@ __global__ void __launch_bounds__(256) k_k_encode(const __nv_bfloat16* __restric
     sh = neg ? __hneg(__habs(sh)) : __habs(sh);
     const int cell = c / NV, k = c % NV;
     const long long slot = ds[cell];
-    uint8_t* chunk = pool + ((slot / PAGE) * Hkv + h) * static_cast<long long>(CB);
-    reinterpret_cast<__half2*>(chunk + OFF_KM + static_cast<int>(slot % PAGE) * (D / 8))[k] =
+    uint8_t* chunk = pool + ((slot / PAGE) * Hkv + h) * static_cast<long long>(KLay<false>::CB);
+    reinterpret_cast<__half2*>(chunk + KLay<false>::KM + static_cast<int>(slot % PAGE) * (D / 8))[k] =
         __halves2half2(sh, __float2half_rn(s_par[cand][0][c]));
+  }
   }
 }
 
@@ -397,25 +453,38 @@ __global__ void __launch_bounds__(128) k_kv_merge(const float* __restrict__ opar
 
 // ------------------------------------------------------------------------------------------------ page dequantisation
 // positions [32 g0, 32 g1) of one request -> K, V rows in the writers' basis (inverse H32 / H_D applied); warp per token
-template <typename OT>
+template <typename OT, bool F8>
 __global__ void __launch_bounds__(128) k_kv_dequant(const uint8_t* __restrict__ pool, const int* __restrict__ bt, int g0, int Hkv,
                                                     int nvalid, OT* __restrict__ ok, OT* __restrict__ ov) {
+  using L = KLay<F8>;
   const int gi = blockIdx.x, h = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = g0 + gi;
-  const uint8_t* chA = pool + (static_cast<long long>(bt[2 * g]) * Hkv + h) * CB;
-  const uint8_t* chB = pool + (static_cast<long long>(bt[2 * g + 1]) * Hkv + h) * CB;
-  const uint32_t* m0 = reinterpret_cast<const uint32_t*>(chA + OFF_KM);
-  uint32_t lm = 0;
-  for (int j = 0; j < NV; ++j) lm |= ((m0[j] >> 15) & 1u) << j;
-  const uint32_t fF = (reinterpret_cast<const uint32_t*>(chA + OFF_KM + D / 8)[0] >> 15) & 1u;
+  const uint8_t* chA = pool + (static_cast<long long>(bt[2 * g]) * Hkv + h) * L::CB;
+  const uint8_t* chB = pool + (static_cast<long long>(bt[2 * g + 1]) * Hkv + h) * L::CB;
+  // (scale with its flag, min) of pair k of a cell as floats; the flag comes back as the sign of the scale
+  auto meta = [](const uint8_t* cellp, int k) -> float2 {
+    if (F8) {
+      const uint16_t pr = reinterpret_cast<const uint16_t*>(cellp)[k];
+      const float2 v = e4m3x2_val(static_cast<uint16_t>(pr & 0xFF7Fu));
+      return make_float2((pr & 0x80u) ? -v.x : v.x, v.y);            // (a zero scale loses the flag: callers test the byte)
+    }
+    const uint32_t wv = reinterpret_cast<const uint32_t*>(cellp)[k];
+    const __half2 hv = *reinterpret_cast<const __half2*>(&wv);
+    return make_float2(__low2float(hv), __high2float(hv));
+  };
+  auto flag = [](const uint8_t* cellp, int k) -> uint32_t {
+    return F8 ? (cellp[2 * k] >> 7) & 1u : (reinterpret_cast<const uint32_t*>(cellp)[k] >> 15) & 1u;
+  };
+  uint32_t lm = 0;                                                     // key flags of the group
+  for (int j = 0; j < NV; ++j) lm |= (F8 ? flag(chA + L::KM + j * L::MCELL, 0) : flag(chA + L::KM, j)) << j;
+  const uint32_t fF = F8 ? flag(chA + L::KM + NV * L::MCELL, 0) : flag(chA + L::KM + L::MCELL, 0);
   const uint8_t* cm = lane < 16 ? chA : chB;       // this lane's channels 4 lane .. 4 lane + 3 = cell `lane`
   float ks[4], kmn[4];
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    const uint32_t wv = reinterpret_cast<const uint32_t*>(cm + OFF_KM + (lane % 16) * (D / 8))[i];
-    const __half2 hv = *reinterpret_cast<const __half2*>(&wv);
-    ks[i] = fabsf(__low2float(hv));
-    kmn[i] = __high2float(hv);
+    const float2 m = meta(cm + L::KM + (lane % 16) * L::MCELL, i);
+    ks[i] = fabsf(m.x);
+    kmn[i] = m.y;
   }
   auto store = [&](OT* dst, const float (&x)[4]) {
 #pragma unroll
@@ -439,14 +508,13 @@ __global__ void __launch_bounds__(128) k_kv_dequant(const uint8_t* __restrict__ 
     }
     if (o < nvalid) store(ok + (o * Hkv + h) * D + 4 * lane, x);
     const int cell = t % 16;
-    const uint32_t* vm = reinterpret_cast<const uint32_t*>(ch + OFF_VM + cell * (D / 8));
+    const uint8_t* vmc = ch + L::VM + cell * L::MCELL;
     uint32_t l = 0;
-    for (int j = 0; j < NV; ++j) l |= ((vm[j] >> 15) & 1u) << j;
-    const bool f = ch[OFF_VF + cell] != 0;
-    const uint32_t wv = vm[lane >> 3];
-    const __half2 hv = *reinterpret_cast<const __half2*>(&wv);
-    const float vs = fabsf(__low2float(hv)), vmn = __high2float(hv);
-    const uint8_t byte = ch[OFF_VC + cell * (D / 4) + lane];
+    for (int j = 0; j < NV; ++j) l |= flag(vmc, j) << j;
+    const bool f = F8 ? flag(ch + L::KM + cell * L::MCELL, NV - 1) != 0 : ch[L::VF + cell] != 0;
+    const float2 vmeta = meta(vmc, lane >> 3);
+    const float vs = fabsf(vmeta.x), vmn = vmeta.y;
+    const uint8_t byte = ch[L::VC + cell * (D / 4) + lane];
 #pragma unroll
     for (int i = 0; i < 4; ++i) x[i] = __fadd_rn(__fmul_rn(static_cast<float>((byte >> (2 * i)) & 3), vs), vmn);
     if (f) hada_row(x, lane, 128);
@@ -484,14 +552,14 @@ __global__ void k_kv_lse_merge(const __nv_bfloat16* __restrict__ oa, const float
 
 // one launch: grid (Hkv, max(NS, 1), 2 B); z < B are the page splits (y >= NS exits: a call with NS == 0 has only BF16
 // rows), z >= B (y == 0) the BF16 sink / window splits.
-template <int G>
+template <int G, bool F8>
 int launch_attn(const void* q, long long q_rs, const void* pool, const void* bt, long long bt_rs, const void* cached,
                 int kv_start, int B, int Hkv, int NS, int chunk, float qscale, const void* ring, const void* tail_len,
                 const void* tail_idx, int T, void* opart, void* ml, cudaStream_t st) {
   static_assert(kvm::TAIL_SMEM <= kvm::SMEM2, "the window split runs in the page-split kernel's shared memory");
   static unsigned long long ready = 0;
-  if (!fr::smem_limit_ready(kvm::k_kv_attn_mma2<G>, kvm::SMEM2, ready)) return 1;
-  kvm::k_kv_attn_mma2<G><<<dim3(Hkv, NS > 0 ? NS : 1, 2 * B), 128, kvm::SMEM2, st>>>(
+  if (!fr::smem_limit_ready(kvm::k_kv_attn_mma2<G, F8>, kvm::SMEM2, ready)) return 1;
+  kvm::k_kv_attn_mma2<G, F8><<<dim3(Hkv, NS > 0 ? NS : 1, 2 * B), 128, kvm::SMEM2, st>>>(
       static_cast<const __nv_bfloat16*>(q), q_rs, static_cast<const uint8_t*>(pool), static_cast<const int*>(bt), bt_rs,
       static_cast<const int*>(cached), kv_start, Hkv, NS, chunk, qscale, static_cast<const __nv_bfloat16*>(ring),
       static_cast<const int*>(tail_len), static_cast<const int*>(tail_idx), T, B, static_cast<float*>(opart), static_cast<float*>(ml));
@@ -511,11 +579,15 @@ int kv_v_write(const void* kv, long long kv_rs, int n, int Hkv, int Dd, const vo
                void* pool, int ident, const void* vfix, int f8, void* stream) {
   if (n <= 0) return 0;
   if (Dd != D) return fail("kv_v_write: D %d (head dim 128 only)", Dd);
-  if (f8) return fail("kv_v_write: FP8-metadata pages are not built");
   if (M != nullptr && !ident && vfix == nullptr) return fail("kv_v_write: matrix-weighted selection (M) is not built");
-  k_v_write<<<static_cast<unsigned>((static_cast<long long>(n) * Hkv + 3) / 4), 128, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(kv), kv_rs, n, Hkv, static_cast<const long long*>(slots),
-      static_cast<const float*>(co), static_cast<uint8_t*>(pool), ident, static_cast<const int*>(vfix));
+  const unsigned blocks = static_cast<unsigned>((static_cast<long long>(n) * Hkv + 3) / 4);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (f8 & 1)
+    k_v_write<true><<<blocks, 128, 0, st>>>(static_cast<const __nv_bfloat16*>(kv), kv_rs, n, Hkv, static_cast<const long long*>(slots),
+                                            static_cast<const float*>(co), static_cast<uint8_t*>(pool), ident, static_cast<const int*>(vfix));
+  else
+    k_v_write<false><<<blocks, 128, 0, st>>>(static_cast<const __nv_bfloat16*>(kv), kv_rs, n, Hkv, static_cast<const long long*>(slots),
+                                             static_cast<const float*>(co), static_cast<uint8_t*>(pool), ident, static_cast<const int*>(vfix));
   return check_launch("kv_v_write");
 }
 
@@ -524,13 +596,17 @@ int kv_k_encode(const void* src, long long src_rs, const void* src2, long long s
                 const void* kfix, int f8, void* stream) {
   if (N <= 0) return 0;
   if (Dd != D) return fail("kv_k_encode: D %d (head dim 128 only)", Dd);
-  if (f8) return fail("kv_k_encode: FP8-metadata pages are not built");
-  static unsigned long long ready = 0;
-  if (!fr::smem_limit_ready(k_k_encode, static_cast<int>(KENC_SMEM), ready)) return check_launch("kv_k_encode (shared memory)") ? 1 : 1;
-  k_k_encode<<<dim3(N, Hkv), 256, KENC_SMEM, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(src), src_rs, static_cast<const __nv_bfloat16*>(src2), src2_rs,
-      static_cast<const long long*>(sidx), static_cast<const long long*>(dslot), Hkv, static_cast<const float*>(qs),
-      static_cast<const float*>(lz), NQ, qsc, static_cast<uint8_t*>(pool), ident, static_cast<const int*>(kfix));
+  static unsigned long long ready = 0, ready8 = 0;
+  if (!((f8 & 1) ? fr::smem_limit_ready(k_k_encode<true>, static_cast<int>(KENC_SMEM), ready8)
+                 : fr::smem_limit_ready(k_k_encode<false>, static_cast<int>(KENC_SMEM), ready)))
+    return check_launch("kv_k_encode (shared memory)") ? 1 : 1;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+#define KV_ENC(F) k_k_encode<F><<<dim3(N, Hkv), 256, KENC_SMEM, st>>>( \
+      static_cast<const __nv_bfloat16*>(src), src_rs, static_cast<const __nv_bfloat16*>(src2), src2_rs, \
+      static_cast<const long long*>(sidx), static_cast<const long long*>(dslot), Hkv, static_cast<const float*>(qs), \
+      static_cast<const float*>(lz), NQ, qsc, static_cast<uint8_t*>(pool), ident, static_cast<const int*>(kfix))
+  if (f8 & 1) KV_ENC(true); else KV_ENC(false);
+#undef KV_ENC
   return check_launch("kv_k_encode");
 }
 
@@ -540,11 +616,12 @@ int kv_attn(const void* q, long long q_rs, const void* pool, const void* bt, lon
   if (B <= 0) return 0;
   if (G > 8 || G < 1 || chunk % GRP) return fail("kv_attn: G %d chunk %d", G, chunk);
   if (Dd != D) return fail("kv_attn: D %d (head dim 128 only)", Dd);
-  if (f8 & 1) return fail("kv_attn: FP8-metadata pages are not built");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   int rc = 0;
-#define KV_CASE(GG) case GG: rc = launch_attn<GG>(q, q_rs, pool, bt, bt_rs, cached, kv_start, B, Hkv, NS, chunk, qscale, ring, \
-                                                  tail_len, tail_idx, T, opart, ml, st); break;
+#define KV_CASE(GG) case GG: rc = (f8 & 1) ? launch_attn<GG, true>(q, q_rs, pool, bt, bt_rs, cached, kv_start, B, Hkv, NS, chunk, qscale, ring, \
+                                                                    tail_len, tail_idx, T, opart, ml, st) \
+                                           : launch_attn<GG, false>(q, q_rs, pool, bt, bt_rs, cached, kv_start, B, Hkv, NS, chunk, qscale, ring, \
+                                                                     tail_len, tail_idx, T, opart, ml, st); break;
   switch (G) { KV_CASE(1) KV_CASE(2) KV_CASE(3) KV_CASE(4) KV_CASE(5) KV_CASE(6) KV_CASE(7) KV_CASE(8) }
 #undef KV_CASE
   if (rc) return check_launch("kv_attn (shared memory)") ? 1 : 1;
@@ -557,15 +634,13 @@ int kv_dequant(const void* pool, const void* bt, int g0, int g1, int nvalid, int
                int f8, void* stream) {
   if (g1 <= g0) return 0;
   if (Dd != D) return fail("kv_dequant: D %d (head dim 128 only)", Dd);
-  if (f8 & 1) return fail("kv_dequant: FP8-metadata pages are not built");
   const dim3 grid(g1 - g0, Hkv);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (fp32)
-    k_kv_dequant<float><<<grid, 128, 0, st>>>(static_cast<const uint8_t*>(pool), static_cast<const int*>(bt), g0, Hkv, nvalid,
-                                              static_cast<float*>(ok), static_cast<float*>(ov));
-  else
-    k_kv_dequant<__nv_bfloat16><<<grid, 128, 0, st>>>(static_cast<const uint8_t*>(pool), static_cast<const int*>(bt), g0, Hkv,
-                                                      nvalid, static_cast<__nv_bfloat16*>(ok), static_cast<__nv_bfloat16*>(ov));
+#define KV_DQ(T, F) k_kv_dequant<T, F><<<grid, 128, 0, st>>>(static_cast<const uint8_t*>(pool), static_cast<const int*>(bt), g0, Hkv, \
+                                                             nvalid, static_cast<T*>(ok), static_cast<T*>(ov))
+  if (fp32) { if (f8 & 1) KV_DQ(float, true); else KV_DQ(float, false); }
+  else { if (f8 & 1) KV_DQ(__nv_bfloat16, true); else KV_DQ(__nv_bfloat16, false); }
+#undef KV_DQ
   return check_launch("kv_dequant");
 }
 

@@ -4,8 +4,10 @@
  * (integrations/vllm_flagrot/vllm_flagrot/kivi.py:49-77): same symbols, argument orders and page byte layout
  * (kivi.cu:15-26: 12 D + 16 bytes per (16-token page, kv head)).  Raw DEVICE pointers, element strides, the caller's
  * cudaStream_t as void*; asynchronous, allocation-free.  Return 0 ok, 1 launch error, 2 unsupported argument; text in
- * kv_last_error().  Built: head dim 128, FP16-metadata pages.  Not built (code 2): head dim 256, FP8-metadata pages
- * (f8 bit 0), matrix-weighted value selection (M).
+ * kv_last_error().  Built: head dim 128; the kivi2 pages (FP16 scale / min) and, with f8 bit 0 set in every entry, the
+ * kivi2p8 pages (kivi.cu:28-35: FP8 E4M3 scale / min, 10 D bytes per (page, kv head), flags in the scale sign bits, codes
+ * computed from the stored values).  f8 bit 1 (the reference's "fast" / "v2" kernel variants, which compute the same
+ * values) is accepted everywhere and selects nothing.  Not built (code 2): head dim 256, matrix-weighted value selection (M).
  */
 #ifndef FLAGROT_KIVI_H
 #define FLAGROT_KIVI_H
@@ -41,7 +43,7 @@ int kv_k_encode(const void* src, long long src_rs, const void* src2, long long s
  * [B, bt_rs], cached int32 [B] (page tokens read: [kv_start, cached)), NS splits of `chunk` tokens (multiple of 32),
  * qscale = softmax scale * log2(e), ring bf16 [(R + 1) T, 2 Hkv, D] with tail_len / tail_idx int32 [B], workspace
  * opart fp32 [B Hkv (NS + 1) G D], ml fp32 [B Hkv (NS + 1) G 2], out bf16 (row stride out_rs); G <= 8.
- * f8 bit 1 (the reference's "fast" variant) is accepted and ignored.  replaces kivi.cu:1983-2060 */
+ * replaces kivi.cu:1983-2060 */
 int kv_attn(const void* q, long long q_rs, const void* pool, const void* bt, long long bt_rs, const void* cached, int kv_start,
             int B, int Hkv, int G, int D, int NS, int chunk, float qscale, const void* ring, const void* tail_len,
             const void* tail_idx, int T, void* opart, void* ml, void* out, long long out_rs, int f8, void* stream);

@@ -9,6 +9,8 @@ differing choices, integrations/vllm_flagrot/tests/test_kivi.py:140,175):
   * decode attention: within 1e-2 of max|ref| of float64 attention over the parsed pages + BF16 ring rows (the
     reference's own bound, test_kivi.py:249), for GQA 4 / 6 / 8, lengths 1 .. 2077, two split plans;
   * dequantisation kernel == the oracle's parser; LSE merge == the formula evaluated in fp32.
+Every case runs for the kivi2 pages (FP16 scale / min, 1552-byte chunks) and for the kivi2p8 pages (FP8 E4M3 scale / min,
+1280-byte chunks, flags in the scale sign bits: `f8`).
 """
 import ctypes
 import math
@@ -47,7 +49,10 @@ def calib(Hkv, g, NQ=256):
             1 / math.sqrt(D))
 
 
-def setup(T, Hkv, g, S=4):
+F8 = pytest.mark.parametrize("f8", [False, True], ids=["kivi2", "kivi2p8"])
+
+
+def setup(T, Hkv, g, S=4, f8=False):
     k = keys(T, Hkv, g)
     v = (keys(T, Hkv, g).float() * 0.3).bfloat16()
     kv = torch.cat([k, v], 1).contiguous()
@@ -59,75 +64,83 @@ def setup(T, Hkv, g, S=4):
     gp = pos.view(ng, GRP)
     sidx = torch.where(gp < S, torch.full_like(gp, -1), gp).contiguous()
     dslot = slots.view(ng, GRP).contiguous()
-    pool0 = torch.randint(0, 256, (npg, Hkv, KO.CB), dtype=torch.uint8, generator=g)
+    pool0 = torch.randint(0, 256, (npg, Hkv, KO.CB8 if f8 else KO.CB), dtype=torch.uint8, generator=g)
     return kv, slots, sidx, dslot, pool0, perm
 
 
-def oracle_pool(pool0, kv, slots, sidx, dslot, qs, lz, qsc, co, ident=False, fix=None):
+def oracle_pool(pool0, kv, slots, sidx, dslot, qs, lz, qsc, co, ident=False, fix=None, f8=False):
     exp = pool0.numpy().copy()
     x = O.bf16_bits_to_f32(bits(kv))
     Hkv = x.shape[1] // 2
-    ev = KO.encode_values(x[:, Hkv:], co.numpy(), ident=ident, vfix=None if fix is None else fix.numpy(), recip=True)
-    KO.write_values(exp, slots.numpy(), ev["codes"], ev["meta"], ev["vf"])
+    ev = KO.encode_values(x[:, Hkv:], co.numpy(), ident=ident, vfix=None if fix is None else fix.numpy(), recip=True, f8=f8)
+    KO.write_values(exp, slots.numpy(), ev["codes"], ev["meta"], ev["vf"], f8=f8)
     ch = []
     for n in range(sidx.shape[0]):
         valid = sidx[n].numpy() != -1
         e = KO.encode_key_group(x[32 * n:32 * n + 32, :Hkv], valid, qs.numpy(), lz.numpy(), qsc, ident=ident,
-                                kfix=None if fix is None else fix.numpy(), recip=True)
-        KO.write_key_group(exp, dslot[n].numpy(), valid, e["codes"], e["meta"])
+                                kfix=None if fix is None else fix.numpy(), recip=True, f8=f8)
+        KO.write_key_group(exp, dslot[n].numpy(), valid, e["codes"], e["meta"], f8=f8)
         ch.append(e["choice"])
     return exp, ev["cand"], np.stack(ch)
 
 
-def run_writers(KV, pool0, kv, slots, sidx, dslot, qs, lz, qsc, co, Hkv, ident=False, fix=None):
+def run_writers(KV, pool0, kv, slots, sidx, dslot, qs, lz, qsc, co, Hkv, ident=False, fix=None, f8=False):
     pool = pool0.clone().to(DEV)
     kvd = kv.to(DEV)
     fx = None if fix is None else fix.to(DEV)
-    KV.v_write(kvd, slots.to(DEV), co.to(DEV), None, pool, Hkv, D, ident=ident, fix=fx)
-    KV.k_encode(kvd, sidx.to(DEV), dslot.to(DEV), qs.to(DEV), lz.to(DEV), qsc, pool, Hkv, D, ident=ident, fix=fx)
+    KV.v_write(kvd, slots.to(DEV), co.to(DEV), None, pool, Hkv, D, ident=ident, fix=fx, f8=f8)
+    KV.k_encode(kvd, sidx.to(DEV), dslot.to(DEV), qs.to(DEV), lz.to(DEV), qsc, pool, Hkv, D, ident=ident, fix=fx, f8=f8)
     torch.cuda.synchronize()
     return pool
 
 
+@F8
 @pytest.mark.parametrize("mode", ["ident", "fixed"])
-def test_writers_exact_modes_vs_oracle(KV, mode):
+def test_writers_exact_modes_vs_oracle(KV, mode, f8):
     g = torch.Generator().manual_seed(61)
     Hkv, T = 4, 192
     qs, lz, co, qsc = calib(Hkv, g)
-    kv, slots, sidx, dslot, pool0, _ = setup(T, Hkv, g)
+    kv, slots, sidx, dslot, pool0, _ = setup(T, Hkv, g, f8=f8)
     fix = None
     if mode == "fixed":
         fix = torch.tensor([0b0101, 0b1 << 16, 0b1111, 0], dtype=torch.int32)
-    exp, _, _ = oracle_pool(pool0, kv, slots, sidx, dslot, qs, lz, qsc, co, ident=mode == "ident", fix=fix)
-    pool = run_writers(KV, pool0, kv, slots, sidx, dslot, qs, lz, qsc, co, Hkv, ident=mode == "ident", fix=fix)
+    exp, _, _ = oracle_pool(pool0, kv, slots, sidx, dslot, qs, lz, qsc, co, ident=mode == "ident", fix=fix, f8=f8)
+    pool = run_writers(KV, pool0, kv, slots, sidx, dslot, qs, lz, qsc, co, Hkv, ident=mode == "ident", fix=fix, f8=f8)
     got = pool.cpu().numpy()
     assert np.array_equal(got, exp), int((got != exp).sum())
 
 
-def _flags(pool_np, perm, Hkv):
+def _flags(pool_np, perm, Hkv, f8=False):
     """key flags per (group, head) [ng, H, 5] and value candidates per (token, head) [T, H, 4] read back from the pages."""
     ch = pool_np[perm.numpy()]
     npg = ch.shape[0]
     ng = npg // 2
-    km = np.ascontiguousarray(ch[..., KO.OFF_KM:KO.OFF_VC]).view(np.float16).reshape(npg, Hkv, PAGE, 4, 2)
+    km, vm, vF, _, _ = KO._meta_fields(ch, f8)
     kmg = km.reshape(ng, 2, Hkv, PAGE, 4, 2).transpose(0, 2, 1, 3, 4, 5).reshape(ng, Hkv, D, 2)
-    kf = np.signbit(kmg[..., :5, 0]).astype(int)
-    vm = np.ascontiguousarray(ch[..., KO.OFF_VM:KO.OFF_VF]).view(np.float16).reshape(npg, Hkv, PAGE, 4, 2)
+    CHL = 4 if f8 else 1
+    kf = np.signbit(kmg[..., 0:5 * CHL:CHL, 0]).astype(int)
     vl = np.signbit(vm[..., 0]).astype(int)
-    vF = (ch[..., KO.OFF_VF:KO.OFF_VF + PAGE] != 0)
     cand = np.where(vF[..., None], 2, vl).transpose(0, 2, 1, 3).reshape(npg * PAGE, Hkv, 4)
     return kf, cand
 
 
-def test_writers_dynamic_vs_oracle(KV):
+def _fields(f8):
+    """byte ranges of a chunk: (key codes + key meta end, value codes, value meta, value flag bytes or None)"""
+    if f8:
+        return KO.OFF_VC8, (KO.OFF_VC8, 32), (KO.OFF_VM8, 8), None
+    return KO.OFF_VC, (KO.OFF_VC, 32), (KO.OFF_VM, 16), (KO.OFF_VF, 1)
+
+
+@F8
+def test_writers_dynamic_vs_oracle(KV, f8):
     g = torch.Generator().manual_seed(62)
     Hkv, T = 8, 512
     qs, lz, co, qsc = calib(Hkv, g)
-    kv, slots, sidx, dslot, pool0, perm = setup(T, Hkv, g)
-    exp, vcand, kch = oracle_pool(pool0, kv, slots, sidx, dslot, qs, lz, qsc, co)
-    pool = run_writers(KV, pool0, kv, slots, sidx, dslot, qs, lz, qsc, co, Hkv)
+    kv, slots, sidx, dslot, pool0, perm = setup(T, Hkv, g, f8=f8)
+    exp, vcand, kch = oracle_pool(pool0, kv, slots, sidx, dslot, qs, lz, qsc, co, f8=f8)
+    pool = run_writers(KV, pool0, kv, slots, sidx, dslot, qs, lz, qsc, co, Hkv, f8=f8)
     got = pool.cpu().numpy()
-    kf, cand = _flags(got, perm, Hkv)
+    kf, cand = _flags(got, perm, Hkv, f8)
     kexp = kch.copy()
     kexp[..., :4] = np.where(kch[..., 4:5] == 1, 0, kch[..., :4])          # H32 flags are stored only when the head choice is base
     k_ok = (kf == kexp).all(-1)
@@ -137,12 +150,20 @@ def test_writers_dynamic_vs_oracle(KV):
     # the bytes of the items whose choices agree are equal
     gch, ech = got[perm.numpy()], exp[perm.numpy()]
     tok_ok = v_ok.reshape(-1, PAGE, Hkv).transpose(0, 2, 1)                # [page, H, cell]
-    for name, lo, w in (("VC", KO.OFF_VC, 32), ("VM", KO.OFF_VM, 16), ("VF", KO.OFF_VF, 1)):
+    kend, vc, vmf, vff = _fields(f8)
+    for name, fld in (("VC", vc), ("VM", vmf), ("VF", vff)):
+        if fld is None:
+            continue
+        lo, w = fld
         a = gch[..., lo:lo + PAGE * w].reshape(*gch.shape[:2], PAGE, w)
         b = ech[..., lo:lo + PAGE * w].reshape(*gch.shape[:2], PAGE, w)
         assert np.array_equal(a[tok_ok], b[tok_ok]), name
     grp_ok = np.repeat(k_ok, 2, 0)                                         # [page, H]
-    assert np.array_equal(gch[..., :KO.OFF_VC][grp_ok], ech[..., :KO.OFF_VC][grp_ok])
+    ka, kb = gch[..., :kend].copy(), ech[..., :kend].copy()
+    if f8:                                                                 # bit 7 of the slot-3 key scales is the value flag
+        ka[..., KO.OFF_KM8 + 6::8] &= 0x7F
+        kb[..., KO.OFF_KM8 + 6::8] &= 0x7F
+    assert np.array_equal(ka[grp_ok], kb[grp_ok])
 
 
 def _ref(KV):
@@ -156,50 +177,57 @@ def _ref(KV):
     return L
 
 
-def ref_writers(L, pool0, kv, slots, sidx, dslot, qs, lz, qsc, co, Hkv, ident=False, fix=None):
+def ref_writers(L, pool0, kv, slots, sidx, dslot, qs, lz, qsc, co, Hkv, ident=False, fix=None, f8=False):
     pool = pool0.clone().to(DEV)
     kvd, sl, si, ds = kv.to(DEV), slots.to(DEV), sidx.to(DEV), dslot.to(DEV)
     q_, l_, c_ = qs.to(DEV), lz.to(DEV), co.to(DEV)
     fx = None if fix is None else fix.to(DEV)
     st = torch.cuda.current_stream().cuda_stream
     assert L.kv_v_write(kvd.data_ptr(), kvd.stride(0), kvd.shape[0], Hkv, D, sl.data_ptr(), c_.data_ptr(), None, pool.data_ptr(),
-                        int(ident), None if fx is None else fx.data_ptr(), 0, st) == 0
+                        int(ident), None if fx is None else fx.data_ptr(), int(f8), st) == 0
     assert L.kv_k_encode(kvd.data_ptr(), kvd.stride(0), None, 0, si.data_ptr(), ds.data_ptr(), si.shape[0], Hkv, D, q_.data_ptr(),
-                         l_.data_ptr(), q_.shape[1], qsc, pool.data_ptr(), int(ident), None if fx is None else fx.data_ptr(), 0,
+                         l_.data_ptr(), q_.shape[1], qsc, pool.data_ptr(), int(ident), None if fx is None else fx.data_ptr(), int(f8),
                          st) == 0
     torch.cuda.synchronize()
     return pool
 
 
-def test_writers_vs_reference_library(KV):
+@F8
+def test_writers_vs_reference_library(KV, f8):
     L = _ref(KV)
     g = torch.Generator().manual_seed(63)
     Hkv, T = 8, 1024
     qs, lz, co, qsc = calib(Hkv, g)
-    kv, slots, sidx, dslot, pool0, perm = setup(T, Hkv, g)
+    kv, slots, sidx, dslot, pool0, perm = setup(T, Hkv, g, f8=f8)
     fix = torch.tensor([0b0101, 1 << 16, 0b1111, 0, 0b0011, 1 << 16, 0b1000, 0b0110], dtype=torch.int32)
     for ident, fx in ((True, None), (False, fix)):
-        a = ref_writers(L, pool0, kv, slots, sidx, dslot, qs, lz, qsc, co, Hkv, ident=ident, fix=fx)
-        b = run_writers(KV, pool0, kv, slots, sidx, dslot, qs, lz, qsc, co, Hkv, ident=ident, fix=fx)
+        a = ref_writers(L, pool0, kv, slots, sidx, dslot, qs, lz, qsc, co, Hkv, ident=ident, fix=fx, f8=f8)
+        b = run_writers(KV, pool0, kv, slots, sidx, dslot, qs, lz, qsc, co, Hkv, ident=ident, fix=fx, f8=f8)
         assert torch.equal(a, b), (ident, int((a != b).sum()))
-    a = ref_writers(L, pool0, kv, slots, sidx, dslot, qs, lz, qsc, co, Hkv).cpu().numpy()
-    b = run_writers(KV, pool0, kv, slots, sidx, dslot, qs, lz, qsc, co, Hkv).cpu().numpy()
-    kfa, ca = _flags(a, perm, Hkv)
-    kfb, cb = _flags(b, perm, Hkv)
+    a = ref_writers(L, pool0, kv, slots, sidx, dslot, qs, lz, qsc, co, Hkv, f8=f8).cpu().numpy()
+    b = run_writers(KV, pool0, kv, slots, sidx, dslot, qs, lz, qsc, co, Hkv, f8=f8).cpu().numpy()
+    kfa, ca = _flags(a, perm, Hkv, f8)
+    kfb, cb = _flags(b, perm, Hkv, f8)
     k_ok, v_ok = (kfa == kfb).all(-1), (ca == cb).all(-1)
     assert k_ok.mean() >= 0.99 and v_ok.mean() >= 0.99, (k_ok.mean(), v_ok.mean())
     ga, gb = a[perm.numpy()], b[perm.numpy()]
     grp_ok = np.repeat(k_ok, 2, 0)
-    assert np.array_equal(ga[..., :KO.OFF_VC][grp_ok], gb[..., :KO.OFF_VC][grp_ok])
+    kend, (vlo, _), (vmlo, _), _ = _fields(f8)
+    ka, kb = ga[..., :kend].copy(), gb[..., :kend].copy()
+    if f8:
+        ka[..., KO.OFF_KM8 + 6::8] &= 0x7F
+        kb[..., KO.OFF_KM8 + 6::8] &= 0x7F
+    assert np.array_equal(ka[grp_ok], kb[grp_ok])
     tok_ok = v_ok.reshape(-1, PAGE, Hkv).transpose(0, 2, 1)
-    va = ga[..., KO.OFF_VC:KO.OFF_VM].reshape(*ga.shape[:2], PAGE, 32)
-    vb = gb[..., KO.OFF_VC:KO.OFF_VM].reshape(*ga.shape[:2], PAGE, 32)
+    va = ga[..., vlo:vmlo].reshape(*ga.shape[:2], PAGE, 32)
+    vb = gb[..., vlo:vmlo].reshape(*ga.shape[:2], PAGE, 32)
     assert np.array_equal(va[tok_ok], vb[tok_ok])
 
 
+@F8
 @pytest.mark.parametrize("values", ["gauss", "offset"])
 @pytest.mark.parametrize("G", [4, 6, 8])
-def test_decode_attention(KV, G, values):
+def test_decode_attention(KV, G, values, f8):
     """values "gauss": V ~ N(0, 1) as the baseline configurations state, outputs of order one: the stated absolute bound
     applies.  values "offset": V with per-channel offsets up to about 10 and outlier tokens (outputs up to about 20, where
     the bf16 spacing of the output alone is 0.06 - 0.12): the bound is taken relative to the row's largest value."""
@@ -210,7 +238,7 @@ def test_decode_attention(KV, G, values):
     B, Lmax, T = len(Ls), max(Ls), S + W
     npgr = ((Lmax + GRP - 1) // GRP) * 2
     nb = B * npgr + 5
-    pool = torch.randint(0, 256, (nb, Hkv, KO.CB), dtype=torch.uint8, generator=g).to(DEV)
+    pool = torch.randint(0, 256, (nb, Hkv, KO.CB8 if f8 else KO.CB), dtype=torch.uint8, generator=g).to(DEV)
     perm = torch.randperm(nb, generator=g)[:B * npgr].view(B, npgr).int()
     ring = torch.zeros(B + 1, T, 2 * Hkv, D, dtype=torch.bfloat16)
     q = (torch.randn(B, Hkv * G, D, generator=g) * 0.5).bfloat16()
@@ -220,13 +248,13 @@ def test_decode_attention(KV, G, values):
         kv = torch.cat([k, v], 1).contiguous()
         pos = torch.arange(L)
         slots = perm[b].long()[pos // PAGE] * PAGE + pos % PAGE
-        KV.v_write(kv.to(DEV), slots.to(DEV), co.to(DEV), None, pool, Hkv, D)
+        KV.v_write(kv.to(DEV), slots.to(DEV), co.to(DEV), None, pool, Hkv, D, f8=f8)
         ngc = L // GRP
         if ngc:
             gp = torch.arange(ngc * GRP).view(ngc, GRP)
             sidx = torch.where(gp < S, torch.full_like(gp, -1), gp).contiguous()
             dslot = (perm[b].long()[gp // PAGE] * PAGE + gp % PAGE).contiguous()
-            KV.k_encode(kv.to(DEV), sidx.to(DEV), dslot.to(DEV), qs.to(DEV), lz.to(DEV), qsc, pool, Hkv, D)
+            KV.k_encode(kv.to(DEV), sidx.to(DEV), dslot.to(DEV), qs.to(DEV), lz.to(DEV), qsc, pool, Hkv, D, f8=f8)
         for p in range(L):
             if p < S:
                 ring[b, p] = kv[p]
@@ -237,8 +265,9 @@ def test_decode_attention(KV, G, values):
     tl = torch.tensor([min(L, T) for L in Ls], dtype=torch.int32)
     ti = torch.arange(B, dtype=torch.int32)
     scale = 1 / math.sqrt(D)
-    ref = KO.decode_reference(bits(q), pool.cpu().numpy(), perm.numpy(), cached.numpy(), scale, S, G, ring=bits(ring),
-                              tail_len=tl.numpy(), tail_idx=ti.numpy())
+    pool_np = pool.cpu().numpy()
+    ref = KO.decode_reference(bits(q), pool_np, perm.numpy(), cached.numpy(), scale, S, G, ring=bits(ring),
+                              tail_len=tl.numpy(), tail_idx=ti.numpy(), f8=f8)
     ns, chunk = KV.plan(B, Lmax, Hkv)
     L = ref_lib("libflagrot_kivi_ref.so")
     if L is not None:
@@ -249,7 +278,7 @@ def test_decode_attention(KV, G, values):
         ws = KV.Workspace(B * Hkv * (ns_ + 1), G, D, DEV)
         out = torch.zeros(B, Hkv * G * D, dtype=torch.bfloat16, device=DEV)
         KV.attn(qd, pool, btd, cd, out, ns_, ch_, ws, scale * 1.4426950408889634, S, G,
-                ring=rd.view(-1, 2 * Hkv, D), tail_len=tld, tail_idx=tid, T=T)
+                ring=rd.view(-1, 2 * Hkv, D), tail_len=tld, tail_idx=tid, T=T, f8=f8, fast=f8 and ch_ == 256)
         torch.cuda.synchronize()
         got = out.view(B, Hkv * G, D).double().cpu().numpy()
         check_attn(got, ref, (G, ns_, ch_, "oracle"), Ls, values == "gauss")
@@ -259,7 +288,7 @@ def test_decode_attention(KV, G, values):
             out2 = torch.zeros_like(out)
             rc = L.kv_attn(qd.data_ptr(), qd.stride(0), pool.data_ptr(), btd.data_ptr(), btd.stride(0), cd.data_ptr(), S, B, Hkv, G,
                            D, ns_, ch_, scale * 1.4426950408889634, rd.data_ptr(), tld.data_ptr(), tid.data_ptr(), T,
-                           ws2.opart.data_ptr(), ws2.ml.data_ptr(), out2.data_ptr(), out2.stride(0), 0,
+                           ws2.opart.data_ptr(), ws2.ml.data_ptr(), out2.data_ptr(), out2.stride(0), int(f8),
                            torch.cuda.current_stream().cuda_stream)
             torch.cuda.synchronize()
             assert rc == 0, rc
@@ -306,19 +335,20 @@ def test_decode_attention_window_only(KV):
     check_attn(out.view(B, Hkv * G, D).double().cpu().numpy(), ref, "window only", Ls)
 
 
-def test_dequant_and_lse_merge(KV):
+@F8
+def test_dequant_and_lse_merge(KV, f8):
     g = torch.Generator().manual_seed(81)
     Hkv, T = 4, 640
     qs, lz, co, qsc = calib(Hkv, g)
-    kv, slots, sidx, dslot, pool0, perm = setup(T, Hkv, g)
-    pool = run_writers(KV, pool0, kv, slots, sidx, dslot, qs, lz, qsc, co, Hkv)
-    K0, V0 = KO.dequant_groups(pool.cpu().numpy()[perm.numpy()])
+    kv, slots, sidx, dslot, pool0, perm = setup(T, Hkv, g, f8=f8)
+    pool = run_writers(KV, pool0, kv, slots, sidx, dslot, qs, lz, qsc, co, Hkv, f8=f8)
+    K0, V0 = KO.dequant_groups(pool.cpu().numpy()[perm.numpy()], f8)
     bt = perm.int().to(DEV)
     for a, n in ((0, T), (4, 300), (96, 97), (37, T)):
-        k1, v1 = KV.dequant_cuda(pool, bt, a, n, Hkv, D, torch.float32)
+        k1, v1 = KV.dequant_cuda(pool, bt, a, n, Hkv, D, torch.float32, f8=f8, v2=f8 and a == 4)
         assert np.abs(k1.cpu().numpy() - K0[a:n]).max() <= 1e-4 * np.abs(K0).max()
         assert np.abs(v1.cpu().numpy() - V0[a:n]).max() <= 1e-4 * np.abs(V0).max()
-        k2, _ = KV.dequant_cuda(pool, bt, a, n, Hkv, D, torch.bfloat16)
+        k2, _ = KV.dequant_cuda(pool, bt, a, n, Hkv, D, torch.bfloat16, f8=f8)
         assert np.abs(k2.float().cpu().numpy() - K0[a:n]).max() <= 2 ** -7 * np.abs(K0).max()
     n, H = 77, 6
     oa = torch.randn(n, H, D, generator=g).bfloat16().to(DEV)
@@ -335,13 +365,47 @@ def test_dequant_and_lse_merge(KV):
     assert torch.equal(out, exp)
 
 
+def test_value_flag_survives_key_encoding(KV):
+    """kivi2p8: the value whole-head flag is bit 7 of a key scale byte (cell i, slot 3); the key group encoder writes those
+    bytes later and must keep it, in any interleaving of the two writers (the reference's own check:
+    integrations/vllm_flagrot/tests/test_kivi.py:358-404)."""
+    g = torch.Generator().manual_seed(64)
+    Hkv, ng = 4, 6
+    T = ng * GRP
+    qs, lz, co, qsc = calib(Hkv, g)
+    kv, slots, sidx, dslot, pool0, perm = setup(T, Hkv, g, f8=True)
+    pool = pool0.clone().to(DEV)
+    kvd, sl, si, ds = kv.to(DEV), slots.to(DEV), sidx.to(DEV), dslot.to(DEV)
+    q_, l_, c_ = qs.to(DEV), lz.to(DEV), co.to(DEV)
+
+    def venc(a, b):
+        KV.v_write(kvd[a:b], sl[a:b].contiguous(), c_, None, pool, Hkv, D, f8=True)
+
+    def kenc(gs):
+        KV.k_encode(kvd, si[gs].contiguous(), ds[gs].contiguous(), q_, l_, qsc, pool, Hkv, D, f8=True)
+
+    def vflags(pl):
+        return KO._meta_fields(pl.cpu().numpy()[perm.numpy()], True)[2]
+    venc(0, GRP); kenc([0]); venc(GRP, T - GRP); kenc(list(range(1, ng - 1))); kenc([0]); venc(T - GRP, T); kenc([ng - 1])
+    torch.cuda.synchronize()
+    after = vflags(pool)
+    only_v = pool0.clone().to(DEV)
+    only_v[..., KO.OFF_KM8:KO.OFF_VC8] = 0
+    KV.v_write(kvd, sl, c_, None, only_v, Hkv, D, f8=True)
+    torch.cuda.synchronize()
+    ref = vflags(only_v)
+    assert ref.any() and np.array_equal(after, ref)
+    # and the whole pool equals one ordinary pass (values, then keys)
+    straight = run_writers(KV, pool0, kv, slots, sidx, dslot, qs, lz, qsc, co, Hkv, f8=True)
+    assert torch.equal(pool, straight)
+
+
 def test_error_codes(KV):
     L = KV.lib()
     z = torch.zeros(64, dtype=torch.uint8, device=DEV)
     p = z.data_ptr()
     assert L.kv_v_write(p, 0, 1, 1, 256, p, p, None, p, 0, None, 0, None) == 2
     assert b"head dim 128" in L.kv_last_error()
-    assert L.kv_v_write(p, 0, 1, 1, 128, p, p, None, p, 0, None, 1, None) == 2
     assert L.kv_v_write(p, 0, 0, 1, 128, p, p, None, p, 0, None, 0, None) == 0
     assert L.kv_attn(p, 0, p, p, 0, p, 0, 1, 1, 9, 128, 1, 256, 1.0, p, p, p, 0, p, p, p, 0, 0, None) == 2
     assert L.kv_attn(p, 0, p, p, 0, p, 0, 1, 1, 4, 128, 1, 100, 1.0, p, p, p, 0, p, p, p, 0, 0, None) == 2
