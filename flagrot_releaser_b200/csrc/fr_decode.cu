@@ -484,16 +484,11 @@ __global__ void __launch_bounds__(128, MINB) k_decode(const DecodeParams p) {
   float* sfs = reinterpret_cast<float*>(smem + S::SF);
   int* pidx = reinterpret_cast<int*>(smem + S::PIDX);
 
-  {
-    const int* bt = p.block_table + static_cast<size_t>(b) * p.bt_stride + c0 / L::P;
-    const int npg = (ntok + L::P - 1) / L::P;
-    for (int i = tid; i < npg && i < MAXPG; i += 128) pidx[i] = __ldg(bt + i);
-  }
-  q_prologue<NV>(p, b, kvh, qt, qtab, sqs, sfs);
-  __syncthreads();
-
   // ---- page loads: every lane copies 16-byte pieces of the block's page chunks (cp.async, one commit group per block), so
-  // the issue is spread over the warp instead of stalling one lane on the copy engine
+  // the issue is spread over the warp instead of stalling one lane on the copy engine.  The first ST - 1 blocks of a warp
+  // are requested before anything else, with their page numbers straight from the global block table, so that the q
+  // prologue and the staging of the table run under the latency of those loads.
+  const int* bt = p.block_table + static_cast<size_t>(b) * p.bt_stride + c0 / L::P;
   const uint8_t* poolh = p.pool + static_cast<size_t>(kvh) * L::CHUNK + 16 * lane;
   const size_t pstride = static_cast<size_t>(p.Hkv) * L::CHUNK;
   const uint32_t ring = smem_u32(smem + S::RING) + w * ST * L::STAGE;
@@ -505,21 +500,30 @@ __global__ void __launch_bounds__(128, MINB) k_decode(const DecodeParams p) {
     for (int v = 0; v < NV16 / 32; ++v) cp16(dst + 512 * v, src + 512 * v);
     if (NV16 % 32 != 0 && lane < NV16 % 32) cp16(dst + 512 * (NV16 / 32), src + 512 * (NV16 / 32));
   };
-  auto issue = [&](int n) {                                           // all lanes; n may lie past the warp's last block
+  auto issue = [&](int n, bool early) {                               // all lanes; n may lie past the warp's last block
     if (n < nmine) {
       const int blk = w + NWARP * n;
       const uint32_t dst = ring + (n % ST) * L::STAGE + 16 * lane;
       if constexpr (L::P == 16) {
-        copy_chunk(dst, poolh + static_cast<size_t>(pidx[2 * blk]) * pstride);
-        if (ntok - blk * BLK > L::P) copy_chunk(dst + L::PG1, poolh + static_cast<size_t>(pidx[2 * blk + 1]) * pstride);
+        const bool two = ntok - blk * BLK > L::P;
+        const int pg0 = early ? __ldg(bt + 2 * blk) : pidx[2 * blk];
+        const int pg1 = two ? (early ? __ldg(bt + 2 * blk + 1) : pidx[2 * blk + 1]) : 0;
+        copy_chunk(dst, poolh + static_cast<size_t>(pg0) * pstride);
+        if (two) copy_chunk(dst + L::PG1, poolh + static_cast<size_t>(pg1) * pstride);
       } else {                          // one 32-token page per step
-        copy_chunk(dst, poolh + static_cast<size_t>(pidx[blk]) * pstride);
+        copy_chunk(dst, poolh + static_cast<size_t>(early ? __ldg(bt + blk) : pidx[blk]) * pstride);
       }
     }
     cp_commit();                        // an empty group past the end keeps the group count in step with n
   };
 #pragma unroll
-  for (int n = 0; n < ST - 1; ++n) issue(n);
+  for (int n = 0; n < ST - 1; ++n) issue(n, true);
+  {
+    const int npg = (ntok + L::P - 1) / L::P;
+    for (int i = tid; i < npg && i < MAXPG; i += 128) pidx[i] = __ldg(bt + i);
+  }
+  q_prologue<NV>(p, b, kvh, qt, qtab, sqs, sfs);
+  __syncthreads();
 
   // ---- per-thread constants
   // q B fragments: column gid = (head gid >> 1, part gid & 1: hi / lo); k = 4 tig .. (b0), 16 + 4 tig .. (b1)
@@ -806,7 +810,7 @@ __global__ void __launch_bounds__(128, MINB) k_decode(const DecodeParams p) {
   for (int n = 0; n < nmine; ++n) {
     const int blk = w + NWARP * n, s = n % ST;
     __syncwarp();                       // every lane is done with the stage that block n + ST - 1 overwrites
-    issue(n + ST - 1);
+    issue(n + ST - 1, false);
     cp_wait<ST - 1>();                  // this lane's pieces of block n have landed ...
     __syncwarp();                       // ... and so have everybody else's
     const uint32_t st = ring + s * L::STAGE;
