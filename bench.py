@@ -133,6 +133,8 @@ def max_over_ranks(ms, dist, device="cuda"):
 def timed(fn, steps, warmup, dist=None, sustain_s=0.0):
     """W warm-up steps (+ the same step repeated untimed for sustain_s seconds), then exactly `steps` steps between two
     CUDA events on the launch stream, bracketed by barrier + synchronize; max over ranks.  Returns ms per step."""
+    if dist is not None:
+        dist.barrier()                                   # ranks enter a leg together (a step may wait for its peers)
     for i in range(warmup):
         fn(i)
     torch.cuda.synchronize()
@@ -221,6 +223,7 @@ class DecodeWorkload:
         self.plan = (ns, ch)
         self.ws = K.Workspace(self.B, w["Hkv"], self.B * w["Hkv"] * (ns + 1), dev)
         self.dist = None
+        self.xchg = None
 
     def build(self, seed):
         """synthetic inputs of the named shape and the quantised caches (written by the library's own dynamic writer, which
@@ -300,7 +303,11 @@ class DecodeWorkload:
         tkw = self._attn_args(c) if first else {}
         K.attn_partial(self.q, self.pools[c], self.bts[c], self.seq, self.part, ns, ch, self.ws, LOG2E * SCALE, w["kind"], page=P,
                        kv_start=w["S"] if first else 0, **tkw)
-        if self.dist is not None:
+        if self.dist is not None and self.a.kvseq_exchange == "p2p":
+            if self.xchg is None:                          # set-up on the first (uncaptured) step: buffers + IPC handles
+                self.xchg = K.ShardExchange(self.rank, self.world, self.part.shape[0] * self.part.shape[1], self.dist)
+            self.xchg.merge(self.part, self.out)           # one kernel: push to the peers, wait, merge
+        elif self.dist is not None:
             self.dist.all_gather_into_tensor(self.parts.view(-1, *self.part.shape[1:]), self.part)
             K.merge_partials_into(self.parts, self.out)
         else:
@@ -353,12 +360,15 @@ class DecodeWorkload:
     def config(self):
         w, world = self.w, self.world
         par = {"replica": f"batch replicas x{world}, no collective", "batch": f"batch-sharded x{world} ({self.B} rows per rank), no collective",
-               "kvseq": f"kv-sequence sharded x{world}, NCCL all-gather of (o, m, l) rows + LSE merge"}[w["shard"]]
+               "kvseq": (f"kv-sequence sharded x{world}, (o, m, l) rows pushed to the peers and merged by one kernel over peer memory"
+                         if self.a.kvseq_exchange == "p2p" else
+                         f"kv-sequence sharded x{world}, NCCL all-gather of (o, m, l) rows + LSE merge")}[w["shard"]]
         return {"batch_per_gpu": self.B, "nsplit": self.plan[0], "chunk": self.plan[1],
                 "l2": f"{self.ncopy} distinct {self.pools[0].numel() >> 20} MiB pools cycled "
                       f"({self.ncopy * self.pools[0].numel() >> 20} MiB in all, more than the 126 MB L2)",
                 "parallelism": par if world > 1 else "single gpu",
-                "step": ("fr_cb_write (last rank) + fr_attn_partial + all-gather + fr_merge_partials" if self.kvseq
+                "step": (("fr_cb_write (last rank) + fr_attn_partial + fr_xchg_merge" if self.a.kvseq_exchange == "p2p" and self.world > 1
+                          else "fr_cb_write (last rank) + fr_attn_partial + all-gather + fr_merge_partials") if self.kvseq
                          else "fr_cb_write (T = batch) + fr_cb_attn")}
 
     def status(self):
@@ -851,6 +861,9 @@ def main():
     ap.add_argument("--no-step-graph", action="store_true", help="resident step: separate launches from Python instead of a CUDA graph")
     ap.add_argument("--batch", type=int, default=0, help="override the workload's batch (requests for cfg5a): smaller cases for "
                                                          "profiler captures; the line's config names the batch actually run")
+    ap.add_argument("--kvseq-exchange", default="p2p", choices=["p2p", "nccl"],
+                    help="kv-sequence shard: partial rows exchanged and merged by one kernel over peer memory (fr_xchg_merge) or "
+                         "by an NCCL all-gather + fr_merge_partials")
     ap.add_argument("--race", action="store_true", help="also time the reference's own sm_100a-capable kernel on the same pools (cfg4)")
     a = ap.parse_args()
     w = dict(WORKLOADS[a.workload])
@@ -922,6 +935,8 @@ def main():
     ms = timed(run_res, a.steps, a.warmup, dist, a.sustain_s)
     clocks = sampler.stop() if rank == 0 else None
     ms_e2e = timed(lambda i: wl.e2e(i % nc), a.steps, a.warmup, dist, min(a.sustain_s, 0.2))
+    if dist is not None:
+        dist.barrier()
     wl.resident(0)                                          # (prefill: the kernel-only loop reuses the staged q)
     ms_burst = timed(lambda i: wl.kernel(i % nc), a.steps, a.warmup, None)
     ms_k, n_k, clk_k = sustained(lambda i: wl.kernel(i % nc), ms_burst, a.sustain_s, local)

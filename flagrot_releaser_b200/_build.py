@@ -21,7 +21,7 @@ ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 FLAGS = ["-O3", "-std=c++17", *ARCH, "--expt-relaxed-constexpr", "-lineinfo", "-Xcompiler", "-fPIC", f"-I{CSRC}"]
 
 LIBS = {
-    "libflagrot_kernels.so": ["fr_capi.cu", "fr_writer.cu", "fr_decode.cu", "fr_dequant.cu"],
+    "libflagrot_kernels.so": ["fr_capi.cu", "fr_writer.cu", "fr_decode.cu", "fr_dequant.cu", "fr_xchg.cu"],
     "libflagrot_kivi.so": ["kv_capi.cu"],
     "libflagrot_mq.so": ["mq_capi.cu"],
     # test-only: known-answer kernels for the tcgen05 primitives of csrc/fr_tc5.cuh (not part of any C ABI)

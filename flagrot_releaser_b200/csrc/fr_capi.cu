@@ -7,6 +7,7 @@
 // -4 unknown format / kind, -5 page size, -8 head dim.  Formats built here: int4a (5), int2a (8), konlya (7 / kind 10),
 // konlya2 (9 / kind 11); the symmetric INT4 formats and the ablation codebooks answer -4.
 #include <cstdint>
+#include <cstring>
 #include <cstdio>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
@@ -194,7 +195,9 @@ int fr_dequant_pages(int fmt, const uint8_t* pool, const int* bt_row, int start,
 
 int fr_device_status() {
   const int d = fr::decode_status();
-  return d != 0 ? d : fr::writer_status();
+  if (d != 0) return d;
+  const int w = fr::writer_status();
+  return w != 0 ? w : fr::xchg_status();
 }
 
 }  // extern "C"
@@ -240,6 +243,40 @@ int fr_merge_partials(const float* parts, int R, int rows, void* out, int out_fp
   if (rows <= 0 || R <= 0) return 0;
   k_merge_partials<<<(rows + 3) / 4, 128, 0, static_cast<cudaStream_t>(stream)>>>(parts, R, rows, out, out_fp32);
   return cudaPeekAtLastError() == cudaSuccess ? 0 : -1;
+}
+
+// ---- KV-sequence shards: exchange + merge over peer memory (csrc/fr_xchg.cu)
+long long fr_xchg_bytes(int rows) { return static_cast<long long>(fr::xchg_bytes(rows)); }
+
+int fr_xchg_alloc(int rows, void** ptr, void* handle64) {
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "the handle travels as 64 bytes");
+  void* d = nullptr;
+  const size_t n = fr::xchg_bytes(rows);
+  if (cudaMalloc(&d, n) != cudaSuccess) return -1;
+  if (cudaMemset(d, 0, n) != cudaSuccess || cudaDeviceSynchronize() != cudaSuccess ||
+      cudaIpcGetMemHandle(static_cast<cudaIpcMemHandle_t*>(handle64), d) != cudaSuccess) {
+    cudaFree(d);
+    return -1;
+  }
+  *ptr = d;
+  return 0;
+}
+
+int fr_xchg_open(const void* handle64, void** ptr) {
+  cudaIpcMemHandle_t h;
+  std::memcpy(&h, handle64, sizeof(h));
+  return cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess) == cudaSuccess ? 0 : -1;
+}
+
+int fr_xchg_close(void* ptr) { return cudaIpcCloseMemHandle(ptr) == cudaSuccess ? 0 : -1; }
+int fr_xchg_free(void* ptr) { return cudaFree(ptr) == cudaSuccess ? 0 : -1; }
+
+int fr_xchg_merge(const float* part, void* const* bufs, int rank, int R, int rows, void* out, int out_fp32, void* stream) {
+  return fr::xchg_launch(part, bufs, rank, R, rows, out, out_fp32, static_cast<cudaStream_t>(stream));
+}
+
+int fr_xchg_selftest(const float* const* parts, void* const* bufs, int R, int rows, void* const* outs, int out_fp32, void* stream) {
+  return fr::xchg_selftest_launch(parts, bufs, R, rows, outs, out_fp32, static_cast<cudaStream_t>(stream));
 }
 
 // ---- decode attention for callers that may not allocate device memory

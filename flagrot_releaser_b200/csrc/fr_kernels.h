@@ -40,6 +40,11 @@ struct DecodeParams {
 };
 int decode_launch(const DecodeParams& p, cudaStream_t st);
 int decode_occupancy(int nb, int key_only);
+// exchange + merge of KV-sequence shard partials over peer memory (fr_xchg.cu)
+size_t xchg_bytes(int rows);
+int xchg_launch(const float* part, void* const* bufs, int rank, int R, int rows, void* out, int out_fp32, cudaStream_t st);
+int xchg_selftest_launch(const float* const* parts, void* const* bufs, int R, int rows, void* const* outs, int out_fp32, cudaStream_t st);
+int xchg_status();     // 0, or the source line of the peer wait that gave up (sticky)
 int writer_status();   // 0, or the source line of the staging wait that gave up (sticky; results stay correct)
 int decode_status();   // 0, or the source line of a bounded wait that gave up (sticky)
 

@@ -75,9 +75,17 @@ def lib():
     L.fr_attn_partial.argtypes = [I, P, LL, P, P, I, P, I, I, I, I, I, F, P, P, P, P, P, P, P, P, P, LL, LL, P, I, I]
     L.fr_merge_partials.argtypes = [P, I, I, P, I, P]
     L.fr_dequant_pages.argtypes = [I, P, P, I, I, I, I, P, P, P, P, P, P, I, P]
+    L.fr_xchg_bytes.argtypes, L.fr_xchg_bytes.restype = [I], LL
+    L.fr_xchg_alloc.argtypes = [I, ctypes.POINTER(P), ctypes.c_char_p]
+    L.fr_xchg_open.argtypes = [ctypes.c_char_p, ctypes.POINTER(P)]
+    L.fr_xchg_close.argtypes = [P]
+    L.fr_xchg_free.argtypes = [P]
+    L.fr_xchg_merge.argtypes = [P, ctypes.POINTER(P), I, I, I, P, I, P]
+    L.fr_xchg_selftest.argtypes = [ctypes.POINTER(P), ctypes.POINTER(P), I, I, ctypes.POINTER(P), I, P]
     for n in ("fr_v2_attn", "fr_v2_write", "fr_v2_occupancy", "fr_v2_chunk_bytes", "fr_cb_write", "fr_cb_attn",
               "fr_cb_occupancy", "fr_cb_chunk_bytes", "fr_cb_nsg", "fr_head_fwht", "fr_cb_write3",
               "fr_w3_static_write", "fr_cb_write_smem", "fr_attn_partial", "fr_device_status", "fr_cb_attn_noalloc", "fr_merge_partials",
+              "fr_xchg_alloc", "fr_xchg_open", "fr_xchg_close", "fr_xchg_free", "fr_xchg_merge", "fr_xchg_selftest",
               "fr_dequant_pages"):
         getattr(L, n).restype = I
     _LIB = L
@@ -471,6 +479,69 @@ def merge_partials_into(parts: torch.Tensor, out: torch.Tensor):
     _check(lib().fr_merge_partials(parts.data_ptr(), R, B * Hq, out.data_ptr(), int(out.dtype == torch.float32), _stream()),
            "fr_merge_partials")
     return out
+
+
+class ShardExchange:
+    """Exchange + merge of KV-sequence shard partials over peer memory (fr_xchg_merge): every rank of the node owns one
+    exchange buffer, maps the others' through CUDA IPC, and one kernel per rank pushes its partial rows [rows, 130] to every
+    peer, waits (bounded) for theirs and merges.  Collective: all ranks call merge() the same number of times.  `dist` is
+    torch.distributed (any backend: it only carries the 64-byte handles at set-up)."""
+
+    def __init__(self, rank: int, world: int, rows: int, dist):
+        assert 1 <= world <= 8 and 1 <= rows <= 1024
+        self.rank, self.world, self.rows = rank, world, rows
+        L = lib()
+        own = ctypes.c_void_p()
+        handle = ctypes.create_string_buffer(64)
+        _check(L.fr_xchg_alloc(rows, ctypes.byref(own), handle), "fr_xchg_alloc")
+        self.own = own.value
+        handles = [None] * world
+        dist.all_gather_object(handles, handle.raw)
+        self.ptrs = (ctypes.c_void_p * world)()
+        self.opened = []
+        for r in range(world):
+            if r == rank:
+                self.ptrs[r] = self.own
+                continue
+            p = ctypes.c_void_p()
+            _check(L.fr_xchg_open(handles[r], ctypes.byref(p)), "fr_xchg_open")
+            self.ptrs[r] = p.value
+            self.opened.append(p.value)
+        dist.barrier()
+
+    def merge(self, part: torch.Tensor, out: torch.Tensor):
+        """part fp32 [B, Hq, 130] of this rank -> out [B, Hq * 128] bf16 | fp32: the merge over all ranks' partials"""
+        assert part.dtype == torch.float32 and part.is_contiguous() and part.numel() == self.rows * 130
+        assert out.is_contiguous() and out.numel() == self.rows * 128 and out.dtype in (torch.bfloat16, torch.float32)
+        _check(lib().fr_xchg_merge(part.data_ptr(), self.ptrs, self.rank, self.world, self.rows, out.data_ptr(),
+                                   int(out.dtype == torch.float32), _stream()), "fr_xchg_merge")
+        return out
+
+    def close(self):
+        L = lib()
+        for p in self.opened:
+            L.fr_xchg_close(p)
+        self.opened = []
+        if self.own:
+            L.fr_xchg_free(self.own)
+            self.own = None
+
+
+def xchg_selftest(parts, outs):
+    """R emulated ranks on ONE device as one cooperative launch: parts[r] fp32 [rows, 130] -> outs[r] [rows, 128]; every
+    rank must end with the same merge.  Returns the exchange buffers (keep them to run further steps on the same buffers)."""
+    L = lib()
+    R, rows = len(parts), parts[0].shape[0]
+    n = L.fr_xchg_bytes(rows)
+    bufs = [torch.zeros(n, dtype=torch.uint8, device=parts[0].device) for _ in range(R)]
+    return xchg_selftest_step(parts, outs, bufs), bufs
+
+
+def xchg_selftest_step(parts, outs, bufs):
+    L = lib()
+    R, rows = len(parts), parts[0].shape[0]
+    arr = lambda ts: (ctypes.c_void_p * R)(*[t.data_ptr() for t in ts])  # noqa: E731
+    return L.fr_xchg_selftest(arr(parts), arr(bufs), R, rows, arr(outs), int(outs[0].dtype == torch.float32), _stream())
 
 
 def dequant_pages(pool, bt_row, start, n, fmt, page=16, dtype=torch.bfloat16, kmask=None, vmask=None, kfull=None, vfull=None):

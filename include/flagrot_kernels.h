@@ -119,6 +119,27 @@ int fr_dequant_pages(int fmt, const uint8_t* pool, const int* bt_row, int start,
                      const uint8_t* vmask, const uint8_t* kfull, const uint8_t* vfull, void* ok, void* ov, int out_fp32,
                      void* stream);
 
+/* No counterpart in the reference.  KV-sequence shards on the GPUs of one node: exchange of the partial rows written by
+ * fr_attn_partial over peer memory and their merge, one kernel per rank instead of an all-gather collective plus
+ * fr_merge_partials.  Every rank allocates one exchange buffer (fr_xchg_alloc: device memory of fr_xchg_bytes(rows) bytes,
+ * zeroed, and its 64-byte CUDA IPC handle), hands the handle to the other ranks (any host channel) and maps theirs
+ * (fr_xchg_open).  fr_xchg_merge(part, bufs, rank, R, rows, out, ...): part fp32 [rows, 130] of this rank, bufs = HOST array
+ * of the R buffers as mapped in this process (bufs[rank] the own one), R <= 8, rows <= 1024 -> out [rows, 128] bf16 (fp32
+ * when out_fp32) = the merge over all ranks.  Collective semantics: every rank makes the same sequence of calls on the
+ * buffers; the step counters live in the buffers, so a captured launch replays correctly.  The wait for the peers' rows is
+ * bounded (about nine seconds: a peer's launch may trail by host time); if it runs out, fr_device_status reports it and the
+ * output must be discarded.
+ * fr_xchg_selftest runs the same protocol for R emulated ranks on ONE device as one cooperative launch (parts / bufs / outs:
+ * host arrays of R device pointers). */
+long long fr_xchg_bytes(int rows);
+int fr_xchg_alloc(int rows, void** ptr, void* handle64);
+int fr_xchg_open(const void* handle64, void** ptr);
+int fr_xchg_close(void* ptr);
+int fr_xchg_free(void* ptr);
+int fr_xchg_merge(const float* part, void* const* bufs, int rank, int R, int rows, void* out, int out_fp32, void* stream);
+int fr_xchg_selftest(const float* const* parts, void* const* bufs, int R, int rows, void* const* outs, int out_fp32,
+                     void* stream);
+
 /* 0, or the source line of a bounded device-side wait that gave up (sticky; synchronises the device). */
 int fr_device_status(void);
 
