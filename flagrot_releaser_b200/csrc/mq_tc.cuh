@@ -10,9 +10,10 @@
 //               of the P operand columns, and the row sum.  The reference is lazy: it only moves when the maximum grew by
 //               more than 2^8 (p stays <= 256), so the O accumulator is rescaled a few times per item, not per block;
 //   warps 4-19  conversion: raw page chunks -> FP16 operand tiles in shared memory (128-byte swizzle, K-major):
-//               K [64 keys][128 dims] as (code - zero point) * scale, exact in FP16, one rounding; V^T [128 dims][64 keys];
+//               K [64 keys][128 dims] as (code - zero point) * scale, exact in FP16, one rounding (warps 4-11);
+//               V^T [128 dims][64 keys] (warps 12-19); the two run side by side, each on its own hand-over barriers;
 //   warp 24     issues the MMAs (lane 0; the whole warp waits) and owns the tensor-memory allocation;
-//   warp 25     bulk-copies the four page chunks of a block into a 3-stage ring.
+//   warp 25     bulk-copies the four page chunks of a block into a 6-stage ring.
 // Key-only pages (per-token rotation flags) are not rotated back per token: the kernel keeps Q in three bases (identity,
 // per-group H32, whole-head H128) in tensor memory, the conversion drops each (key, group) into the operand tile of its
 // base and zeros into the other two, and S accumulates the three products - three times the QK tensor work, which the
@@ -25,9 +26,10 @@
 constexpr int TQ_THREADS = 832;       // 26 warps
 constexpr int TQ_SOFT = 128;          // query rows = softmax threads per column half
 constexpr int TQ_CONV = 512;          // conversion threads (warps 4 .. 19)
+constexpr int TQ_CONVH = 256;         // ... of which warps 4 .. 11 convert K tiles and warps 12 .. 19 V tiles
 constexpr int TQ_WSOFTB = 20;         // warps 20 .. 23: the second softmax thread of every row (warps 0 .. 3: the first)
 constexpr int TQ_WMMA = 24, TQ_WLOAD = 25;
-constexpr int TQ_RAWST = 3;
+constexpr int TQ_RAWST = 6;          // stages of the raw page ring: a block's chunks arrive about 1.5 us after they are asked for
 __device__ int g_mq_status;
 
 template <int NB, int NBASE> struct TQMap {
@@ -35,10 +37,10 @@ template <int NB, int NBASE> struct TQMap {
   static constexpr int KT = 0;                                   // [2 buffers][NBASE][2 dim halves][64 rows][128 B]
   static constexpr int KT_TILE = 16384;
   static constexpr int VT = KT + 2 * NBASE * KT_TILE;            // [2 buffers][128 rows][128 B]
-  static constexpr int RAW = VT + 2 * 16384;                     // [3][4 pages][CHUNK]
+  static constexpr int RAW = VT + 2 * 16384;                     // [TQ_RAWST][4 pages][CHUNK]
   static constexpr int RAW_STAGE = PPB * CHUNK;
   static constexpr int BAR = RAW + TQ_RAWST * RAW_STAGE;         // mbarriers
-  static constexpr int NBAR = 3 + 3 + 2 + 2 + 2 + 2 + 2 + 2 + 1 + 1 + 1;
+  static constexpr int NBAR = 2 * TQ_RAWST + 2 + 2 + 2 + 2 + 2 + 2 + 1 + 1 + 1;
   static constexpr int MISC = BAR + NBAR * 8;
   static constexpr int XCH = MISC + 16;                          // softmax pair exchange: float [2][2][128] maxima, [128] sums
   static constexpr int TOTAL = XCH + 5 * 128 * 4 + 1024;         // + slack for the 1024-byte alignment of the tiles
@@ -76,8 +78,8 @@ FR_DEVI void tq_convert_k(uint32_t raw, uint32_t kt, int nvalid, int ctid, bool 
   using L = MLay<NB>;
   constexpr uint32_t FM = NB == 4 ? 0x000F000Fu : 0x00030003u;
 #pragma unroll
-  for (int it = 0; it < (BN * 8) / TQ_CONV; ++it) {
-    const int item = ctid + TQ_CONV * it, tok = item >> 3, tgp = (item >> 2) & 1, j = item & 3;
+  for (int it = 0; it < (BN * 8) / TQ_CONVH; ++it) {
+    const int item = ctid + TQ_CONVH * it, tok = item >> 3, tgp = (item >> 2) & 1, j = item & 3;
     const int pos = tok & 15;
     const uint32_t rc = raw + (tok >> 4) * L::CHUNK;
     const uint32_t dlo = (j >> 1) * 8192 + tc5::sw128_off(tok, 4 * (j & 1) + tgp);
@@ -144,8 +146,8 @@ FR_DEVI void tq_convert_v(uint32_t raw, uint32_t vt, int nvalid, int ctid) {
   using L = MLay<NB>;
   constexpr uint32_t NM = NB == 4 ? 0x0F0F0F0Fu : 0x03030303u;
 #pragma unroll
-  for (int it = 0; it < (PPB * 64 * 2) / TQ_CONV; ++it) {
-    const int item = ctid + TQ_CONV * it;
+  for (int it = 0; it < (PPB * 64 * 2) / TQ_CONVH; ++it) {
+    const int item = ctid + TQ_CONVH * it;
     const int pg = item >> 7, e = (item >> 1) & 63, m = item & 1;
     const int c8 = e & 1, gid = (e >> 1) & 7, w = e >> 4;
     const int d0 = 64 * m + 16 * w + gid, j = 2 * m + (w >> 1);
@@ -232,15 +234,16 @@ __global__ void __launch_bounds__(TQ_THREADS, 1) k_mq_tc(const MqParams p) {
 
   // ---- barriers, tensor memory
   const uint32_t bar = sb + S::BAR;
-  const uint32_t b_rawf = bar, b_rawe = bar + 24, b_kf = bar + 48, b_ke = bar + 64, b_vf = bar + 80, b_ve = bar + 96;
-  const uint32_t b_sf = bar + 112, b_pf = bar + 128, b_od = bar + 144, b_q = bar + 152, b_fin = bar + 160;
+  const uint32_t b_rawf = bar, b_rawe = bar + 8 * TQ_RAWST, bb = bar + 16 * TQ_RAWST;
+  const uint32_t b_kf = bb, b_ke = bb + 16, b_vf = bb + 32, b_ve = bb + 48;
+  const uint32_t b_sf = bb + 64, b_pf = bb + 80, b_od = bb + 96, b_q = bb + 104, b_fin = bb + 112;
   volatile uint32_t* misc = reinterpret_cast<volatile uint32_t*>(smem + S::MISC);
   volatile uint32_t* abortf = misc + 1;
   if (tid == 0) {
-    for (int i = 0; i < 3; ++i) { tc5::mbar_init(b_rawf + 8 * i, 1); tc5::mbar_init(b_rawe + 8 * i, TQ_CONV); }
+    for (int i = 0; i < TQ_RAWST; ++i) { tc5::mbar_init(b_rawf + 8 * i, 1); tc5::mbar_init(b_rawe + 8 * i, TQ_CONV); }
     for (int i = 0; i < 2; ++i) {
-      tc5::mbar_init(b_kf + 8 * i, TQ_CONV); tc5::mbar_init(b_ke + 8 * i, 1);
-      tc5::mbar_init(b_vf + 8 * i, TQ_CONV); tc5::mbar_init(b_ve + 8 * i, 1);
+      tc5::mbar_init(b_kf + 8 * i, TQ_CONVH); tc5::mbar_init(b_ke + 8 * i, 1);
+      tc5::mbar_init(b_vf + 8 * i, TQ_CONVH); tc5::mbar_init(b_ve + 8 * i, 1);
       tc5::mbar_init(b_sf + 8 * i, 1); tc5::mbar_init(b_pf + 8 * i, 2 * TQ_SOFT);
     }
     tc5::mbar_init(b_od, 1);
@@ -400,30 +403,32 @@ __global__ void __launch_bounds__(TQ_THREADS, 1) k_mq_tc(const MqParams p) {
       if (rval && hf == 0) *reinterpret_cast<float2*>(p.ml + (pbase + r) * 2) = make_float2(mref, lsum + xsum[r]);
     }
     tc5::fence_before_sync();
-  } else if (warp >= 4 && warp < 4 + TQ_CONV / 32) {
-    // =========================================================================== conversion warps
+  } else if (warp >= 4 && warp < 4 + TQ_CONVH / 32) {
+    // =========================================================================== K conversion warps (two items per thread)
     const int ctid = tid - TQ_SOFT;
     tq_wait_relaxed(b_q, 0, abortf);          // the q staging (which lies over the operand tiles) has been read
     uint32_t prev = 0;
-    // K runs one block ahead of V: K(j + 1) only needs QK(j - 1) to be done, while V(j) has to wait for PV(j - 2), which
-    // hangs on the softmax - so the next scores can be under way while the softmax still holds the V tile back
-    auto conv_k = [&](int j) {
-      const int buf = j & 1, rs = j % TQ_RAWST;
-      tq_wait_relaxed(b_rawf + 8 * rs, (j / TQ_RAWST) & 1, abortf);
-      if (j >= 2) tq_wait_relaxed(b_ke + 8 * buf, ((j >> 1) - 1) & 1, abortf);
-      tq_convert_k<NB, KO>(sb + S::RAW + rs * S::RAW_STAGE, sb + S::KT + buf * NBASE * S::KT_TILE, kend - (kblk0 + j) * BN, ctid,
-                           j < 2, buf, prev);
-    };
-    conv_k(0);
-    tc5::fence_async_smem();
-    tc5::mbar_arrive(b_kf);
     for (int j = 0; j < nblk; ++j) {
       const int buf = j & 1, rs = j % TQ_RAWST;
-      if (j + 1 < nblk) conv_k(j + 1);
-      if (j >= 2) tq_wait_relaxed(b_ve + 8 * buf, ((j >> 1) - 1) & 1, abortf);
+      tq_wait_relaxed(b_rawf + 8 * rs, (j / TQ_RAWST) & 1, abortf);
+      if (j >= 2) tq_wait_relaxed(b_ke + 8 * buf, ((j >> 1) - 1) & 1, abortf);     // QK(j - 2) has read this tile buffer
+      tq_convert_k<NB, KO>(sb + S::RAW + rs * S::RAW_STAGE, sb + S::KT + buf * NBASE * S::KT_TILE, kend - (kblk0 + j) * BN, ctid,
+                           j < 2, buf, prev);
+      tc5::fence_async_smem();
+      tc5::mbar_arrive(b_kf + 8 * buf);
+      tc5::mbar_arrive(b_rawe + 8 * rs);
+    }
+  } else if (warp >= 4 + TQ_CONVH / 32 && warp < 4 + TQ_CONV / 32) {
+    // =========================================================================== V conversion warps (two items per thread)
+    // K and V tiles of a block are produced side by side: a block costs the longer of the two conversions, not their sum
+    const int ctid = tid - TQ_SOFT - TQ_CONVH;
+    tq_wait_relaxed(b_q, 0, abortf);
+    for (int j = 0; j < nblk; ++j) {
+      const int buf = j & 1, rs = j % TQ_RAWST;
+      tq_wait_relaxed(b_rawf + 8 * rs, (j / TQ_RAWST) & 1, abortf);
+      if (j >= 2) tq_wait_relaxed(b_ve + 8 * buf, ((j >> 1) - 1) & 1, abortf);     // PV(j - 2) has read this tile buffer
       tq_convert_v<NB>(sb + S::RAW + rs * S::RAW_STAGE, sb + S::VT + buf * 16384, kend - (kblk0 + j) * BN, ctid);
-      tc5::fence_async_smem();                 // one fence for the K tile of the next block and the V tile of this one
-      if (j + 1 < nblk) tc5::mbar_arrive(b_kf + 8 * (buf ^ 1));
+      tc5::fence_async_smem();
       tc5::mbar_arrive(b_vf + 8 * buf);
       tc5::mbar_arrive(b_rawe + 8 * rs);
     }
