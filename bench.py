@@ -320,6 +320,15 @@ class DecodeWorkload:
                   kv_start=w["S"], **self._attn_args(c))
 
     def e2e(self, c):
+        if self.a.e2e_launch == "graph" and not (self.kvseq and self.world > 1):
+            # the whole step - copies in, append, decode, copy back - as ONE graph launch (graphs.HostStep)
+            hs = self.__dict__.setdefault("hsteps", {})
+            if c not in hs:
+                from flagrot_releaser_b200.graphs import HostStep
+                hs[c] = HostStep([(self.q, self.q_host), (self.kv, self.kv_host), (self.slots[c], self.slots_host[c])],
+                                 lambda: self.resident(c), [(self.out_host, self.out)])
+            hs[c].run()
+            return
         self.q.copy_(self.q_host, non_blocking=True)
         if not self.kvseq or self.rank == self.world - 1:
             self.kv.copy_(self.kv_host, non_blocking=True)
@@ -864,6 +873,9 @@ def main():
     ap.add_argument("--kvseq-exchange", default="p2p", choices=["p2p", "nccl"],
                     help="kv-sequence shard: partial rows exchanged and merged by one kernel over peer memory (fr_xchg_merge) or "
                          "by an NCCL all-gather + fr_merge_partials")
+    ap.add_argument("--e2e-launch", default="calls", choices=["calls", "graph"],
+                    help="e2e leg of the decode workloads: copies issued from Python around the step graph, or copies + step as one "
+                         "graph launch (graphs.HostStep)")
     ap.add_argument("--race", action="store_true", help="also time the reference's own sm_100a-capable kernel on the same pools (cfg4)")
     a = ap.parse_args()
     w = dict(WORKLOADS[a.workload])
@@ -974,8 +986,9 @@ def main():
         "warmup": a.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak" if w["shard"] == "replica" else "strong",
         "vs_baseline": None, "dtype": "f16" if wl.bound == "tensor" else "u8", "data": "synthetic", "config": cfg,
         "e2e": {"value": wl.job_units() / (ms_e2e * 1e-3) / scale, "unit": unit, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                "ms_per_step": ms_e2e, "launch": "copies from Python, the step as one CUDA graph" if use_graph
-                else "separate launches from Python"},
+                "ms_per_step": ms_e2e, "launch": ("copies in, step and copy back as one CUDA graph" if getattr(wl, "hsteps", None)
+                                                   else "copies from Python, the step as one CUDA graph" if use_graph
+                                                   else "separate launches from Python")},
         "gpu_launches": wl.launches * a.steps,
         "roofline": {"bound": wl.bound, "achieved": ach, "peak": peak, "unit": unit, "frac": ach / peak, "traffic": traffic,
                      "kernel": wl.kernel_name, "peak_source": which + (" (sustained dense bf16)" if wl.bound == "tensor" else " (copy)"),

@@ -13,7 +13,7 @@
 # prebuilt files).
 set -euo pipefail
 HERE="$(cd "$(dirname "${BASH_SOURCE[0]}")" && pwd)"
-REF="${REF:-/root/reference}"
+REF="${REF:-${FLAGROT_REFERENCE:-$HERE/../../reference}}"      # default: a checkout named "reference" beside this repository
 OUT="$HERE/_ref"
 [ -d "$REF/kernels/csrc" ] || { echo "reference tree not found at $REF: keeping prebuilt oracle/_ref"; exit 0; }
 mkdir -p "$OUT"

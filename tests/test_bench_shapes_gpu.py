@@ -17,7 +17,7 @@ from oracle import kivi_oracle as KO
 from tests._util import bits
 
 pytestmark = pytest.mark.gpu
-ARGS = argparse.Namespace(ncopy=1, nsplit=0, kvseq_exchange="p2p")
+ARGS = argparse.Namespace(ncopy=1, nsplit=0, kvseq_exchange="p2p", e2e_launch="calls")
 
 
 def _bounds(got, ref, what):

@@ -19,7 +19,7 @@ def test_host_step_replay_matches_separate_launches():
     torch.cuda.set_device(dev)
     import argparse
     w = dict(bench.WORKLOADS["cfg2"], B=3, L=768)
-    st = bench.DecodeWorkload(w, 0, 1, dev, argparse.Namespace(ncopy=1, nsplit=0, kvseq_exchange="p2p"))
+    st = bench.DecodeWorkload(w, 0, 1, dev, argparse.Namespace(ncopy=1, nsplit=0, kvseq_exchange="p2p", e2e_launch="calls"))
     st.resident(0)                                      # first calls outside the capture
     torch.cuda.synchronize()
     hs = HostStep([(st.q, st.q_host), (st.kv, st.kv_host), (st.slots[0], st.slots_host[0])],
