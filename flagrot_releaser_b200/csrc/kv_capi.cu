@@ -19,7 +19,7 @@
 // Flags sit in the sign bits of the non-negative scales: key sub-vector j -> cell j slot 0, key whole head -> cell 4 slot 0,
 // the VALUE whole-head flag of the token in cell i -> key scale of cell i slot 3 (set by the value writer, kept by the key
 // encoder).  Every kernel is templated on the page kind; f8 bit 1 (the reference's "fast" kernel variants, same values)
-// selects nothing here.  Head dim 256 and the matrix-weighted value selection answer code 2 with a message.
+// selects nothing here.  Head dim 256 answers code 2 with a message.
 #include <cmath>
 #include <cstdint>
 #include <cstdio>
@@ -90,7 +90,9 @@ FR_DEVI void hada_row(float (&v)[4], int lane, int n) {
 template <bool F8>
 __global__ void __launch_bounds__(128) k_v_write(const __nv_bfloat16* __restrict__ kv, long long kv_rs, int n, int Hkv,
                                                  const long long* __restrict__ slots, const float* __restrict__ co,
-                                                 uint8_t* __restrict__ pool, int ident, const int* __restrict__ vfix) {
+                                                 const float* __restrict__ M, uint8_t* __restrict__ pool, int ident,
+                                                 const int* __restrict__ vfix) {
+  __shared__ float esh[4][3][D];            // matrix weighting: the warp's error vectors (I, H32, whole head)
   const int lane = threadIdx.x & 31;
   const long long item = static_cast<long long>(blockIdx.x) * 4 + (threadIdx.x >> 5);
   if (item >= static_cast<long long>(n) * Hkv) return;
@@ -122,6 +124,60 @@ __global__ void __launch_bounds__(128) k_v_write(const __nv_bfloat16* __restrict
   if (!ident && vfix != nullptr) {   // frozen choice of this kv head: bits 0..3 = H32 per sub-vector, bit 16 = whole head
     useF = (vfix[h] >> 16) & 1;
     cand = useF ? 2 : ((vfix[h] >> (lane >> 3)) & 1);
+  } else if (!ident && M != nullptr) {
+    // weighting by a full matrix M [Hkv, D, D] (e^T M e): the I / H32 errors of a sub-vector use its diagonal 32 x 32 block,
+    // the whole-head error and the error of the chosen combination the whole matrix (reference kivi.cu:222-275; sums in
+    // the reference's order, products contracted as its compiler contracts them)
+    const int wp = threadIdx.x >> 5, jb = lane >> 3;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      esh[wp][0][4 * lane + i] = __fsub_rn(rec[0][i], x[i]);
+      esh[wp][1][4 * lane + i] = __fsub_rn(rec[1][i], x[i]);
+      esh[wp][2][4 * lane + i] = __fsub_rn(rec[2][i], x[i]);
+    }
+    __syncwarp();
+    const float* Mh = M + static_cast<long long>(h) * D * D;
+    float eI = 0.f, eH = 0.f, eF = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int r = 4 * lane + i;
+      const float* row = Mh + static_cast<long long>(r) * D;
+      float a0 = 0.f, a1 = 0.f, a2 = 0.f;
+      for (int k = jb * 32; k < jb * 32 + 32; ++k) {
+        const float m = row[k];
+        a0 = fmaf(m, esh[wp][0][k], a0);
+        a1 = fmaf(m, esh[wp][1][k], a1);
+      }
+      for (int k = 0; k < D; ++k) a2 = fmaf(row[k], esh[wp][2][k], a2);
+      eI = fmaf(esh[wp][0][r], a0, eI);
+      eH = fmaf(esh[wp][1][r], a1, eH);
+      eF = fmaf(esh[wp][2][r], a2, eF);
+    }
+#pragma unroll
+    for (int m = 1; m < 8; m <<= 1) {
+      eI = __fadd_rn(eI, __shfl_xor_sync(FULLMASK, eI, m));
+      eH = __fadd_rn(eH, __shfl_xor_sync(FULLMASK, eH, m));
+    }
+#pragma unroll
+    for (int m = 1; m < 32; m <<= 1) eF = __fadd_rn(eF, __shfl_xor_sync(FULLMASK, eF, m));
+    const bool useH = eH < eI;
+    __syncwarp();
+#pragma unroll
+    for (int i = 0; i < 4; ++i) esh[wp][0][4 * lane + i] = useH ? esh[wp][1][4 * lane + i] : esh[wp][0][4 * lane + i];
+    __syncwarp();
+    float a = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int r = 4 * lane + i;
+      const float* row = Mh + static_cast<long long>(r) * D;
+      float sacc = 0.f;
+      for (int k = 0; k < D; ++k) sacc = fmaf(row[k], esh[wp][0][k], sacc);
+      a = fmaf(esh[wp][0][r], sacc, a);
+    }
+#pragma unroll
+    for (int m = 1; m < 32; m <<= 1) a = __fadd_rn(a, __shfl_xor_sync(FULLMASK, a, m));
+    useF = eF < a;
+    cand = useF ? 2 : (useH ? 1 : 0);
   } else if (!ident) {
     const float4 cw4 = *reinterpret_cast<const float4*>(co + static_cast<long long>(h) * D + 4 * lane);
     const float cw[4] = {cw4.x, cw4.y, cw4.z, cw4.w};
@@ -579,15 +635,16 @@ int kv_v_write(const void* kv, long long kv_rs, int n, int Hkv, int Dd, const vo
                void* pool, int ident, const void* vfix, int f8, void* stream) {
   if (n <= 0) return 0;
   if (Dd != D) return fail("kv_v_write: D %d (head dim 128 only)", Dd);
-  if (M != nullptr && !ident && vfix == nullptr) return fail("kv_v_write: matrix-weighted selection (M) is not built");
   const unsigned blocks = static_cast<unsigned>((static_cast<long long>(n) * Hkv + 3) / 4);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (f8 & 1)
     k_v_write<true><<<blocks, 128, 0, st>>>(static_cast<const __nv_bfloat16*>(kv), kv_rs, n, Hkv, static_cast<const long long*>(slots),
-                                            static_cast<const float*>(co), static_cast<uint8_t*>(pool), ident, static_cast<const int*>(vfix));
+                                            static_cast<const float*>(co), static_cast<const float*>(M), static_cast<uint8_t*>(pool),
+                                            ident, static_cast<const int*>(vfix));
   else
     k_v_write<false><<<blocks, 128, 0, st>>>(static_cast<const __nv_bfloat16*>(kv), kv_rs, n, Hkv, static_cast<const long long*>(slots),
-                                             static_cast<const float*>(co), static_cast<uint8_t*>(pool), ident, static_cast<const int*>(vfix));
+                                             static_cast<const float*>(co), static_cast<const float*>(M), static_cast<uint8_t*>(pool),
+                                             ident, static_cast<const int*>(vfix));
   return check_launch("kv_v_write");
 }
 

@@ -7,7 +7,7 @@
  * kv_last_error().  Built: head dim 128; the kivi2 pages (FP16 scale / min) and, with f8 bit 0 set in every entry, the
  * kivi2p8 pages (kivi.cu:28-35: FP8 E4M3 scale / min, 10 D bytes per (page, kv head), flags in the scale sign bits, codes
  * computed from the stored values).  f8 bit 1 (the reference's "fast" / "v2" kernel variants, which compute the same
- * values) is accepted everywhere and selects nothing.  Not built (code 2): head dim 256, matrix-weighted value selection (M).
+ * values) is accepted everywhere and selects nothing.  Not built (code 2): head dim 256.
  */
 #ifndef FLAGROT_KIVI_H
 #define FLAGROT_KIVI_H
@@ -26,7 +26,8 @@ int kv_chunk_bytes8(int D);
 
 /* Per-token value encoder: kv bf16 [n, 2 Hkv, D] (row stride kv_rs elements, V rows Hkv .. 2 Hkv - 1) -> pool at slots
  * int64 [n] (< 0 skipped); candidates identity / H32 per 32-dim sub-vector / whole-head H_D chosen by sum d^2 co
- * (co fp32 [Hkv, D]); ident 1: identity only; vfix int32 [Hkv]: frozen choice (bits 0..3 H32, bit 16 whole head).
+ * (co fp32 [Hkv, D]) or, when M fp32 [Hkv, D, D] is given, by e^T M e; ident 1: identity only; vfix int32 [Hkv]: frozen choice
+ * (bits 0..3 H32, bit 16 whole head).
  * replaces kivi.cu:1934-1948 */
 int kv_v_write(const void* kv, long long kv_rs, int n, int Hkv, int D, const void* slots, const void* co, const void* M,
                void* pool, int ident, const void* vfix, int f8, void* stream);

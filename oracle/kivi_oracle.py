@@ -78,12 +78,14 @@ def _f16(x):
 
 
 # ------------------------------------------------------------------------------------------------ values (per token)
-def encode_values(x, co, ident=False, vfix=None, recip=True, f8=False):
+def encode_values(x, co, ident=False, vfix=None, recip=True, f8=False, M=None):
     """x fp32 [T, H, 128]; co fp32 [H, 128].  Candidates identity / H32 per 32-dim sub-vector / whole-head H128, groups of
     32 along the head dim; error sum d^2 co; H32 only if strictly better, whole head only if strictly better than the
     combination (kivi.cu:163-328).  Returns dict: codes uint8 [T, H, 128], meta float16 [T, H, 4, 2] (scale with the H32 flag
     in its sign, min), vf uint8 [T, H], cand int [T, H, 4] (0 I, 1 H32, 2 whole head), s / mn fp32 [T, H, 4] before storage.
-    f8: meta is uint8 [T, H, 4, 2] (E4M3 scale | H32 flag << 7, E4M3 min)."""
+    f8: meta is uint8 [T, H, 4, 2] (E4M3 scale | H32 flag << 7, E4M3 min).  M fp32 [H, 128, 128]: the error of a candidate is
+    e^T M e instead of sum e^2 co (the diagonal 32 x 32 block for a sub-vector's I / H32 choice, the whole matrix for the
+    whole-head candidate and for the chosen combination; kivi.cu:222-275)."""
     x = np.asarray(x, F32)
     T, H, _ = x.shape
     outs = []
@@ -102,6 +104,16 @@ def encode_values(x, co, ident=False, vfix=None, recip=True, f8=False):
         vfix = np.asarray(vfix)
         loc = ((vfix[:, None] >> np.arange(NV)[None]) & 1)
         cand = np.where(((vfix >> 16) & 1)[:, None] == 1, 2, loc)[None].repeat(T, 0)
+    elif M is not None:
+        Mm = np.asarray(M, F32)
+        ev = [(o[3] - x).astype(F32) for o in outs]                                           # [T, H, 128]
+        Mb = np.stack([Mm[:, 32 * j:32 * j + 32, 32 * j:32 * j + 32] for j in range(NV)], 1)     # [H, 4, 32, 32]
+        blk = lambda e: np.einsum("thvi,hvik,thvk->thv", e.reshape(T, H, NV, 32), Mb, e.reshape(T, H, NV, 32))  # noqa: E731
+        full = lambda e: np.einsum("thi,hik,thk->th", e, Mm, e)                               # noqa: E731
+        useH = blk(ev[1]) < blk(ev[0])
+        eb = np.where(np.repeat(useH, 32, -1), ev[1], ev[0])
+        useF = full(ev[2]) < full(eb)
+        cand = np.where(useF[..., None], 2, useH.astype(int))
     else:
         e = [((o[3] - x) ** 2 * np.asarray(co, F32)[None]).reshape(T, H, NV, 32).sum(-1) for o in outs]
         useH = e[1] < e[0]

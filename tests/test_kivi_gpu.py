@@ -225,6 +225,53 @@ def test_writers_vs_reference_library(KV, f8):
 
 
 @F8
+def test_value_writer_matrix_weighting(KV, f8):
+    """kv_v_write with a full weighting matrix M [Hkv, 128, 128] (e^T M e): choices against the oracle and, byte for byte
+    where the choices agree, against the reference's own library (which sums in the same order)."""
+    g = torch.Generator().manual_seed(65)
+    Hkv, T = 4, 512
+    qs, lz, co, qsc = calib(Hkv, g)
+    kv, slots, sidx, dslot, pool0, perm = setup(T, Hkv, g, f8=f8)
+    A = torch.randn(Hkv, D, D, generator=g) / math.sqrt(D)
+    M = (A.transpose(1, 2) @ A + torch.diag_embed(torch.rand(Hkv, D, generator=g) * 0.5)).contiguous()
+    pool = pool0.clone().to(DEV)
+    KV.v_write(kv.to(DEV), slots.to(DEV), co.to(DEV), M.to(DEV), pool, Hkv, D, f8=f8)
+    torch.cuda.synchronize()
+    got = pool.cpu().numpy()
+    x = O.bf16_bits_to_f32(bits(kv))
+    ev = KO.encode_values(x[:, Hkv:], co.numpy(), recip=True, f8=f8, M=M.numpy())
+    exp = pool0.numpy().copy()
+    KO.write_values(exp, slots.numpy(), ev["codes"], ev["meta"], ev["vf"], f8=f8)
+    _, cand = _flags(got, perm, Hkv, f8)
+    v_ok = (cand == ev["cand"]).all(-1)
+    assert v_ok.mean() >= 0.98, v_ok.mean()
+    assert (ev["cand"] == 1).any() and (ev["cand"] == 2).any() and (ev["cand"] == 0).any()
+    _, (vlo, _), (vmlo, vmw), _ = _fields(f8)
+    gch, ech = got[perm.numpy()], exp[perm.numpy()]
+    tok_ok = v_ok.reshape(-1, PAGE, Hkv).transpose(0, 2, 1)
+    for lo, w in ((vlo, 32), (vmlo, vmw)):
+        a = gch[..., lo:lo + PAGE * w].reshape(*gch.shape[:2], PAGE, w)
+        b = ech[..., lo:lo + PAGE * w].reshape(*gch.shape[:2], PAGE, w)
+        assert np.array_equal(a[tok_ok], b[tok_ok])
+    L = ref_lib("libflagrot_kivi_ref.so")
+    if L is not None:
+        L = _ref(KV)
+        rp = pool0.clone().to(DEV)
+        kvd, sl, c_, Md = kv.to(DEV), slots.to(DEV), co.to(DEV), M.to(DEV)
+        assert L.kv_v_write(kvd.data_ptr(), kvd.stride(0), T, Hkv, D, sl.data_ptr(), c_.data_ptr(), Md.data_ptr(), rp.data_ptr(), 0,
+                            None, int(f8), torch.cuda.current_stream().cuda_stream) == 0
+        torch.cuda.synchronize()
+        _, cref = _flags(rp.cpu().numpy(), perm, Hkv, f8)
+        agree = (cref == cand).all(-1).mean()
+        assert agree >= 0.995, agree                     # same sums in the same order: equal up to contraction choices
+        rch = rp.cpu().numpy()[perm.numpy()]
+        same = (cref == cand).all(-1).reshape(-1, PAGE, Hkv).transpose(0, 2, 1)
+        a = gch[..., vlo:vmlo].reshape(*gch.shape[:2], PAGE, 32)
+        b = rch[..., vlo:vmlo].reshape(*gch.shape[:2], PAGE, 32)
+        assert np.array_equal(a[same], b[same])
+
+
+@F8
 @pytest.mark.parametrize("values", ["gauss", "offset"])
 @pytest.mark.parametrize("G", [4, 6, 8])
 def test_decode_attention(KV, G, values, f8):
