@@ -487,3 +487,104 @@ def decode_reference(q_bits, pool, bt, lens, scale, bits, P, key_only, kmask=Non
     with np.errstate(invalid="ignore", over="ignore"):
         o = attention(qr, rnd(Kc), rnd(Vc), lens, scale, tr, kv_start)
     return sel_rot64(o.reshape(B, Hkv, G, D).transpose(0, 2, 1, 3), vm).transpose(0, 2, 1, 3).reshape(B, Hq, D)
+
+
+# ------------------------------------------------------------------------------------------------ symmetric INT4 (int4 / konly)
+def quant_sym_store(y: np.ndarray):
+    """symmetric INT4 per 32 (the `int4` page format): s = fp16(amax * fp32(1 / 7)), q = clamp(rne(y / s), -7, 7), q = 0
+    where s = 0 (kernels/ref.py:151-160; kernels/csrc/attn_decode_v2.cu:1769-1781).  Returns q int8 [..., D] and the scale
+    words int32 [..., D / 32] (the FP16 bit pattern of s; bit 15 is free for a flag)."""
+    b = _grp(y)
+    s16 = (np.abs(b).max(-1, keepdims=True) * (F32(1.0) / F32(7.0))).astype(np.float16)
+    s = s16.astype(F32)
+    with np.errstate(divide="ignore", invalid="ignore"):
+        q = np.where(s != 0, np.rint(b / np.where(s != 0, s, F32(1.0))), F32(0.0))
+    q = np.clip(q, -7, 7)
+    return q.astype(np.int8).reshape(np.shape(y)), s16.view(np.uint16).astype(np.int32)[..., 0]
+
+
+def static_rows_sym(kv_bits: np.ndarray, mask: np.ndarray | None, hfull: np.ndarray | None, kmu: np.ndarray | None = None):
+    """static_rows for the symmetric format: codes int8 [T, Hkv, 2, 128] in [-7, 7], words int32 [T, Hkv, 2, 4]."""
+    H2 = kv_bits.shape[1]
+    Hkv = H2 // 2
+    if hfull is not None:
+        kv_bits = head_fwht(kv_bits, hfull, 1.0 / 16.0)
+    x = bf16_bits_to_f32(kv_bits).copy()
+    if kmu is not None:
+        x[:, :Hkv] = x[:, :Hkv] - np.asarray(kmu, dtype=F32)[None]
+    if mask is not None:
+        T = x.shape[0]
+        x = sel_fwht_rb(x.reshape(T, H2 * D), np.asarray(mask), RB).reshape(T, H2, D)
+    q, w = quant_sym_store(x)
+    return np.stack([q[:, :Hkv], q[:, Hkv:]], 2), np.stack([w[:, :Hkv], w[:, Hkv:]], 2)
+
+
+def _maps_sym(P: int):
+    """bit positions of the sign-magnitude elements of the symmetric layout (kernels/csrc/attn_decode_v2.cuh:26-28): element
+    A_i of a 32-bit word: sign -> bit 7 of byte i, |q| -> bits 0 - 2 of byte i; B_i: sign -> bit 3 of byte i, |q| -> bits
+    4 - 6 of byte (i + 3) % 4.  Which element of which word a (token, dim) is follows the INT4A maps (A = low nibble there).
+    Returns per K and V: (magnitude byte, magnitude shift, sign byte, sign shift), each [P, 128]."""
+    kb, ks, vb, vs, ksw, vsw = _maps(4, P)
+
+    def conv(bm, sm):
+        i = bm % 4
+        base = bm - i
+        isB = sm == 4
+        return (np.where(isB, base + (i + 3) % 4, bm), np.where(isB, 4, 0), bm, np.where(isB, 3, 7))
+    return conv(kb, ks), conv(vb, vs), ksw, vsw
+
+
+def write_pool_sym(pool: np.ndarray, slots: np.ndarray, q: np.ndarray, words: np.ndarray, P: int) -> None:
+    """write_pool for the symmetric format: q int8 [T, Hkv, 2, 128] in [-7, 7] (sign of zero: plus), words [T, Hkv, 2, 4]."""
+    (kmap, vmap, ksw, vsw) = _maps_sym(P)
+    Np, Hkv, CH = pool.shape
+    flat = pool.reshape(-1)
+    slots = np.asarray(slots).astype(np.int64)
+    tt = np.nonzero(slots >= 0)[0]
+    if tt.size == 0:
+        return
+    page, pos = slots[tt] // P, slots[tt] % P
+    base = (page[:, None] * Hkv + np.arange(Hkv)[None, :]) * CH
+    for side, (mb, ms, sb, ss), wmap in ((0, kmap, ksw), (1, vmap, vsw)):
+        c = q[tt, :, side].astype(np.int16)
+        mag, sgn = np.abs(c).astype(np.uint8), (c < 0).astype(np.uint8)
+        for bm, sh, val, width in ((mb, ms, mag, 7), (sb, ss, sgn, 1)):
+            idx = base[:, :, None] + bm[pos][:, None, :]
+            s8 = sh[pos][:, None, :].astype(np.uint8)
+            np.bitwise_and.at(flat, idx, (~(np.uint8(width) << s8)).astype(np.uint8))
+            np.bitwise_or.at(flat, idx, (val << s8).astype(np.uint8))
+        idx = base[:, :, None] + wmap[pos][:, None, :]
+        wv = words[tt, :, side].astype(np.int64) & 0xFFFF
+        flat[idx] = (wv & 0xFF).astype(np.uint8)
+        flat[idx + 1] = (wv >> 8).astype(np.uint8)
+
+
+def parse_pool_sym(pool: np.ndarray, P: int):
+    """signed codes int8 [Np, Hkv, P, 2, 128] and scale words uint16 [Np, Hkv, P, 2, 4] (independent restatement of
+    integrations/vllm_flagrot/vllm_flagrot/kernels.py:580-626 with asym=False)."""
+    (kmap, vmap, ksw, vsw) = _maps_sym(P)
+    out = []
+    for mb, ms, sb, ss in (kmap, vmap):
+        mag = ((pool[:, :, mb] >> ms.astype(np.uint8)) & 7).astype(np.int8)
+        neg = ((pool[:, :, sb] >> ss.astype(np.uint8)) & 1).astype(bool)
+        out.append(np.where(neg, -mag, mag))
+    kw = pool[:, :, ksw].astype(np.uint16) | (pool[:, :, ksw + 1].astype(np.uint16) << 8)
+    vw = pool[:, :, vsw].astype(np.uint16) | (pool[:, :, vsw + 1].astype(np.uint16) << 8)
+    return np.stack(out, 3).astype(np.int8), np.stack([kw, vw], 3)
+
+
+def dequant_pool_sym(pool: np.ndarray, P: int, key_only: bool):
+    """dequant_pool for the symmetric format: x = q * fp16(word & 0x7FFF); key_only (konly): flags as for konlya."""
+    codes, words = parse_pool_sym(pool, P)
+    mag = word_value(words).astype(np.float64)
+    Np, H = pool.shape[:2]
+    d = codes.astype(np.float64).reshape(Np, H, P, 2, NG, RB) * mag[..., None]
+    k, v = d[..., 0, :, :], d[..., 1, :, :]
+    if key_only:
+        lk = ((words[..., 0, :] >> 15) & 1).astype(bool)
+        fk = ((words[..., 1, 0] >> 15) & 1).astype(bool)
+        kl = np.where(lk[..., None], k @ hadamard(RB), k).reshape(Np, H, P, D)
+        k = np.where(fk[..., None], k.reshape(Np, H, P, D) @ hadamard(D), kl)
+    else:
+        k = k.reshape(Np, H, P, D)
+    return k.transpose(0, 2, 1, 3), v.reshape(Np, H, P, D).transpose(0, 2, 1, 3)
