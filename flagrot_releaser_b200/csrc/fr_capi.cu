@@ -17,11 +17,14 @@
 
 namespace {
 enum { FMT_INT4 = 4, FMT_INT4A = 5, FMT_KONLY = 6, FMT_KONLYA = 7, FMT_INT2A = 8, FMT_KONLYA2 = 9 };
-enum { KIND_KONLYA = 10, KIND_KONLYA2 = 11 };
+enum { KIND_KONLY = 6, KIND_KONLYA = 10, KIND_KONLYA2 = 11 };
 constexpr int VAR_HD256 = 4096;
 
+// nb = code bits, ko bit 0 = key-only kind (per-token flags), ko bit 1 = symmetric INT4 (sign-magnitude codes)
 bool fmt_info(int fmt, int& nb, int& ko) {
   switch (fmt) {
+    case FMT_INT4: nb = 4; ko = 2; return true;
+    case FMT_KONLY: nb = 4; ko = 3; return true;
     case FMT_INT4A: nb = 4; ko = 0; return true;
     case FMT_INT2A: nb = 2; ko = 0; return true;
     case FMT_KONLYA: nb = 4; ko = 1; return true;
@@ -45,7 +48,7 @@ int attn_common(int nb, int ko, const void* q, long long q_bs, const uint8_t* po
   p.kmask = kmask; p.vmask = vmask; p.vmask_tail = vmask_tail;
   p.opart = opart; p.mlpart = mlpart; p.counter = counter; p.out = out; p.o_bs = o_bs;
   p.tail = tail; p.tail_len = tail_len; p.tail_idx = tail_idx; p.tail_bs = tail_bs; p.tail_ts = tail_ts;
-  p.kv_start = kv_start; p.nb = nb; p.key_only = ko; p.part_out = part_out;
+  p.kv_start = kv_start; p.nb = nb; p.key_only = ko & 1; p.sym = ko >> 1; p.part_out = part_out;
   return fr::decode_launch(p, static_cast<cudaStream_t>(stream));
 }
 }  // namespace
@@ -64,9 +67,10 @@ int fr_v2_attn(int fmt, const void* q, long long q_bs, const uint8_t* pool, cons
   int nb, ko;
   if (!fmt_info(fmt, nb, ko)) return -4;
   if (variant & VAR_HD256) return -8;
-  const uint8_t* km = (!ko && qrot) ? kmask : nullptr;
-  const uint8_t* vm = (!ko && vrot) ? vmask : nullptr;
-  const uint8_t* vt = (!ko && (vrot || tail != nullptr)) ? vmask : nullptr;
+  const bool kon = (ko & 1) != 0;
+  const uint8_t* km = (!kon && qrot) ? kmask : nullptr;
+  const uint8_t* vm = (!kon && vrot) ? vmask : nullptr;
+  const uint8_t* vt = (!kon && (vrot || tail != nullptr)) ? vmask : nullptr;
   if ((km || vm || vt) && rb != 32) return -3;
   return attn_common(nb, ko, q, q_bs, pool, block_table, bt_stride, seq_lens, B, Hkv, gqa > 0 ? gqa : 4, page, nsplit,
                      chunk, qscale, km, vm, vt, opart, mlpart, counter, out, o_bs, tail, tail_len, tail_idx, tail_bs,
@@ -77,18 +81,18 @@ int fr_v2_write(int fmt, const void* kv, long long kv_ts, const long long* slots
                 const uint8_t* mask, int rb, uint8_t* pool, void* stream, int hd, const float* kmu) {
   if (T <= 0) return 0;
   if (hd != 0 && hd != 128) return -8;
-  if (fmt != FMT_INT4A && fmt != FMT_INT2A) return -4;
+  if (fmt != FMT_INT4 && fmt != FMT_INT4A && fmt != FMT_INT2A) return -4;
   if (page != 16 && page != 32) return -5;
   if (mask != nullptr && rb != 32) return -3;
-  return fr::rows_launch(fmt == FMT_INT4A ? 4 : 2, kv, kv_ts, slots, 0, T, Hkv, page, mask, nullptr, kmu, pool, 0, 2 * Hkv, 0,
-                         static_cast<cudaStream_t>(stream));
+  return fr::rows_launch(fmt == FMT_INT2A ? 2 : 4, kv, kv_ts, slots, 0, T, Hkv, page, mask, nullptr, kmu, pool, 0, 2 * Hkv, 0,
+                         static_cast<cudaStream_t>(stream), fmt == FMT_INT4);
 }
 
 int fr_v2_occupancy(int fmt, int variant, int stages, int page) {
   (void)variant; (void)stages; (void)page;
   int nb, ko;
   if (!fmt_info(fmt, nb, ko)) return 0;
-  return fr::decode_occupancy(nb, ko);
+  return fr::decode_occupancy(nb, ko & 1);
 }
 int fr_v2_chunk_bytes(int fmt, int page) { return page * ((fmt == FMT_INT2A || fmt == FMT_KONLYA2) ? 80 : 144); }
 
@@ -128,10 +132,10 @@ int fr_w3_static_write(const void* kv, long long kv_ts, const long long* slots, 
                        const float* kmu) {
   (void)path;
   if (T <= 0) return 0;
-  if (asym != 1 && asym != 2) return -4;
+  if (asym < 0 || asym > 2) return -4;
   if (page != 16 && page != 32) return -5;
-  return fr::rows_launch(asym == 1 ? 4 : 2, kv, kv_ts, slots, 0, T, Hkv, page, mask, hfull, kmu, pool, 0, 2 * Hkv, 0,
-                         static_cast<cudaStream_t>(stream));
+  return fr::rows_launch(asym == 2 ? 2 : 4, kv, kv_ts, slots, 0, T, Hkv, page, mask, hfull, kmu, pool, 0, 2 * Hkv, 0,
+                         static_cast<cudaStream_t>(stream), asym == 0);
 }
 
 int fr_cb_attn(const void* q, long long q_bs, const uint8_t* pool, const int* block_table, int bt_stride,
@@ -140,17 +144,17 @@ int fr_cb_attn(const void* q, long long q_bs, const uint8_t* pool, const int* bl
                const void* tail, const int* tail_len, const int* tail_idx, long long tail_bs, long long tail_ts,
                void* stream, int kv_start) {
   (void)sg; (void)variant; (void)stages;
-  int nb;
-  if (!kind_info(kind, nb)) return -4;
-  return attn_common(nb, 1, q, q_bs, pool, block_table, bt_stride, seq_lens, B, Hkv, 4, page, nsplit, chunk, qscale,
-                     nullptr, nullptr, nullptr, opart, mlpart, counter, out, o_bs, tail, tail_len, tail_idx, tail_bs,
+  int nb = 4;
+  if (kind != KIND_KONLY && !kind_info(kind, nb)) return -4;     // konly: the symmetric key-only pages (decode only)
+  return attn_common(nb, kind == KIND_KONLY ? 3 : 1, q, q_bs, pool, block_table, bt_stride, seq_lens, B, Hkv, 4, page, nsplit, chunk,
+                     qscale, nullptr, nullptr, nullptr, opart, mlpart, counter, out, o_bs, tail, tail_len, tail_idx, tail_bs,
                      tail_ts, stream, kv_start, nullptr);
 }
 
 int fr_cb_occupancy(int kind, int variant, int stages, int page) {
   (void)variant; (void)stages; (void)page;
-  int nb;
-  if (!kind_info(kind, nb)) return 0;
+  int nb = 4;
+  if (kind != KIND_KONLY && !kind_info(kind, nb)) return 0;
   return fr::decode_occupancy(nb, 1);
 }
 int fr_cb_chunk_bytes(int kind, int page) { return page * (kind == KIND_KONLYA2 ? 80 : 144); }
@@ -178,7 +182,7 @@ int fr_attn_partial(int fmt, const void* q, long long q_bs, const uint8_t* pool,
   int nb, ko;
   if (!fmt_info(fmt, nb, ko)) return -4;
   return attn_common(nb, ko, q, q_bs, pool, block_table, bt_stride, seq_lens, B, Hkv, gqa > 0 ? gqa : 4, page, nsplit, chunk,
-                     qscale, ko ? nullptr : kmask, ko ? nullptr : vmask, ko ? nullptr : vmask, opart, mlpart, counter,
+                     qscale, (ko & 1) ? nullptr : kmask, (ko & 1) ? nullptr : vmask, (ko & 1) ? nullptr : vmask, opart, mlpart, counter,
                      nullptr, 0, tail, tail_len, tail_idx, tail_bs, tail_ts, stream, kv_start, part);
 }
 
@@ -189,8 +193,10 @@ int fr_dequant_pages(int fmt, const uint8_t* pool, const int* bt_row, int start,
   if (!fmt_info(fmt, nb, ko)) return -4;
   if (page != 16 && page != 32) return -5;
   if (start < 0 || Hkv <= 0) return -3;
-  return fr::dequant_pages_launch(nb, ko, pool, bt_row, start, n, Hkv, page, ko ? nullptr : kmask, ko ? nullptr : vmask,
-                                  ko ? nullptr : kfull, ko ? nullptr : vfull, ok, ov, out_fp32, static_cast<cudaStream_t>(stream));
+  const bool kon = (ko & 1) != 0;
+  return fr::dequant_pages_launch(nb, kon, pool, bt_row, start, n, Hkv, page, kon ? nullptr : kmask, kon ? nullptr : vmask,
+                                  kon ? nullptr : kfull, kon ? nullptr : vfull, ok, ov, out_fp32, static_cast<cudaStream_t>(stream),
+                                  ko >> 1);
 }
 
 int fr_device_status() {

@@ -63,6 +63,41 @@ template <int NB> FR_DEVI void quant_store(float y, float mn, float mx, unsigned
   word = scale_word<NB>(s, static_cast<unsigned>(z));
 }
 // error form: unwidened range, unbounded zero point, deq = (q - z) s (reference: kernels/codebook_ref.py:99-108)
+// symmetric INT4 (`int4` pages): s = fp16(amax * fp32(1 / 7)), q = clamp(rne(y / s), -7, 7), 0 where s = 0 (reference
+// attn_decode_v2.cu:1769-1781).  code = sign-magnitude (8 | |q| for q < 0), word = FP16 bits of s.
+FR_DEVI void quant_store_sym(float y, float amax, unsigned& code, unsigned& word) {
+  const __half sh = __float2half_rn(__fmul_rn(amax, 1.0f / 7.0f));
+  const float sf = __half2float(sh);
+  float q = sf != 0.f ? rintf(__fdiv_rn(y, sf)) : 0.f;
+  q = fminf(fmaxf(q, -7.f), 7.f);
+  const int qi = static_cast<int>(q);
+  code = static_cast<unsigned>(qi < 0 ? (8 | -qi) : qi);
+  word = __half_as_ushort(sh);
+}
+// bits of a sign-magnitude element in its 32-bit word (byte i holds A_i): A_i: sign -> bit 8 i + 7, |q| -> bits 8 i .. + 2;
+// B_i: sign -> bit 8 i + 3, |q| -> bits 4 .. 6 of byte (i + 3) % 4 (reference attn_decode_v2.cuh:26-28)
+FR_DEVI unsigned sym_bits(unsigned c, bool isB, int i) {
+  const unsigned s = (c >> 3) & 1u, mag = c & 7u;
+  return isB ? (s << (8 * i + 3)) | (mag << (8 * ((i + 3) & 3) + 4)) : ((s << 7) | mag) << (8 * i);
+}
+FR_DEVI unsigned sym_mask(bool isB, int i) { return isB ? (0x08u << (8 * i)) | (0x70u << (8 * ((i + 3) & 3))) : 0x87u << (8 * i); }
+// the bits `mask` of the 32-bit word at chunk + word_off (4-byte aligned) := bits, whatever other threads do to the rest
+FR_DEVI void put_bits(uint8_t* chunk, int word_off, unsigned mask, unsigned bits) {
+  uint32_t* wp = reinterpret_cast<uint32_t*>(chunk + word_off);
+  const unsigned delta = (*reinterpret_cast<volatile uint32_t*>(wp) ^ bits) & mask;
+  if (delta) atomicXor(wp, delta);
+}
+
+// sign-magnitude bytes (sign bit 7, |q| bits 0 - 2) -> q + 8 per byte (1 .. 15): no carry leaves a byte
+FR_DEVI uint32_t sym_offset_bytes(uint32_t x) {
+  const uint32_t n7 = ((x >> 7) & 0x01010101u) * 7u;
+  return ((x & 0x07070707u) ^ n7) + (0x08080808u - n7);
+}
+// a word of 4 A + 4 B sign-magnitude elements -> the INT4A word (A low, B high nibble of byte i) of q + 8
+FR_DEVI uint32_t sym_to_asym(uint32_t w) {
+  return sym_offset_bytes(w & 0x87878787u) | (sym_offset_bytes(__funnelshift_l(w, w, 4) & 0x87878787u) << 4);
+}
+
 template <int NB> FR_DEVI float quant_err_deq(float y, float mn, float mx) {
   float s, z;
   asym_params<NB>(mn, mx, s, z);

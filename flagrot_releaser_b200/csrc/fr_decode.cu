@@ -440,7 +440,10 @@ FR_DEVI int row_pieces(const DecodeParams& p, int b, int& np) {
 }
 
 // ------------------------------------------------------------------------------------------------ the kernel
-template <int NB, bool KO, int PG>
+// SYM (NB 4 only): the symmetric `int4` / `konly` pages (reference attn_decode_v2.cuh:26-28): sign-magnitude elements, plain
+// FP16 scale words.  A code word is rewritten on the fly as the INT4A word of q + 8 (carry-free byte arithmetic) and every
+// zero point is 8, after which the asymmetric path applies unchanged.
+template <int NB, bool KO, int PG, bool SYM = false>
 __global__ void __launch_bounds__(128, MINB) k_decode(const DecodeParams p) {
   constexpr int NV = KO ? 3 : 1;
   using L = DLay<NB, PG>;
@@ -619,8 +622,8 @@ __global__ void __launch_bounds__(128, MINB) k_decode(const DecodeParams p) {
       const uint2 t = lds64(st + kt_ld);
       float2 f01 = h2x2f(t.x), f23 = h2x2f(t.y);
       if (NB == 2) { f01.x *= L::kfinv(0); f01.y *= L::kfinv(1); f23.x *= L::kfinv(2); f23.y *= L::kfinv(3); }
-      sts128(kt_dst, __float_as_uint(f01.x), __float_as_uint(f01.y), t.x & L::ZM, (t.x >> 16) & L::ZM);         // groups 0, 1
-      sts128(kt_dst + 512, __float_as_uint(f23.x), __float_as_uint(f23.y), t.y & L::ZM, (t.y >> 16) & L::ZM);   // groups 2, 3
+      sts128(kt_dst, __float_as_uint(f01.x), __float_as_uint(f01.y), SYM ? 8u : t.x & L::ZM, SYM ? 8u : (t.x >> 16) & L::ZM);   // groups 0, 1
+      sts128(kt_dst + 512, __float_as_uint(f23.x), __float_as_uint(f23.y), SYM ? 8u : t.y & L::ZM, SYM ? 8u : (t.y >> 16) & L::ZM);   // 2, 3
     }
     // ---- V scale words of the lane's 4 tokens (group j: tokens 0 1 | 2 3); group 0 now (it carries the whole-head flags
     // of the keys), groups 1 - 3 after the scores
@@ -656,6 +659,10 @@ __global__ void __launch_bounds__(128, MINB) k_decode(const DecodeParams p) {
         if (NB == 4) {
           const uint4 t = lds128(st + kc_base + kc_row(2 * u + r));
           ka[r][0] = t.x; ka[r][1] = t.y; ka[r][2] = t.z; ka[r][3] = t.w;
+          if (SYM) {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) ka[r][k] = sym_to_asym(ka[r][k]);
+          }
         } else {
           const uint2 t = lds64(st + kc_base + kc_row(2 * u + r));
           ka[r][0] = t.x; ka[r][1] = t.y; ka[r][2] = 0; ka[r][3] = 0;
@@ -768,7 +775,7 @@ __global__ void __launch_bounds__(128, MINB) k_decode(const DecodeParams p) {
       hiw[j] = prmt(x01, x23, 0x7531u);
       low[j] = prmt(x01, x23, 0x6420u);
       // zero-point sums with the same integers the tensor path sees: bytes (z0, z1, z2, z3)
-      const uint32_t zb = prmt(vsw[j][0], vsw[j][1], 0x6420u) & (L::ZM * 0x01010101u);
+      const uint32_t zb = SYM ? 0x08080808u : prmt(vsw[j][0], vsw[j][1], 0x6420u) & (L::ZM * 0x01010101u);
       Zi[j] = __dp2a_hi(x23, zb, __dp2a_lo(x01, zb, static_cast<unsigned>(Zi[j])));
     }
     sts128(pw_dst, hiw[0], hiw[1], hiw[2], hiw[3]);
@@ -787,6 +794,10 @@ __global__ void __launch_bounds__(128, MINB) k_decode(const DecodeParams p) {
       if (NB == 4) {
         const uint4 t = lds128(st + vc_off + 16 * (ww * 8 * (L::P / 8)));
         vw[0] = t.x; vw[1] = t.y; vw[2] = t.z; vw[3] = t.w;
+        if (SYM) {
+#pragma unroll
+          for (int k = 0; k < 4; ++k) vw[k] = sym_to_asym(vw[k]);
+        }
       } else {
         const uint2 t = lds64(st + vc_off + 8 * (ww * 8 * (L::P / 8)));
         vw[0] = t.x; vw[1] = t.y; vw[2] = 0; vw[3] = 0;
@@ -910,25 +921,25 @@ int pack_rows(int B, int X, int p, int chunk, int slots, bool tail, int& chunk_w
   return best;
 }
 
-template <int NB, bool KO, int PG> int launch_k(DecodeParams p, cudaStream_t st) {
+template <int NB, bool KO, int PG, bool SYM = false> int launch_k(DecodeParams p, cudaStream_t st) {
   constexpr int NV = KO ? 3 : 1;
   constexpr int smem = SMap<NB, NV, PG>::TOTAL > TAILM_BYTES ? SMap<NB, NV, PG>::TOTAL : TAILM_BYTES;
   static unsigned long long ready = 0;
-  if (!smem_limit_ready(k_decode<NB, KO, PG>, smem, ready)) return -2;
+  if (!smem_limit_ready(k_decode<NB, KO, PG, SYM>, smem, ready)) return -2;
   static int slots_of[64];                   // resident CTAs of this instantiation per device ordinal (0: not asked yet)
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -1;
   if (slots_of[dev] == 0) {
     int sms = 0, occ = 0;
     if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
-        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, k_decode<NB, KO, PG>, 128, smem) != cudaSuccess || occ < 1)
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, k_decode<NB, KO, PG, SYM>, 128, smem) != cudaSuccess || occ < 1)
       return -2;
     slots_of[dev] = sms * occ;
   }
   const int NT = (p.G + 3) / 4;
   p.rows_wide = pack_rows(p.B, p.Hkv * NT, p.nsplit, p.chunk, slots_of[dev], p.tail != nullptr, p.chunk_w);
   const dim3 grid(p.Hkv * NT, p.nsplit, p.B * (p.tail != nullptr ? 2 : 1));
-  k_decode<NB, KO, PG><<<grid, 128, smem, st>>>(p);
+  k_decode<NB, KO, PG, SYM><<<grid, 128, smem, st>>>(p);
   return cudaPeekAtLastError() == cudaSuccess ? 0 : -1;
 }
 
@@ -939,9 +950,11 @@ int decode_launch(const DecodeParams& p, cudaStream_t st) {
   if (p.page != 16 && p.page != 32) return -5;
   if (p.chunk <= 0 || p.chunk % 64 != 0 || p.chunk > MAXPG * 16 || p.nsplit < 1) return -3;
   if (p.page == 32) {
+    if (p.sym) return p.key_only ? launch_k<4, true, 32, true>(p, st) : launch_k<4, false, 32, true>(p, st);
     if (p.nb == 4) return p.key_only ? launch_k<4, true, 32>(p, st) : launch_k<4, false, 32>(p, st);
     return p.key_only ? launch_k<2, true, 32>(p, st) : launch_k<2, false, 32>(p, st);
   }
+  if (p.sym) return p.key_only ? launch_k<4, true, 16, true>(p, st) : launch_k<4, false, 16, true>(p, st);
   if (p.nb == 4) return p.key_only ? launch_k<4, true, 16>(p, st) : launch_k<4, false, 16>(p, st);
   return p.key_only ? launch_k<2, true, 16>(p, st) : launch_k<2, false, 16>(p, st);
 }

@@ -27,7 +27,7 @@ struct DqParams {
   const uint8_t* pool;        // [pages, Hkv, chunk]
   const int* bt;              // block-table row of the request
   int start, n, Hkv, page, pg0;
-  int key_only;
+  int key_only, sym;
   const uint8_t *kmask, *vmask, *kfull, *vfull;   // static formats; any may be null
   void *ok, *ov;              // [n - start, Hkv, 128]
   int fp32;
@@ -65,7 +65,7 @@ FR_DEVI void unrotate_static(float (&x)[4], const uint8_t* mask4, bool full, int
   }
 }
 
-template <int NB>
+template <int NB, bool SYM = false>
 __global__ void __launch_bounds__(128) k_dequant_pages(const DqParams p) {
   extern __shared__ __align__(16) uint8_t chunk[];
   const int P = p.page, h = blockIdx.y, pg = p.pg0 + blockIdx.x;
@@ -87,10 +87,14 @@ __global__ void __launch_bounds__(128) k_dequant_pages(const DqParams p) {
     float x[4];
     {
       unsigned word;
-      if (NB == 4) word = *reinterpret_cast<const uint32_t*>(chunk + 64 * pos + 16 * tg + 4 * j) >> (4 * isb);
+      if (NB == 4) {
+        word = *reinterpret_cast<const uint32_t*>(chunk + 64 * pos + 16 * tg + 4 * j);
+        if (SYM) word = sym_to_asym(word);                                   // symmetric pages: the INT4A word of q + 8
+        word >>= 4 * isb;
+      }
       else word = *reinterpret_cast<const uint32_t*>(chunk + Lay<2>::krow(pos) + 8 * tg + 4 * (j >> 1)) >> (4 * (j & 1) + 2 * isb);
       const float s = __half2float(__ushort_as_half(static_cast<unsigned short>(kw & 0x7FFFu)));
-      const int z = static_cast<int>(kw & FM);
+      const int z = SYM ? 8 : static_cast<int>(kw & FM);
 #pragma unroll
       for (int i = 0; i < 4; ++i) x[i] = static_cast<float>(static_cast<int>((word >> (8 * i)) & FM) - z) * s;
     }
@@ -118,14 +122,15 @@ __global__ void __launch_bounds__(128) k_dequant_pages(const DqParams p) {
     {
       const unsigned sw = *reinterpret_cast<const uint16_t*>(chunk + vs_off + 2 * (j * P + 8 * (pos >> 3) + vslot8(pos)));
       const float s = __half2float(__ushort_as_half(static_cast<unsigned short>(sw & 0x7FFFu)));
-      const int z = static_cast<int>(sw & FM);
+      const int z = SYM ? 8 : static_cast<int>(sw & FM);
       const int c8 = pos >> 3, ii = (pos & 7) >> 1, odd = pos & 1;
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const int d = 4 * lane + i, m = d >> 6, ww = (d & 63) >> 4, gid = d & 7, r8 = (d & 15) >> 3;
         const int e = (ww * 8 + gid) * (P / 8) + c8;
         unsigned c;
-        if (NB == 4) c = (chunk[v_off + 16 * e + 4 * (2 * m + r8) + ii] >> (4 * odd)) & 15u;
+        if (NB == 4 && SYM) c = (sym_to_asym(*reinterpret_cast<const uint32_t*>(chunk + v_off + 16 * e + 4 * (2 * m + r8))) >> (8 * ii + 4 * odd)) & 15u;
+        else if (NB == 4) c = (chunk[v_off + 16 * e + 4 * (2 * m + r8) + ii] >> (4 * odd)) & 15u;
         else c = (chunk[v_off + 8 * e + 4 * m + ii] >> (4 * r8 + 2 * odd)) & 3u;
         x[i] = static_cast<float>(static_cast<int>(c) - z) * s;
       }
@@ -139,13 +144,14 @@ __global__ void __launch_bounds__(128) k_dequant_pages(const DqParams p) {
 
 int dequant_pages_launch(int nb, int key_only, const uint8_t* pool, const int* bt_row, int start, int n, int Hkv, int page,
                          const uint8_t* kmask, const uint8_t* vmask, const uint8_t* kfull, const uint8_t* vfull, void* ok, void* ov,
-                         int fp32, cudaStream_t st) {
+                         int fp32, cudaStream_t st, int sym) {
   if (n <= start) return 0;
   const int pg0 = start / page, npg = (n + page - 1) / page - pg0;
-  DqParams p{pool, bt_row, start, n, Hkv, page, pg0, key_only, kmask, vmask, kfull, vfull, ok, ov, fp32};
+  DqParams p{pool, bt_row, start, n, Hkv, page, pg0, key_only, sym, kmask, vmask, kfull, vfull, ok, ov, fp32};
   const dim3 grid(npg, Hkv);
   const int smem = (nb == 4 ? 144 : 80) * page;
-  if (nb == 4) k_dequant_pages<4><<<grid, 128, smem, st>>>(p);
+  if (sym) k_dequant_pages<4, true><<<grid, 128, smem, st>>>(p);
+  else if (nb == 4) k_dequant_pages<4><<<grid, 128, smem, st>>>(p);
   else k_dequant_pages<2><<<grid, 128, smem, st>>>(p);
   return cudaPeekAtLastError() == cudaSuccess ? 0 : -1;
 }

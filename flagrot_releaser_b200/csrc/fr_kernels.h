@@ -10,14 +10,14 @@ int head_fwht_launch(const void* x, long long x_ts, void* out, long long o_ts, i
 // rows [row0, row0 + nrow) of every token through the static row writer (nb = 4 | 2 code bits)
 int rows_launch(int nb, const void* kv, long long kv_ts, const long long* slots, int slot_ph, int T, int Hkv, int page,
                 const uint8_t* mask, const uint8_t* hfull, const float* kmu, uint8_t* pool, int row0, int nrow,
-                int shared15, cudaStream_t st);
+                int shared15, cudaStream_t st, int sym = 0);
 int dyn_keys_launch(int nb, const void* kv, long long kv_ts, const long long* slots, int slot_ph, int T, int Hkv, int page,
                     const float* CT, const float* kmu, uint8_t* pool, cudaStream_t st, int with_values = 0);
 
 // positions [start, n) of one request's pages -> K / V rows in the original basis (fr_dequant.cu)
 int dequant_pages_launch(int nb, int key_only, const uint8_t* pool, const int* bt_row, int start, int n, int Hkv, int page,
                          const uint8_t* kmask, const uint8_t* vmask, const uint8_t* kfull, const uint8_t* vfull, void* ok, void* ov,
-                         int fp32, cudaStream_t st);
+                         int fp32, cudaStream_t st, int sym = 0);
 
 // paged decode attention (fr_decode.cu)
 struct DecodeParams {
@@ -34,7 +34,8 @@ struct DecodeParams {
   const void* tail; const int* tail_len; const int* tail_idx; long long tail_bs, tail_ts;
   int kv_start;
   int nb;                                    // code bits 4 | 2
-  int key_only;                              // 1: per-token flags in the scale sign bits (konlya / konlya2)
+  int key_only;                              // 1: per-token flags in the scale sign bits (konlya / konlya2 / konly)
+  int sym;                                   // 1: symmetric INT4 pages (int4 / konly): sign-magnitude codes, no zero points
   float* part_out;                           // optional: unmerged (m, l, o) of the whole row (extension entry)
   int rows_wide, chunk_w;                    // set by decode_launch: rows [0, rows_wide) use nsplit - 1 pieces of chunk_w tokens
 };

@@ -46,7 +46,7 @@ __global__ void __launch_bounds__(256) k_head_fwht(const __nv_bfloat16* __restri
 
 // ------------------------------------------------------------------------------------------------ page stores
 // K row of one token from the 128 codes of the row (row mapping: lane l holds d = 4 l .. 4 l + 3)
-template <int NB>
+template <int NB, bool SYM = false>
 FR_DEVI void store_k_row(uint8_t* chunk, int P, int pos, int lane, const unsigned (&code)[4], unsigned word) {
   unsigned cb[4];
 #pragma unroll
@@ -55,7 +55,8 @@ FR_DEVI void store_k_row(uint8_t* chunk, int P, int pos, int lane, const unsigne
   if (NB == 4) {
     unsigned wd = 0;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) wd |= (code[i] << (8 * i)) | (cb[i] << (8 * i + 4));
+    for (int i = 0; i < 4; ++i)
+      wd |= SYM ? sym_bits(code[i], false, i) | sym_bits(cb[i], true, i) : (code[i] << (8 * i)) | (cb[i] << (8 * i + 4));
     if (tg < 4) *reinterpret_cast<uint32_t*>(chunk + Lay<4>::krow(pos) + 16 * tg + 4 * j) = wd;
   } else {
     unsigned hw = 0;
@@ -68,7 +69,7 @@ FR_DEVI void store_k_row(uint8_t* chunk, int P, int pos, int lane, const unsigne
 }
 
 // V^T codes + V scale of one token (row mapping).  shared15: bit 15 of the group-0 word belongs to the key writer.
-template <int NB>
+template <int NB, bool SYM = false>
 FR_DEVI void store_v_row(uint8_t* chunk, int P, int pos, int lane, const unsigned (&code)[4], unsigned word, bool shared15) {
   const int c8 = pos >> 3, ii = (pos & 7) >> 1, b = pos & 1;
   const int w = (lane & 15) >> 2, r8 = (lane & 3) >> 1, m = lane >> 4;
@@ -76,7 +77,8 @@ FR_DEVI void store_v_row(uint8_t* chunk, int P, int pos, int lane, const unsigne
   for (int i = 0; i < 4; ++i) {
     const int gid = 4 * (lane & 1) + i;
     const int e = (w * 8 + gid) * (P >> 3) + c8;
-    if (NB == 4) put_field(chunk, Lay<4>::v_off(P) + 16 * e + 4 * (2 * m + r8) + ii, 4 * b, 0xFu, code[i]);
+    if (SYM) put_bits(chunk, Lay<4>::v_off(P) + 16 * e + 4 * (2 * m + r8), sym_mask(b != 0, ii), sym_bits(code[i], b != 0, ii));
+    else if (NB == 4) put_field(chunk, Lay<4>::v_off(P) + 16 * e + 4 * (2 * m + r8) + ii, 4 * b, 0xFu, code[i]);
     else put_field(chunk, Lay<2>::v_off(P) + 8 * e + 4 * m + ii, 4 * r8 + 2 * b, 0x3u, code[i]);
   }
   if ((lane & 7) == 0) {
@@ -102,7 +104,7 @@ struct RowParams {
 
 // codes and scale word of row hr of token t (row mapping: lane l holds d = 4 l .. 4 l + 3): bf16 -> fp32, whole-head H128 / 16
 // rounded to bf16, key centering, H32 of the flagged 32-blocks, stored-form quantiser
-template <int NB>
+template <int NB, bool SYM = false>
 FR_DEVI void row_codes(const RowParams& p, int t, int hr, int lane, unsigned (&code)[4], unsigned& word) {
   const bool isv = hr >= p.Hkv;
   const uint2 raw = *reinterpret_cast<const uint2*>(p.kv + t * p.kv_ts + hr * HD + 4 * lane);
@@ -130,12 +132,18 @@ FR_DEVI void row_codes(const RowParams& p, int t, int hr, int lane, unsigned (&c
   const float mn = group_min8(fminf(fminf(v[0], v[1]), fminf(v[2], v[3])));
   const float mx = group_max8(fmaxf(fmaxf(v[0], v[1]), fmaxf(v[2], v[3])));
   word = 0;
+  if (SYM) {
+    const float amax = fmaxf(-mn, mx);                 // = max |v| of the 32-group (exact)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) quant_store_sym(v[i], amax, code[i], word);
+    return;
+  }
 #pragma unroll
   for (int i = 0; i < 4; ++i) quant_store<NB>(v[i], mn, mx, code[i], word);
 }
 
 // one (token, row) of a warp: quantise and store at `slot` (the whole warp takes part; slot < 0: nothing is written)
-template <int NB>
+template <int NB, bool SYM = false>
 FR_DEVI void row_write(const RowParams& p, int t, int hr, long long slot, int lane) {
   if (slot < 0) return;
   const bool isv = hr >= p.Hkv;
@@ -145,29 +153,29 @@ FR_DEVI void row_write(const RowParams& p, int t, int hr, long long slot, int la
   const int pos = static_cast<int>(slot % P);
   uint8_t* chunk = p.pool + (page * p.Hkv + head) * static_cast<long long>(Lay<NB>::chunk(P));
   unsigned code[4], word;
-  row_codes<NB>(p, t, hr, lane, code, word);
-  if (!isv) store_k_row<NB>(chunk, P, pos, lane, code, word);
-  else store_v_row<NB>(chunk, P, pos, lane, code, word, p.shared15 != 0);
+  row_codes<NB, SYM>(p, t, hr, lane, code, word);
+  if (!isv) store_k_row<NB, SYM>(chunk, P, pos, lane, code, word);
+  else store_v_row<NB, SYM>(chunk, P, pos, lane, code, word, p.shared15 != 0);
 }
 
-template <int NB>
+template <int NB, bool SYM = false>
 FR_DEVI void rows_block(const RowParams& p, long long block) {
   const int lane = threadIdx.x & 31;
   const long long item = block * 4 + (threadIdx.x >> 5);
   if (item >= static_cast<long long>(p.T) * p.nrow) return;
   const int t = static_cast<int>(item / p.nrow), hr = p.row0 + static_cast<int>(item % p.nrow);
   const int head = hr >= p.Hkv ? hr - p.Hkv : hr;
-  row_write<NB>(p, t, hr, p.slot_ph ? p.slots[static_cast<long long>(t) * p.Hkv + head] : p.slots[t], lane);
+  row_write<NB, SYM>(p, t, hr, p.slot_ph ? p.slots[static_cast<long long>(t) * p.Hkv + head] : p.slots[t], lane);
 }
 
-template <int NB>
-__global__ void __launch_bounds__(128) k_rows(const RowParams p) { rows_block<NB>(p, blockIdx.x); }
+template <int NB, bool SYM = false>
+__global__ void __launch_bounds__(128) k_rows(const RowParams p) { rows_block<NB, SYM>(p, blockIdx.x); }
 
 // Bulk writes: warp = (8 consecutive tokens, row).  A V^T code word holds ONE dim of the 8 tokens of an aligned 8-slot run of
 // a page (INT2: two dims), so when the group's slots are such a run the warp assembles whole words in registers and stores
 // them plainly (4 words per lane and 16 bytes of scale words per 32-group) instead of flipping 128 four-bit fields per token
 // with atomics.  Any other group (ragged end, holes, scattered slots) and every K row take the per-token path.
-template <int NB>
+template <int NB, bool SYM = false>
 __global__ void __launch_bounds__(128) k_rows8(const RowParams p) {
   const int lane = threadIdx.x & 31;
   const long long item = static_cast<long long>(blockIdx.x) * 4 + (threadIdx.x >> 5);
@@ -182,7 +190,7 @@ __global__ void __launch_bounds__(128) k_rows8(const RowParams p) {
   const long long s0 = __shfl_sync(FULLMASK, sl, 0);
   const bool run = nt == 8 && s0 >= 0 && (s0 & 7) == 0 && __all_sync(FULLMASK, lane >= 8 || sl == s0 + lane);
   if (!isv || !run) {
-    for (int i = 0; i < nt; ++i) row_write<NB>(p, t0 + i, hr, __shfl_sync(FULLMASK, sl, i), lane);
+    for (int i = 0; i < nt; ++i) row_write<NB, SYM>(p, t0 + i, hr, __shfl_sync(FULLMASK, sl, i), lane);
     return;
   }
   const int P = p.page;
@@ -193,9 +201,9 @@ __global__ void __launch_bounds__(128) k_rows8(const RowParams p) {
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
     unsigned code[4], word;
-    row_codes<NB>(p, t0 + i, hr, lane, code, word);
+    row_codes<NB, SYM>(p, t0 + i, hr, lane, code, word);
 #pragma unroll
-    for (int k = 0; k < 4; ++k) acc[k] |= code[k] << (8 * (i >> 1) + NB * (i & 1));
+    for (int k = 0; k < 4; ++k) acc[k] |= SYM ? sym_bits(code[k], (i & 1) != 0, i >> 1) : code[k] << (8 * (i >> 1) + NB * (i & 1));
     const int idx = (i & 1) ? 4 + (i >> 1) : (i >> 1);
     sw[idx >> 1] |= (word & 0xFFFFu) << (16 * (idx & 1));
   }
@@ -409,24 +417,25 @@ int head_fwht_launch(const void* x, long long x_ts, void* out, long long o_ts, i
 }
 
 // quantise-and-pack of whole rows: token groups of 8 for a bulk write, one warp per row for an append
-template <int NB>
+template <int NB, bool SYM = false>
 static void rows_kernel_launch(const RowParams& p, cudaStream_t st) {
   if (p.T >= 256) {                            // bulk write: groups of 8 tokens, whole V^T words where the slots allow
     const long long items = static_cast<long long>((p.T + 7) / 8) * p.nrow;
-    k_rows8<NB><<<static_cast<unsigned>((items + 3) / 4), 128, 0, st>>>(p);
+    k_rows8<NB, SYM><<<static_cast<unsigned>((items + 3) / 4), 128, 0, st>>>(p);
   } else {
     const long long items = static_cast<long long>(p.T) * p.nrow;
-    k_rows<NB><<<static_cast<unsigned>((items + 3) / 4), 128, 0, st>>>(p);
+    k_rows<NB, SYM><<<static_cast<unsigned>((items + 3) / 4), 128, 0, st>>>(p);
   }
 }
 
 int rows_launch(int nb, const void* kv, long long kv_ts, const long long* slots, int slot_ph, int T, int Hkv, int page,
                 const uint8_t* mask, const uint8_t* hfull, const float* kmu, uint8_t* pool, int row0, int nrow,
-                int shared15, cudaStream_t st) {
+                int shared15, cudaStream_t st, int sym) {
   if (T <= 0 || nrow <= 0) return 0;
   RowParams p{static_cast<const __nv_bfloat16*>(kv), kv_ts, slots, slot_ph, T, Hkv, page, mask, hfull, kmu, pool, row0,
               nrow, shared15};
-  if (nb == 4) rows_kernel_launch<4>(p, st);
+  if (sym) rows_kernel_launch<4, true>(p, st);       // symmetric INT4: sign-magnitude codes, plain FP16 scale words
+  else if (nb == 4) rows_kernel_launch<4>(p, st);
   else rows_kernel_launch<2>(p, st);
   return check_launch();
 }

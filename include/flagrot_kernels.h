@@ -5,11 +5,12 @@
  * orders, page byte layouts and return codes.  Every entry takes raw DEVICE pointers, element strides and the caller's
  * cudaStream_t (as void*); launches are asynchronous, allocate nothing and may be captured in CUDA graphs.
  * Return: 0 ok, -1 launch error, -2 shared memory, -3 unsupported variant, -4 unknown format / kind, -5 page size not
- * 16 | 32 (decode: 16), -8 head dim not 128.
+ * 16 | 32, -8 head dim not 128.
  *
- * Formats (fmt of fr_v2_*):  5 int4a, 8 int2a (static block flags), 7 konlya, 9 konlya2 (key-only 2x2 flags).
- * Kinds   (kind of fr_cb_*): 10 konlya (INT4), 11 konlya2 (INT2).
- * The symmetric INT4 formats (fmt 4 / 6, kind 6) and the ablation codebooks (kinds 1-5, 7-9) answer -4.
+ * Formats (fmt of fr_v2_*):  5 int4a, 8 int2a (static block flags), 7 konlya, 9 konlya2 (key-only 2x2 flags), and the
+ *                            symmetric INT4 ones: 4 int4 (static; writer, decode, dequantiser), 6 konly (key-only; decode).
+ * Kinds   (kind of fr_cb_*): 10 konlya (INT4), 11 konlya2 (INT2); 6 konly for fr_cb_attn only (its dynamic writer: -4).
+ * The ablation codebooks (kinds 1-5, 7-9) answer -4.
  * Page layout: one chunk per (page, kv head), 144 * page bytes (INT4) or 80 * page bytes (INT2), as specified in the
  * reference's kernels/csrc/attn_decode_v2.cuh:14-46.
  */
@@ -69,7 +70,7 @@ int fr_cb_write3(const void* kv, long long kv_ts, const long long* slots, int sl
                  uint8_t* pool, int nchunk, int nchunk_v, void* stream, const float* kmu);
 
 /* Static writer fused with the whole-head rotation: rows of heads with hfull set become bf16(H128 x / 16) first;
- * asym 1 int4a, 2 int2a (0 = symmetric INT4: -4); path is accepted and ignored.  replaces flagrot_capi.cu:121-131 */
+ * asym 0 int4 (symmetric), 1 int4a, 2 int2a; path is accepted and ignored.  replaces flagrot_capi.cu:121-131 */
 int fr_w3_static_write(const void* kv, long long kv_ts, const long long* slots, int T, int Hkv, int page,
                        const uint8_t* mask, const uint8_t* hfull, int asym, uint8_t* pool, int path, void* stream,
                        const float* kmu);

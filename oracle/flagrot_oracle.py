@@ -451,7 +451,7 @@ def gather_cache(Kp: np.ndarray, Vp: np.ndarray, bt: np.ndarray, Lmax: int, P: i
 
 
 def decode_reference(q_bits, pool, bt, lens, scale, bits, P, key_only, kmask=None, vmask=None, tail=None, tail_len=None,
-                     tail_idx=None, kv_start=0, bf16_operands=False):
+                     tail_idx=None, kv_start=0, bf16_operands=False, sym=False):
     """decode attention of one step over a quantised pool, the way the reference tests build their expectation
     (integrations/vllm_flagrot/tests/test_kernels.py:119-150): dequantise the pages, float64 attention, BF16 tail rows
     treated identically.  Static formats: q and the tail are rotated into the stored basis by the block masks and the
@@ -462,7 +462,7 @@ def decode_reference(q_bits, pool, bt, lens, scale, bits, P, key_only, kmask=Non
     B, Hq, _ = q.shape
     Hkv = pool.shape[1]
     G = Hq // Hkv
-    Kp, Vp = dequant_pool(pool, bits, P, key_only)
+    Kp, Vp = dequant_pool_sym(pool, P, key_only) if sym else dequant_pool(pool, bits, P, key_only)   # sym: int4 / konly pages
     Lmax = int(max(max(lens), 1))
     Kc, Vc = gather_cache(Kp, Vp, bt, Lmax, P)
     rnd = (lambda a: bf16_round(a.astype(np.float32)).astype(np.float64)) if bf16_operands else (lambda a: a)

@@ -19,7 +19,8 @@ from tests._util import P, bits, calib
 pytestmark = pytest.mark.gpu
 DEV = "cuda"
 LOG2E = 1.4426950408889634
-FMT = {"int4a": (4, False), "int2a": (2, False), "konlya": (4, True), "konlya2": (2, True)}
+FMT = {"int4a": (4, False), "int2a": (2, False), "konlya": (4, True), "konlya2": (2, True), "int4": (4, False), "konly": (4, True)}
+SYM = ("int4", "konly")          # symmetric INT4 pages: sign-magnitude codes, plain FP16 scale words
 
 
 @pytest.fixture(scope="module")
@@ -60,7 +61,18 @@ def run_case(K, fmt, lens, win=None, bt_shared=False, seed=0, G=4, Hkv=8, kv_sta
         kv = kv.bfloat16().to(DEV)
         pos = torch.arange(n)
         sl = (bt[b].long()[pos // P] * P + pos % P).to(DEV)
-        if key_only:
+        if fmt == "konly":      # no dynamic writer for the symmetric key-only kind: rows packed by the oracle with random flags
+            x = O.bf16_bits_to_f32(bits(kv.cpu()))
+            qq, ww = O.quant_sym_store(x)
+            codes = np.stack([qq[:, :Hkv], qq[:, Hkv:]], 2)
+            words = np.stack([ww[:, :Hkv], ww[:, Hkv:]], 2)
+            rs = np.random.RandomState(seed + b)
+            words[:, :, 0] |= (rs.rand(n, Hkv, 4) < 0.3).astype(np.int32) << 15       # H32 flags of the key groups
+            words[:, :, 1, 0] |= (rs.rand(n, Hkv) < 0.2).astype(np.int32) << 15       # whole-head flag of the key
+            pn = pool.cpu().numpy()
+            O.write_pool_sym(pn, sl.cpu().numpy(), codes, words, P)
+            pool.copy_(torch.from_numpy(pn))
+        elif key_only:
             K.cb_write(kv, sl, CT, co.to(DEV), fmt, pool, P)
         else:
             K.v2_write(kv, sl, mask.to(DEV), 32, pool, P, fmt=fmt)
@@ -84,8 +96,9 @@ def run_case(K, fmt, lens, win=None, bt_shared=False, seed=0, G=4, Hkv=8, kv_sta
     kw = dict(tail=None if tail is None else bits(tail), tail_len=None if tail is None else tail_len.numpy(),
               tail_idx=None if tail is None else tail_idx.numpy(), kv_start=kv_start)
     with np.errstate(invalid="ignore", over="ignore"):
-        ref = O.decode_reference(bits(q), pool_np, bt.numpy(), lens, scale, nb, P, key_only, km, vm, **kw)
-        ref_bf = O.decode_reference(bits(q), pool_np, bt.numpy(), lens, scale, nb, P, key_only, km, vm, bf16_operands=True, **kw)
+        ref = O.decode_reference(bits(q), pool_np, bt.numpy(), lens, scale, nb, P, key_only, km, vm, sym=fmt in SYM, **kw)
+        ref_bf = O.decode_reference(bits(q), pool_np, bt.numpy(), lens, scale, nb, P, key_only, km, vm, bf16_operands=True,
+                                    sym=fmt in SYM, **kw)
     Lmax = max(max(lens), 1)
     ns, ch = (K.plan_cb(B, Lmax, Hkv, P, fmt, nsplit, G=G, tail=tail is not None) if key_only
               else K.plan_v2(B, Lmax, Hkv, P, nsplit, fmt=fmt, G=G, tail=tail is not None))
@@ -141,7 +154,7 @@ def check(res, what):
 LENS = ([1], [77], [300, 4101, 17], [1000] * 5, [0, 513, 64])
 
 
-@pytest.mark.parametrize("fmt", ["int4a", "int2a", "konlya", "konlya2"])
+@pytest.mark.parametrize("fmt", ["int4a", "int2a", "konlya", "konlya2", "int4", "konly"])
 @pytest.mark.parametrize("win", [None, (32, 9), (256, 7)])
 def test_decode_lengths_and_windows(K, fmt, win):
     for i, lens in enumerate(LENS):
@@ -160,7 +173,7 @@ def test_decode_shared_block_table_row(K, fmt, shared):
     check(run_case(K, fmt, list(range(1, 200, 7)), bt_shared=shared, win=(64, 40), seed=5), (fmt, shared))
 
 
-@pytest.mark.parametrize("fmt", ["int4a", "int2a", "konlya", "konlya2"])
+@pytest.mark.parametrize("fmt", ["int4a", "int2a", "konlya", "konlya2", "int4", "konly"])
 @pytest.mark.parametrize("ks", [4, 16, 37])
 def test_decode_kv_start(K, fmt, ks):
     for i, lens in enumerate(([ks + 1], [77], [300, 4101, 17 + ks], [0, 513, 64 + ks])):
@@ -168,7 +181,7 @@ def test_decode_kv_start(K, fmt, ks):
             check(run_case(K, fmt, lens, win=win, kv_start=ks, seed=20 + i), (fmt, lens, win, ks))
 
 
-@pytest.mark.parametrize("fmt", ["int4a", "konlya", "konlya2"])
+@pytest.mark.parametrize("fmt", ["int4a", "konlya", "konlya2", "int4"])
 @pytest.mark.parametrize("G,Hkv", [(5, 8), (8, 8), (12, 4), (6, 2)])
 def test_decode_gqa_groups(K, fmt, G, Hkv):
     for i, lens in enumerate(([1], [300, 4101, 17], [0, 513, 64])):
@@ -182,7 +195,7 @@ def test_decode_forced_splits(K, fmt, nsplit):
     check(run_case(K, fmt, [300, 4101, 17], win=(32, 9), nsplit=nsplit, seed=40), (fmt, nsplit))
 
 
-@pytest.mark.parametrize("fmt", ["int4a", "int2a", "konlya", "konlya2"])
+@pytest.mark.parametrize("fmt", ["int4a", "int2a", "konlya", "konlya2", "int4", "konly"])
 def test_decode_32_token_pages(K, fmt):
     """pages of 32 tokens (one page per 32-token step of a warp; reference dispatch kernels/csrc/attn_decode_v2.cu:2018-2060)"""
     for i, (lens, win, ks) in enumerate((([1], None, 0), ([77, 300, 4101, 17], (32, 9), 0), ([0, 513, 64], (256, 7), 0),
@@ -266,7 +279,7 @@ def test_decode_error_codes(K):
     common = lambda fmt, page, chunk, variant: L.fr_v2_attn(fmt, a[0], 512, a[1], a[2], 1, a[3], 1, 1, page, 1, chunk, 1.0,  # noqa: E731
                                                             None, None, 32, 0, 0, variant, 3, a[0], a[0], a[0], a[0], 512,
                                                             None, None, None, 0, 0, None, 4, 0)
-    assert common(4, 16, 64, 264) == -4          # symmetric INT4 pages are not built
+    assert common(3, 16, 64, 264) == -4          # not a page format of this library
     assert common(5, 8, 64, 264) == -5           # pages of 16 or 32 tokens
     assert common(5, 16, 100, 264) == -3         # chunk must be a multiple of 64
     assert common(5, 16, 64, 264 | 4096) == -8   # head dim 256

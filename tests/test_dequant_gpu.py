@@ -12,7 +12,7 @@ from tests._util import bits, calib, edge_rows
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda"
-FMT = {"int4a": (4, False), "int2a": (2, False), "konlya": (4, True), "konlya2": (2, True)}
+FMT = {"int4a": (4, False), "int2a": (2, False), "konlya": (4, True), "konlya2": (2, True), "int4": (4, False)}
 
 
 @pytest.mark.parametrize("fmt", sorted(FMT))
@@ -40,7 +40,8 @@ def test_dequant_pages_vs_oracle(fmt, P):
         K.w3_static_write(kv, slots, mask.to(DEV), hfull.to(DEV), pool, P, fmt=fmt)
     torch.cuda.synchronize()
     with np.errstate(invalid="ignore", over="ignore"):
-        Kp, Vp = O.dequant_pool(pool.cpu().numpy()[bt.numpy().astype(np.int64)], nb, P, key_only)       # [npg, P, Hkv, 128]
+        pages = pool.cpu().numpy()[bt.numpy().astype(np.int64)]
+        Kp, Vp = O.dequant_pool_sym(pages, P, False) if fmt == "int4" else O.dequant_pool(pages, nb, P, key_only)   # [npg, P, Hkv, 128]
     kr, vr = Kp.reshape(npg * P, Hkv, 128)[:L], Vp.reshape(npg * P, Hkv, 128)[:L]
     kw = {}
     if not key_only:       # stored basis -> original: block flags (orthonormal H32), then the whole head (x = H128 y / 8)

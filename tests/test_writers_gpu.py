@@ -37,7 +37,7 @@ def test_head_fwht_bit_exact(K):
         assert torch.equal(y[:, ~flags.bool()], x[:, ~flags.bool()])
 
 
-@pytest.mark.parametrize("fmt,nb", [("int4a", 4), ("int2a", 2)])
+@pytest.mark.parametrize("fmt,nb", [("int4a", 4), ("int2a", 2), ("int4", 4)])
 @pytest.mark.parametrize("T", [1, 7, 64, 129, 257, 1000])
 def test_static_writer_vs_oracle(K, fmt, nb, T):
     g = torch.Generator().manual_seed(100 + T + nb)
@@ -53,9 +53,14 @@ def test_static_writer_vs_oracle(K, fmt, nb, T):
                     mask = ((torch.rand(2 * HKV, 4, generator=g) < 0.5) & (bmode == "rand")).to(torch.uint8)
                     pool0 = torch.randint(0, 256, (npg, HKV, K.v2_chunk_bytes(P, 128, fmt)), dtype=torch.uint8, generator=g)
                     exp = pool0.numpy().copy()
-                    codes, words = O.static_rows(bits(kvb), mask.numpy(), None if hfull is None else hfull.numpy(), nb,
-                                                 kmu.numpy() if cen else None, recip=True)
-                    O.write_pool(exp, slots.numpy(), codes, words, nb, P)
+                    if fmt == "int4":       # symmetric: sign-magnitude codes, plain FP16 scale words
+                        codes, words = O.static_rows_sym(bits(kvb), mask.numpy(), None if hfull is None else hfull.numpy(),
+                                                         kmu.numpy() if cen else None)
+                        O.write_pool_sym(exp, slots.numpy(), codes, words, P)
+                    else:
+                        codes, words = O.static_rows(bits(kvb), mask.numpy(), None if hfull is None else hfull.numpy(), nb,
+                                                     kmu.numpy() if cen else None, recip=True)
+                        O.write_pool(exp, slots.numpy(), codes, words, nb, P)
                     pool = pool0.clone().to(DEV)
                     K.w3_static_write(kv, slots.to(DEV), mask.to(DEV), None if hfull is None else hfull.to(DEV), pool, P,
                                       fmt=fmt, kmu=kmu.to(DEV) if cen else None)
@@ -164,14 +169,14 @@ def test_writer_two_calls_commute(K):
 def test_writer_error_codes(K):
     L = K.lib()
     z = torch.zeros(64, dtype=torch.uint8, device=DEV)
-    assert L.fr_v2_write(4, z.data_ptr(), 0, z.data_ptr(), 1, 1, 16, None, 32, z.data_ptr(), None, 128, None) == -4
+    assert L.fr_v2_write(6, z.data_ptr(), 0, z.data_ptr(), 1, 1, 16, None, 32, z.data_ptr(), None, 128, None) == -4
     assert L.fr_v2_write(5, z.data_ptr(), 0, z.data_ptr(), 1, 1, 8, None, 32, z.data_ptr(), None, 128, None) == -5
     assert L.fr_v2_write(5, z.data_ptr(), 0, z.data_ptr(), 1, 1, 16, None, 32, z.data_ptr(), None, 256, None) == -8
     assert L.fr_v2_write(5, z.data_ptr(), 0, z.data_ptr(), 0, 1, 16, None, 32, z.data_ptr(), None, 128, None) == 0   # T = 0
     assert L.fr_cb_write(z.data_ptr(), 0, z.data_ptr(), 0, 1, 1, 16, 1, z.data_ptr(), z.data_ptr(), K.sign_words(), 3,
                          z.data_ptr(), None, 128, None) == -4
     assert L.fr_head_fwht(z.data_ptr(), 0, z.data_ptr(), 0, 1, 1, z.data_ptr(), 1.0, None, 64) == -8
-    assert L.fr_w3_static_write(z.data_ptr(), 0, z.data_ptr(), 1, 1, 16, None, None, 0, z.data_ptr(), 0, None, None) == -4
+    assert L.fr_w3_static_write(z.data_ptr(), 0, z.data_ptr(), 1, 1, 16, None, None, 3, z.data_ptr(), 0, None, None) == -4
 
 
 def test_all_slots_skipped_leaves_pool_untouched(K):
@@ -261,7 +266,7 @@ def test_static_writer_vs_reference_library(K, T):
     npg = (T + P - 1) // P + 5
     kmu = (torch.randn(HKV, 128, generator=g) * 0.5).float().to(DEV)
     st = torch.cuda.current_stream().cuda_stream
-    for fmt, asym in (("int4a", 1), ("int2a", 2)):
+    for fmt, asym in (("int4a", 1), ("int2a", 2), ("int4", 0)):
         for smode, slots in slot_patterns(T, npg, g).items():
             slots = slots.to(DEV)
             for hm in (False, True):
