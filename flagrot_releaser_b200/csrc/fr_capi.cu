@@ -32,7 +32,9 @@ bool fmt_info(int fmt, int& nb, int& ko) {
     default: return false;
   }
 }
-bool kind_info(int kind, int& nb) {
+bool kind_info(int kind, int& nb, int* sym = nullptr) {      // konly (symmetric INT4) only where the caller takes `sym`
+  if (sym != nullptr) *sym = 0;
+  if (kind == KIND_KONLY && sym != nullptr) { nb = 4; *sym = 1; return true; }
   if (kind == KIND_KONLYA) { nb = 4; return true; }
   if (kind == KIND_KONLYA2) { nb = 2; return true; }
   return false;
@@ -104,11 +106,11 @@ int fr_cb_write(const void* kv, long long kv_ts, const long long* slots, int slo
   (void)tg; (void)co; (void)sg;
   if (T <= 0) return 0;
   if (hd != 0 && hd != 128) return -8;
-  int nb;
-  if (!kind_info(kind, nb)) return -4;
+  int nb, sym;
+  if (!kind_info(kind, nb, &sym)) return -4;
   if (page != 16 && page != 32) return -5;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  return fr::dyn_keys_launch(nb, kv, kv_ts, slots, slot_ph, T, Hkv, page, CT, kmu, pool, st, 1);   // keys and value rows
+  return fr::dyn_keys_launch(nb, kv, kv_ts, slots, slot_ph, T, Hkv, page, CT, kmu, pool, st, 1, sym);   // keys and value rows
 }
 
 int fr_cb_write3(const void* kv, long long kv_ts, const long long* slots, int slot_ph, int T, int Hkv, int page,
@@ -116,14 +118,14 @@ int fr_cb_write3(const void* kv, long long kv_ts, const long long* slots, int sl
                  uint8_t* pool, int nchunk, int nchunk_v, void* stream, const float* kmu) {
   (void)co; (void)C1; (void)beta; (void)sg;   // C1 / beta are the reference's ranking tables: the bytes do not depend on them
   if (T <= 0) return 0;
-  int nb;
-  if (!kind_info(kind, nb)) return -4;
+  int nb, sym;
+  if (!kind_info(kind, nb, &sym)) return -4;
   if (page != 16 && page != 32) return -5;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (nchunk >= 0 && nchunk_v >= 0) return fr::dyn_keys_launch(nb, kv, kv_ts, slots, slot_ph, T, Hkv, page, CT, kmu, pool, st, 1);
-  if (nchunk >= 0) return fr::dyn_keys_launch(nb, kv, kv_ts, slots, slot_ph, T, Hkv, page, CT, kmu, pool, st, 0);
+  if (nchunk >= 0 && nchunk_v >= 0) return fr::dyn_keys_launch(nb, kv, kv_ts, slots, slot_ph, T, Hkv, page, CT, kmu, pool, st, 1, sym);
+  if (nchunk >= 0) return fr::dyn_keys_launch(nb, kv, kv_ts, slots, slot_ph, T, Hkv, page, CT, kmu, pool, st, 0, sym);
   if (nchunk_v >= 0)
-    return fr::rows_launch(nb, kv, kv_ts, slots, slot_ph, T, Hkv, page, nullptr, nullptr, nullptr, pool, Hkv, Hkv, 1, st);
+    return fr::rows_launch(nb, kv, kv_ts, slots, slot_ph, T, Hkv, page, nullptr, nullptr, nullptr, pool, Hkv, Hkv, 1, st, sym);
   return 0;
 }
 
@@ -144,17 +146,17 @@ int fr_cb_attn(const void* q, long long q_bs, const uint8_t* pool, const int* bl
                const void* tail, const int* tail_len, const int* tail_idx, long long tail_bs, long long tail_ts,
                void* stream, int kv_start) {
   (void)sg; (void)variant; (void)stages;
-  int nb = 4;
-  if (kind != KIND_KONLY && !kind_info(kind, nb)) return -4;     // konly: the symmetric key-only pages (decode only)
-  return attn_common(nb, kind == KIND_KONLY ? 3 : 1, q, q_bs, pool, block_table, bt_stride, seq_lens, B, Hkv, 4, page, nsplit, chunk,
+  int nb, sym;
+  if (!kind_info(kind, nb, &sym)) return -4;
+  return attn_common(nb, sym ? 3 : 1, q, q_bs, pool, block_table, bt_stride, seq_lens, B, Hkv, 4, page, nsplit, chunk,
                      qscale, nullptr, nullptr, nullptr, opart, mlpart, counter, out, o_bs, tail, tail_len, tail_idx, tail_bs,
                      tail_ts, stream, kv_start, nullptr);
 }
 
 int fr_cb_occupancy(int kind, int variant, int stages, int page) {
   (void)variant; (void)stages; (void)page;
-  int nb = 4;
-  if (kind != KIND_KONLY && !kind_info(kind, nb)) return 0;
+  int nb, sym;
+  if (!kind_info(kind, nb, &sym)) return 0;
   return fr::decode_occupancy(nb, 1);
 }
 int fr_cb_chunk_bytes(int kind, int page) { return page * (kind == KIND_KONLYA2 ? 80 : 144); }
@@ -302,8 +304,8 @@ int fr_cb_attn_noalloc(const void* q, long long q_bs, const uint8_t* pool, const
                        const int* seq_lens, int B, int Hkv, int page, int nsplit, int chunk, float qscale, int kind,
                        void* out, long long o_bs, const void* tail, const int* tail_len, const int* tail_idx,
                        long long tail_bs, long long tail_ts, void* stream, int kv_start) {
-  int nb;
-  if (!kind_info(kind, nb)) return -4;
+  int nb, sym;
+  if (!kind_info(kind, nb, &sym)) return -4;
   if (B <= 0) return 0;
   if (Hkv <= 0 || nsplit < 1) return -3;
   // layout: tickets int32 [B * Hkv] (rounded up to 256 bytes) | (max, sum) pairs | partial rows
@@ -328,7 +330,7 @@ int fr_cb_attn_noalloc(const void* q, long long q_bs, const uint8_t* pool, const
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   // the array keeps whatever the previous call (or an aborted one) left: the tickets must start at zero
   if (cudaMemsetAsync(base, 0, cnt_bytes, st) != cudaSuccess) return -1;
-  return attn_common(nb, 1, q, q_bs, pool, block_table, bt_stride, seq_lens, B, Hkv, 4, page, nsplit, chunk, qscale, nullptr,
+  return attn_common(nb, sym ? 3 : 1, q, q_bs, pool, block_table, bt_stride, seq_lens, B, Hkv, 4, page, nsplit, chunk, qscale, nullptr,
                      nullptr, nullptr, reinterpret_cast<float*>(base + cnt_bytes + ml_bytes),
                      reinterpret_cast<float*>(base + cnt_bytes), reinterpret_cast<int*>(base), out, o_bs, tail, tail_len,
                      tail_idx, tail_bs, tail_ts, stream, kv_start, nullptr);

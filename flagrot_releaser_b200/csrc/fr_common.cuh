@@ -98,6 +98,25 @@ FR_DEVI uint32_t sym_to_asym(uint32_t w) {
   return sym_offset_bytes(w & 0x87878787u) | (sym_offset_bytes(__funnelshift_l(w, w, 4) & 0x87878787u) << 4);
 }
 
+// quantiser of the dynamic writer by page kind: the symmetric one has a single form (its error form is its stored form)
+FR_DEVI float sym_deq(unsigned code, unsigned word) {
+  const float q = static_cast<float>(static_cast<int>(code & 7u));
+  return __fmul_rn((code & 8u) ? -q : q, __half2float(__ushort_as_half(static_cast<unsigned short>(word))));
+}
+template <int NB> FR_DEVI float quant_err_deq(float y, float mn, float mx);
+template <int NB, bool SYM> FR_DEVI float dyn_err_deq(float y, float mn, float mx) {
+  if (SYM) {
+    unsigned code, word;
+    quant_store_sym(y, fmaxf(-mn, mx), code, word);
+    return sym_deq(code, word);
+  }
+  return quant_err_deq<NB>(y, mn, mx);
+}
+template <int NB, bool SYM> FR_DEVI void dyn_store(float y, float mn, float mx, unsigned& code, unsigned& word) {
+  if (SYM) quant_store_sym(y, fmaxf(-mn, mx), code, word);
+  else quant_store<NB>(y, mn, mx, code, word);
+}
+
 template <int NB> FR_DEVI float quant_err_deq(float y, float mn, float mx) {
   float s, z;
   asym_params<NB>(mn, mx, s, z);

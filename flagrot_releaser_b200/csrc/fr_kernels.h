@@ -12,7 +12,7 @@ int rows_launch(int nb, const void* kv, long long kv_ts, const long long* slots,
                 const uint8_t* mask, const uint8_t* hfull, const float* kmu, uint8_t* pool, int row0, int nrow,
                 int shared15, cudaStream_t st, int sym = 0);
 int dyn_keys_launch(int nb, const void* kv, long long kv_ts, const long long* slots, int slot_ph, int T, int Hkv, int page,
-                    const float* CT, const float* kmu, uint8_t* pool, cudaStream_t st, int with_values = 0);
+                    const float* CT, const float* kmu, uint8_t* pool, cudaStream_t st, int with_values = 0, int sym = 0);
 
 // positions [start, n) of one request's pages -> K / V rows in the original basis (fr_dequant.cu)
 int dequant_pages_launch(int nb, int key_only, const uint8_t* pool, const int* bt_row, int start, int n, int Hkv, int page,

@@ -246,12 +246,12 @@ __device__ int g_wstatus;                   // != 0: the staging copy of C_q^T d
 
 // rows.T > 0 (STAGED launches only): the grid has extra rows y >= ceil(T / TG) whose CTAs write the value rows of the same
 // tokens (rows_block), so that an append is one launch; key and value writers only flip bits of their own fields
-template <int NB, int TG, bool STAGED>
+template <int NB, int TG, bool STAGED, bool SYM = false>
 __global__ void __launch_bounds__(128) k_dyn_keys(const DynParams p, const RowParams rows) {
   if (STAGED && rows.T > 0) {
     const int groups = (p.T + TG - 1) / TG;
     if (static_cast<int>(blockIdx.y) >= groups) {
-      rows_block<NB>(rows, static_cast<long long>(blockIdx.y - groups) * gridDim.x + blockIdx.x);
+      rows_block<NB, SYM>(rows, static_cast<long long>(blockIdx.y - groups) * gridDim.x + blockIdx.x);
       return;
     }
   }
@@ -290,8 +290,8 @@ __global__ void __launch_bounds__(128) k_dyn_keys(const DynParams p, const RowPa
     xs[t][i] = z;
     const float y1 = fwht32_lane(z, lane);
     const float mn0 = warp_min(z), mx0 = warp_max(z), mn1 = warp_min(y1), mx1 = warp_max(y1);
-    const float e0 = __fsub_rn(quant_err_deq<NB>(z, mn0, mx0), z);
-    const float e1 = __fsub_rn(fwht32_lane(quant_err_deq<NB>(y1, mn1, mx1), lane), z);
+    const float e0 = __fsub_rn(dyn_err_deq<NB, SYM>(z, mn0, mx0), z);
+    const float e1 = __fsub_rn(fwht32_lane(dyn_err_deq<NB, SYM>(y1, mn1, mx1), lane), z);
     float u0 = 0.f, u1 = 0.f;
     if (!staged) {                     // first use of C_q^T: the copy has had the loads and the Hadamard above to arrive
       staged = true;
@@ -309,7 +309,7 @@ __global__ void __launch_bounds__(128) k_dyn_keys(const DynParams p, const RowPa
     const float err0 = tree32(__fmul_rn(e0, u0)), err1 = tree32(__fmul_rn(e1, u1));
     const bool ch = err1 < err0;
     unsigned code, word;
-    quant_store<NB>(ch ? y1 : z, ch ? mn1 : mn0, ch ? mx1 : mx0, code, word);
+    dyn_store<NB, SYM>(ch ? y1 : z, ch ? mn1 : mn0, ch ? mx1 : mx0, code, word);
     es[t][0][i] = ch ? e1 : e0;
     cs[t][0][i] = static_cast<uint8_t>(code);
     if (lane == 0) ws[t][0][j] = static_cast<uint16_t>(word | (ch ? 0x8000u : 0u));
@@ -331,8 +331,8 @@ __global__ void __launch_bounds__(128) k_dyn_keys(const DynParams p, const RowPa
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
       unsigned code;
-      d[k] = quant_err_deq<NB>(y[k], mn, mx);
-      quant_store<NB>(y[k], mn, mx, code, word);
+      d[k] = dyn_err_deq<NB, SYM>(y[k], mn, mx);
+      dyn_store<NB, SYM>(y[k], mn, mx, code, word);
       cs[t][1][4 * lane + k] = static_cast<uint8_t>(code);
     }
     fwht_row_stages(d, lane, 128);
@@ -392,7 +392,7 @@ __global__ void __launch_bounds__(128) k_dyn_keys(const DynParams p, const RowPa
     unsigned code[4];
 #pragma unroll
     for (int k = 0; k < 4; ++k) code[k] = cs[t][c][4 * lane + k];
-    store_k_row<NB>(chunk, P, pos, lane, code, ws[t][c][lane >> 3]);
+    store_k_row<NB, SYM>(chunk, P, pos, lane, code, ws[t][c][lane >> 3]);
     if (lane == 0)   // the key's whole-head flag rides in bit 15 of the token's V group-0 scale word
       put_word_bit15(chunk, Lay<NB>::vs_off(P) + 2 * (8 * (pos >> 3) + vslot8(pos)), F);
     }
@@ -444,7 +444,7 @@ constexpr int DYN_SMEM = HD * HD * 4;        // the staged C_q^T
 
 // a decode append (a few tokens per head): one wave of CTAs with C_q^T staged in shared memory, the latency of the
 // 128-step sums is then shared-memory latency; returns 1 when the shape does not fit one wave
-template <int NB, int TG>
+template <int NB, int TG, bool SYM>
 static int dyn_keys_staged(const DynParams& p, const RowParams& rows, cudaStream_t st) {
   static int slots_of[64];                   // resident CTAs of the staged kernel, per device ordinal (0: not asked yet)
   static unsigned long long ready = 0;
@@ -452,9 +452,9 @@ static int dyn_keys_staged(const DynParams& p, const RowParams& rows, cudaStream
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -2;
   if (slots_of[dev] == 0) {
     int sms = 0, occ = 0;
-    if (!smem_limit_ready(k_dyn_keys<NB, TG, true>, DYN_SMEM, ready) ||
+    if (!smem_limit_ready(k_dyn_keys<NB, TG, true, SYM>, DYN_SMEM, ready) ||
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
-        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, k_dyn_keys<NB, TG, true>, 128, DYN_SMEM) != cudaSuccess || occ < 1)
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, k_dyn_keys<NB, TG, true, SYM>, 128, DYN_SMEM) != cudaSuccess || occ < 1)
       return -2;
     slots_of[dev] = sms * occ;
   }
@@ -463,27 +463,27 @@ static int dyn_keys_staged(const DynParams& p, const RowParams& rows, cudaStream
   if (static_cast<long long>(groups) * p.Hkv > slots) return 1;
   const long long rblocks = (static_cast<long long>(rows.T) * rows.nrow + 3) / 4;
   const int extra = static_cast<int>((rblocks + p.Hkv - 1) / p.Hkv);
-  k_dyn_keys<NB, TG, true><<<dim3(p.Hkv, groups + extra), 128, DYN_SMEM, st>>>(p, rows);
+  k_dyn_keys<NB, TG, true, SYM><<<dim3(p.Hkv, groups + extra), 128, DYN_SMEM, st>>>(p, rows);
   return check_launch();
 }
 
 // rows.T > 0: also write those value rows (in the same launch when the append path takes it, else in a second launch)
-template <int NB>
+template <int NB, bool SYM = false>
 static int dyn_keys_nb(const DynParams& p, const RowParams& rows, cudaStream_t st) {
   const long long items = static_cast<long long>(p.T) * p.Hkv;
   if (items <= 1024) {
-    const int rc = items <= 256 ? dyn_keys_staged<NB, 1>(p, rows, st) : dyn_keys_staged<NB, 2>(p, rows, st);
+    const int rc = items <= 256 ? dyn_keys_staged<NB, 1, SYM>(p, rows, st) : dyn_keys_staged<NB, 2, SYM>(p, rows, st);
     if (rc != 1) return rc;
   }
-  if (rows.T > 0) rows_kernel_launch<NB>(rows, st);
+  if (rows.T > 0) rows_kernel_launch<NB, SYM>(rows, st);
   RowParams none = rows;
   none.T = 0;
   // many tokens: C_q^T through L1 / L2 (coalesced rows), more resident CTAs, groups of up to 4 tokens share every value read
   const int tg = items <= 1024 ? 1 : items <= 4096 ? 2 : 4;
   const dim3 grid(p.Hkv, (p.T + tg - 1) / tg);
-  if (tg == 1) k_dyn_keys<NB, 1, false><<<grid, 128, 0, st>>>(p, none);
-  else if (tg == 2) k_dyn_keys<NB, 2, false><<<grid, 128, 0, st>>>(p, none);
-  else k_dyn_keys<NB, 4, false><<<grid, 128, 0, st>>>(p, none);
+  if (tg == 1) k_dyn_keys<NB, 1, false, SYM><<<grid, 128, 0, st>>>(p, none);
+  else if (tg == 2) k_dyn_keys<NB, 2, false, SYM><<<grid, 128, 0, st>>>(p, none);
+  else k_dyn_keys<NB, 4, false, SYM><<<grid, 128, 0, st>>>(p, none);
   return check_launch();
 }
 
@@ -495,11 +495,12 @@ int writer_status() {
 
 // with_values: also the value rows [Hkv, 2 Hkv) of the same tokens (one launch for a decode append, else two)
 int dyn_keys_launch(int nb, const void* kv, long long kv_ts, const long long* slots, int slot_ph, int T, int Hkv, int page,
-                    const float* CT, const float* kmu, uint8_t* pool, cudaStream_t st, int with_values) {
+                    const float* CT, const float* kmu, uint8_t* pool, cudaStream_t st, int with_values, int sym) {
   if (T <= 0) return 0;
   DynParams p{static_cast<const __nv_bfloat16*>(kv), kv_ts, slots, slot_ph, T, Hkv, page, CT, kmu, pool};
   RowParams rows{static_cast<const __nv_bfloat16*>(kv), kv_ts, slots, slot_ph, with_values ? T : 0, Hkv, page, nullptr, nullptr,
                  nullptr, pool, Hkv, Hkv, 1};
+  if (sym) return dyn_keys_nb<4, true>(p, rows, st);          // konly: symmetric INT4 quantiser in the criterion and the pages
   return nb == 4 ? dyn_keys_nb<4>(p, rows, st) : dyn_keys_nb<2>(p, rows, st);
 }
 

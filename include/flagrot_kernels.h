@@ -8,8 +8,8 @@
  * 16 | 32, -8 head dim not 128.
  *
  * Formats (fmt of fr_v2_*):  5 int4a, 8 int2a (static block flags), 7 konlya, 9 konlya2 (key-only 2x2 flags), and the
- *                            symmetric INT4 ones: 4 int4 (static; writer, decode, dequantiser), 6 konly (key-only; decode).
- * Kinds   (kind of fr_cb_*): 10 konlya (INT4), 11 konlya2 (INT2); 6 konly for fr_cb_attn only (its dynamic writer: -4).
+ *                            symmetric INT4 ones: 4 int4 (static), 6 konly (key-only).
+ * Kinds   (kind of fr_cb_*): 10 konlya (INT4), 11 konlya2 (INT2), 6 konly (symmetric INT4).
  * The ablation codebooks (kinds 1-5, 7-9) answer -4.
  * Page layout: one chunk per (page, kv head), 144 * page bytes (INT4) or 80 * page bytes (INT2), as specified in the
  * reference's kernels/csrc/attn_decode_v2.cuh:14-46.

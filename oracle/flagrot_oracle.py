@@ -588,3 +588,40 @@ def dequant_pool_sym(pool: np.ndarray, P: int, key_only: bool):
     else:
         k = k.reshape(Np, H, P, D)
     return k.transpose(0, 2, 1, 3), v.reshape(Np, H, P, D).transpose(0, 2, 1, 3)
+
+
+def dynamic_rows_sym(kv_bits: np.ndarray, C: np.ndarray, kmu: np.ndarray | None = None):
+    """dynamic writer of the symmetric key-only kind `konly`: the konlya criterion (encode_keys) with the symmetric quantiser,
+    whose error form is its stored form: deq = q * s, s = fp16(amax / 7) (kernels/codebook_ref.py:94-116 kind "cache",
+    166-236 with cfg konly).  Returns codes int8 [T, Hkv, 2, 128] in [-7, 7], words int32 [T, Hkv, 2, 4] (FP16 scale bits;
+    K: bit 15 = H32 flag of the group when the head choice is base; V group 0: bit 15 = the key's whole-head flag), and the
+    key encoder's details."""
+    kv = bf16_bits_to_f32(kv_bits)
+    Hkv = kv.shape[1] // 2
+    x = kv[:, :Hkv]
+    if kmu is not None:
+        x = x - np.asarray(kmu, dtype=F32)[None]
+    C = np.asarray(C, dtype=F32)
+
+    def qd(y):
+        q, w = quant_sym_store(y)
+        s = w.astype(np.uint16).view(np.float16).astype(F32)
+        return q, w, (q.astype(F32).reshape(*w.shape, RB) * s[..., None]).reshape(np.shape(y))
+    y1 = fwht(x, RB)
+    q0, w0, d0 = qd(x)
+    q1, w1, d1 = qd(y1)
+    rec1 = fwht(d1, RB)
+    err0, err1 = local_err_k(d0 - x, C), local_err_k(rec1 - x, C)
+    ch = err1 < err0
+    sel = np.repeat(ch, RB, -1)
+    qb, wb, recb = np.where(sel, q1, q0), np.where(ch, w1, w0), np.where(sel, rec1, d0)
+    qF, wF, dF = qd(fwht(x, D))
+    eb, eF = head_err_k(recb - x, C), head_err_k(fwht(dF, D) - x, C)
+    fflag = eF < eb
+    qk = np.where(fflag[..., None], qF, qb)
+    wk = np.where(fflag[..., None], wF, wb | (ch.astype(np.int32) << 15))
+    qv, wv = quant_sym_store(kv[:, Hkv:])
+    wv = wv.copy()
+    wv[..., 0] |= fflag.astype(np.int32) << 15
+    ek = dict(fflag=fflag, local=ch & ~fflag[..., None], head_errs=np.stack([eb, eF]))
+    return np.stack([qk, qv], 2).astype(np.int8), np.stack([wk, wv], 2).astype(np.int32), ek

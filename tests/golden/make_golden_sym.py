@@ -9,6 +9,9 @@ Recorded:
   pool / pool_codes / pool_mag    a pool of random bytes with sane scale words and what vllm_flagrot/kernels.py
                                   parse_int4_pages(asym=False) reads out of it: pins the sign-magnitude bit layout
   pool_K / pool_V                 kernels.py dequant_v2_pages(fmt "int4") of that pool in float64
+  {a,b}_qk / _qv / _wk / _wv / _mode / _local / _herr   kernels/codebook_ref.py encode(cfg "konly", qk "cache") on the inputs of
+                                  tests/golden/writer_dynamic.npz (codes q + 8, words assembled as
+                                  integrations/vllm_flagrot/tests/test_int2.py:141-152 does)
 The reference tree is needed only to regenerate the file, never to run the tests.
 """
 from __future__ import annotations
@@ -26,6 +29,7 @@ sys.path.insert(0, str(REF))
 sys.path.insert(0, str(REF / "kernels"))
 sys.path.insert(0, str(REF / "integrations" / "vllm_flagrot"))
 
+import codebook_ref as CR  # noqa: E402
 import ref as R  # noqa: E402
 from vllm_flagrot import kernels as K  # noqa: E402
 
@@ -59,6 +63,26 @@ def main():
     Kp, Vp = K.dequant_v2_pages(pool, P, torch.float64, fmt="int4")
     out.update(pool=pool.numpy(), pool_codes=codes.numpy().astype(np.int8), pool_mag=mag.numpy(),
                pool_K=Kp.numpy(), pool_V=Vp.numpy())
+    d = np.load(HERE / "writer_dynamic.npz")
+    for name in ("a", "b"):
+        kvd = bf16_of(d[f"{name}_kv"])
+        Hd = kvd.shape[1] // 2
+        Cq, co = torch.from_numpy(d[f"{name}_Cq"]), torch.from_numpy(d[f"{name}_co"])
+        k = kvd[:, :Hd].float()
+        if f"{name}_kmu" in d.files:
+            k = k - torch.from_numpy(d[f"{name}_kmu"])
+        ek = CR.encode(k, Cq, co, "k", cfg="konly", qk="cache")
+        ev = CR.encode(kvd[:, Hd:].float(), Cq, co, "v", cfg="konly", qk="cache")
+        wk = ek["s"].half().view(torch.int16).to(torch.int32) & 0xFFFF
+        wk = wk | (((ek["mode"] == 0)[..., None] & (ek["local"] == 1)).to(torch.int32) << 15)
+        wv = ev["s"].half().view(torch.int16).to(torch.int32) & 0xFFFF
+        wv[..., 0] |= (ek["mode"] == 2).to(torch.int32) << 15
+        out[f"{name}_qk"] = ek["q"].numpy().astype(np.int8)
+        out[f"{name}_qv"] = ev["q"].numpy().astype(np.int8)
+        out[f"{name}_wk"], out[f"{name}_wv"] = wk.numpy().astype(np.int32), wv.numpy().astype(np.int32)
+        out[f"{name}_mode"] = ek["mode"].numpy().astype(np.int8)
+        out[f"{name}_local"] = ek["local"].numpy().astype(np.int8)
+        out[f"{name}_herr"] = ek["head_errs"].numpy()
     np.savez_compressed(HERE / "sym_int4.npz", **out)
     print({n: a.shape for n, a in out.items()})
 

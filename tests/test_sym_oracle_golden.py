@@ -53,3 +53,16 @@ def test_pack_parse_round_trip():
     untouched = np.ones((5, P), bool)
     untouched[pg, pos] = False
     assert np.array_equal(c[untouched.nonzero()[0], :, untouched.nonzero()[1]], c0[untouched.nonzero()[0], :, untouched.nonzero()[1]])
+
+
+@pytest.mark.parametrize("name", ["a", "b"])
+def test_dynamic_konly_encoder_matches_reference(g, golden_dir, name):
+    s, _ = g
+    d = np.load(golden_dir / "writer_dynamic.npz")
+    kmu = d[f"{name}_kmu"] if f"{name}_kmu" in d.files else None
+    codes, words, ek = O.dynamic_rows_sym(d[f"{name}_kv"], d[f"{name}_Cq"], kmu)
+    assert np.array_equal(codes[:, :, 0], s[f"{name}_qk"]) and np.array_equal(codes[:, :, 1], s[f"{name}_qv"])
+    assert np.array_equal(words[:, :, 0], s[f"{name}_wk"]) and np.array_equal(words[:, :, 1], s[f"{name}_wv"])
+    assert np.array_equal(ek["fflag"], s[f"{name}_mode"] == 2) and np.array_equal(ek["local"], s[f"{name}_local"] == 1)
+    assert np.array_equal(ek["head_errs"].view(np.uint32), s[f"{name}_herr"].view(np.uint32))
+    assert ek["fflag"].any() and ek["local"].any() and (~ek["fflag"]).any()

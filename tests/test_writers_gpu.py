@@ -79,7 +79,7 @@ def test_static_writer_vs_oracle(K, fmt, nb, T):
                         assert np.array_equal(pool.cpu().numpy(), exp), ("fwht+v2_write", smode, bmode, cen)
 
 
-@pytest.mark.parametrize("kind,nb", [("konlya", 4), ("konlya2", 2)])
+@pytest.mark.parametrize("kind,nb", [("konlya", 4), ("konlya2", 2), ("konly", 4)])
 @pytest.mark.parametrize("T", [1, 7, 64, 129, 300])
 def test_dynamic_writer_vs_oracle(K, kind, nb, T):
     g = torch.Generator().manual_seed(200 + T + nb)
@@ -90,13 +90,19 @@ def test_dynamic_writer_vs_oracle(K, kind, nb, T):
     npg = (T + P - 1) // P + 5
     kmu = (torch.randn(HKV, 128, generator=g) * 0.5).float()
     for cen in (False, True):
-        codes, words, ek = O.dynamic_rows(bits(kvb), Cq.numpy(), nb, kmu.numpy() if cen else None, recip=True)
+        if kind == "konly":     # symmetric INT4: one quantiser form, sign-magnitude pages
+            codes, words, ek = O.dynamic_rows_sym(bits(kvb), Cq.numpy(), kmu.numpy() if cen else None)
+        else:
+            codes, words, ek = O.dynamic_rows(bits(kvb), Cq.numpy(), nb, kmu.numpy() if cen else None, recip=True)
         if T >= 64:
             assert ek["fflag"].any() and ek["local"].any()
         for smode, slots in slot_patterns(T, npg, g).items():
             pool0 = torch.randint(0, 256, (npg, HKV, K.cb_chunk_bytes(kind, P)), dtype=torch.uint8, generator=g)
             exp = pool0.numpy().copy()
-            O.write_pool(exp, slots.numpy(), codes, words, nb, P)
+            if kind == "konly":
+                O.write_pool_sym(exp, slots.numpy(), codes, words, P)
+            else:
+                O.write_pool(exp, slots.numpy(), codes, words, nb, P)
             km = kmu.to(DEV) if cen else None
             for how in ("v1", "v3", "v3split"):
                 pool = pool0.clone().to(DEV)
@@ -243,7 +249,7 @@ def test_dynamic_writer_vs_reference_library(K, T):
     kmu = (torch.randn(HKV, 128, generator=g) * 0.5).float().to(DEV)
     st = torch.cuda.current_stream().cuda_stream
     nk, nv = max(1, 2 * 148 // HKV), max(1, 3 * 148 // HKV)
-    for kind in ("konlya", "konlya2"):
+    for kind in ("konlya", "konlya2", "konly"):
         for smode, slots in slot_patterns(T, npg, g).items():
             slots = slots.to(DEV)
             for km in (None, kmu):
