@@ -195,6 +195,7 @@ int fr_dequant_pages(int fmt, const uint8_t* pool, const int* bt_row, int start,
   if (!fmt_info(fmt, nb, ko)) return -4;
   if (page != 16 && page != 32) return -5;
   if (start < 0 || Hkv <= 0) return -3;
+  if (n > start && (pool == nullptr || bt_row == nullptr || ok == nullptr || ov == nullptr)) return -3;
   const bool kon = (ko & 1) != 0;
   return fr::dequant_pages_launch(nb, kon, pool, bt_row, start, n, Hkv, page, kon ? nullptr : kmask, kon ? nullptr : vmask,
                                   kon ? nullptr : kfull, kon ? nullptr : vfull, ok, ov, out_fp32, static_cast<cudaStream_t>(stream),

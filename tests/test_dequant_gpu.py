@@ -70,6 +70,7 @@ def test_dequant_pages_vs_oracle(fmt, P):
 def test_dequant_pages_refusals():
     from flagrot_releaser_b200 import kernels as K
     L = K.lib()
-    assert L.fr_dequant_pages(4, None, None, 0, 16, 2, 16, None, None, None, None, None, None, 0, None) == -4
+    assert L.fr_dequant_pages(3, None, None, 0, 16, 2, 16, None, None, None, None, None, None, 0, None) == -4     # not a page format
+    assert L.fr_dequant_pages(4, None, None, 0, 16, 2, 16, None, None, None, None, None, None, 0, None) == -3     # null pool / table / outputs
     assert L.fr_dequant_pages(5, None, None, 0, 16, 2, 8, None, None, None, None, None, None, 0, None) == -5
     assert L.fr_dequant_pages(5, None, None, 7, 7, 2, 16, None, None, None, None, None, None, 0, None) == 0
