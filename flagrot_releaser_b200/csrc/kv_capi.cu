@@ -87,12 +87,14 @@ FR_DEVI void hada_row(float (&v)[4], int lane, int n) {
 }
 
 // ------------------------------------------------------------------------------------------------ value writer
-template <bool F8>
+// WMAT: the selection weighted by a full matrix M (its own instantiation: the error vectors in shared memory and the row
+// loops cost registers and occupancy that the diagonal weighting must not pay)
+template <bool F8, bool WMAT>
 __global__ void __launch_bounds__(128) k_v_write(const __nv_bfloat16* __restrict__ kv, long long kv_rs, int n, int Hkv,
                                                  const long long* __restrict__ slots, const float* __restrict__ co,
                                                  const float* __restrict__ M, uint8_t* __restrict__ pool, int ident,
                                                  const int* __restrict__ vfix) {
-  __shared__ float esh[4][3][D];            // matrix weighting: the warp's error vectors (I, H32, whole head)
+  __shared__ float esh[WMAT ? 4 : 1][3][WMAT ? D : 1];   // matrix weighting: the warp's error vectors (I, H32, whole head)
   const int lane = threadIdx.x & 31;
   const long long item = static_cast<long long>(blockIdx.x) * 4 + (threadIdx.x >> 5);
   if (item >= static_cast<long long>(n) * Hkv) return;
@@ -124,7 +126,7 @@ __global__ void __launch_bounds__(128) k_v_write(const __nv_bfloat16* __restrict
   if (!ident && vfix != nullptr) {   // frozen choice of this kv head: bits 0..3 = H32 per sub-vector, bit 16 = whole head
     useF = (vfix[h] >> 16) & 1;
     cand = useF ? 2 : ((vfix[h] >> (lane >> 3)) & 1);
-  } else if (!ident && M != nullptr) {
+  } else if (WMAT && !ident && M != nullptr) {
     // weighting by a full matrix M [Hkv, D, D] (e^T M e): the I / H32 errors of a sub-vector use its diagonal 32 x 32 block,
     // the whole-head error and the error of the chosen combination the whole matrix (reference kivi.cu:222-275; sums in
     // the reference's order, products contracted as its compiler contracts them)
@@ -637,14 +639,13 @@ int kv_v_write(const void* kv, long long kv_rs, int n, int Hkv, int Dd, const vo
   if (Dd != D) return fail("kv_v_write: D %d (head dim 128 only)", Dd);
   const unsigned blocks = static_cast<unsigned>((static_cast<long long>(n) * Hkv + 3) / 4);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (f8 & 1)
-    k_v_write<true><<<blocks, 128, 0, st>>>(static_cast<const __nv_bfloat16*>(kv), kv_rs, n, Hkv, static_cast<const long long*>(slots),
-                                            static_cast<const float*>(co), static_cast<const float*>(M), static_cast<uint8_t*>(pool),
-                                            ident, static_cast<const int*>(vfix));
-  else
-    k_v_write<false><<<blocks, 128, 0, st>>>(static_cast<const __nv_bfloat16*>(kv), kv_rs, n, Hkv, static_cast<const long long*>(slots),
-                                             static_cast<const float*>(co), static_cast<const float*>(M), static_cast<uint8_t*>(pool),
-                                             ident, static_cast<const int*>(vfix));
+  const bool wmat = M != nullptr && !ident && vfix == nullptr;
+#define KV_VW(F, W) k_v_write<F, W><<<blocks, 128, 0, st>>>(static_cast<const __nv_bfloat16*>(kv), kv_rs, n, Hkv, \
+      static_cast<const long long*>(slots), static_cast<const float*>(co), static_cast<const float*>(M), \
+      static_cast<uint8_t*>(pool), ident, static_cast<const int*>(vfix))
+  if (f8 & 1) { if (wmat) KV_VW(true, true); else KV_VW(true, false); }
+  else { if (wmat) KV_VW(false, true); else KV_VW(false, false); }
+#undef KV_VW
   return check_launch("kv_v_write");
 }
 
