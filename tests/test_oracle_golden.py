@@ -50,13 +50,15 @@ def test_static_writer_matches_reference(golden_dir):
 
 @pytest.mark.parametrize("kind,bits,key_only", [("konlya", 4, True), ("konlya2", 2, True), ("int4a", 4, False),
                                                 ("int2a", 2, False)])
-def test_page_layout_matches_reference_parsers(golden_dir, kind, bits, key_only):
-    g = np.load(golden_dir / "pages.npz")
-    kv, slots = g["kv"], g["slots"]
+@pytest.mark.parametrize("P", [16, 32])
+def test_page_layout_matches_reference_parsers(golden_dir, kind, bits, key_only, P):
+    src = np.load(golden_dir / "pages.npz")
+    g = src if P == 16 else np.load(golden_dir / "pages_p32.npz")       # 32-token pages: same rows, other slots
+    kv, slots = src["kv"], g["slots"]
     if key_only:
-        codes, words, _ = O.dynamic_rows(kv, g["Cq"], bits, None, recip=False)
+        codes, words, _ = O.dynamic_rows(kv, src["Cq"], bits, None, recip=False)
     else:
-        codes, words = O.static_rows(kv, g["mask"], None, bits, None, recip=False)
+        codes, words = O.static_rows(kv, src["mask"], None, bits, None, recip=False)
     pool = g[f"{kind}_pool0"].copy()
     O.write_pool(pool, slots, codes, words, bits, P)
     assert np.array_equal(pool, g[f"{kind}_pool"])
