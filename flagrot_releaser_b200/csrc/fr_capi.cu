@@ -82,10 +82,13 @@ int fr_v2_attn(int fmt, const void* q, long long q_bs, const uint8_t* pool, cons
 int fr_v2_write(int fmt, const void* kv, long long kv_ts, const long long* slots, int T, int Hkv, int page,
                 const uint8_t* mask, int rb, uint8_t* pool, void* stream, int hd, const float* kmu) {
   if (T <= 0) return 0;
-  if (hd != 0 && hd != 128) return -8;
+  if (hd != 0 && hd != 128 && hd != 256) return -8;
   if (fmt != FMT_INT4 && fmt != FMT_INT4A && fmt != FMT_INT2A) return -4;
   if (page != 16 && page != 32) return -5;
   if (mask != nullptr && rb != 32) return -3;
+  // head dim 256: the two 128-d halves of a head are two half heads -- kv [T, 2 Hkv, 256] = [T, 4 Hkv, 128], mask
+  // [2 Hkv, 8] = [4 Hkv, 4], kmu [Hkv, 256] = [2 Hkv, 128], pool [., Hkv, 2 chunk] = [., 2 Hkv, chunk]
+  if (hd == 256) Hkv *= 2;
   return fr::rows_launch(fmt == FMT_INT2A ? 2 : 4, kv, kv_ts, slots, 0, T, Hkv, page, mask, nullptr, kmu, pool, 0, 2 * Hkv, 0,
                          static_cast<cudaStream_t>(stream), fmt == FMT_INT4);
 }
@@ -171,8 +174,8 @@ const char* fr_last_error() { return cudaGetErrorString(cudaGetLastError()); }
 int fr_head_fwht(const void* x, long long x_ts, void* out, long long o_ts, int T, int H, const uint8_t* flags,
                  float scale, void* stream, int D) {
   if (T <= 0) return 0;
-  if (D != 128) return -8;
-  return fr::head_fwht_launch(x, x_ts, out, o_ts, T, H, flags, scale, static_cast<cudaStream_t>(stream));
+  if (D != 128 && D != 256) return -8;
+  return fr::head_fwht_launch(x, x_ts, out, o_ts, T, H, flags, scale, static_cast<cudaStream_t>(stream), D);
 }
 
 // ---- extensions (no counterpart in the reference ABI)

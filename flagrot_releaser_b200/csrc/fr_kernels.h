@@ -6,7 +6,7 @@
 namespace fr {
 
 int head_fwht_launch(const void* x, long long x_ts, void* out, long long o_ts, int T, int H, const uint8_t* flags,
-                     float scale, cudaStream_t st);
+                     float scale, cudaStream_t st, int D = 128);
 // rows [row0, row0 + nrow) of every token through the static row writer (nb = 4 | 2 code bits)
 int rows_launch(int nb, const void* kv, long long kv_ts, const long long* slots, int slot_ph, int T, int Hkv, int page,
                 const uint8_t* mask, const uint8_t* hfull, const float* kmu, uint8_t* pool, int row0, int nrow,

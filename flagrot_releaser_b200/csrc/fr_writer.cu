@@ -3,7 +3,7 @@
 // attention-weighted error; flags in the sign bits of the scale words).
 //
 // Replaces, byte for byte, the reference kernels k_paged_write (kernels/csrc/attn_decode_v2.cu:1717-1881), k_head_fwht
-// (integrations/vllm_flagrot/csrc/flagrot_capi.cu:167-197), k_cb_write (kernels/csrc/attn_codebook.cu:46-361) and the
+// and k_head_fwht256 (integrations/vllm_flagrot/csrc/flagrot_capi.cu:167-245), k_cb_write (kernels/csrc/attn_codebook.cu:46-361) and the
 // fused v3 writers (kernels/csrc/attn_cb_write3.cuh) for the kinds konlya / konlya2 and the formats int4a / int2a.
 //
 // Structure: two kernels.
@@ -24,6 +24,9 @@
 namespace fr {
 
 // ------------------------------------------------------------------------------------------------ whole-head Hadamard
+// One warp per (token, head).  NH = head dim / 128: lane l holds d = 128 s + 4 l .. + 3 of every 128-half s; the
+// butterflies of strides 1 .. 64 run inside each half, the stride-128 one (NH = 2) between the two register sets.
+template <int NH>
 __global__ void __launch_bounds__(256) k_head_fwht(const __nv_bfloat16* __restrict__ x, long long x_ts,
                                                    __nv_bfloat16* out, long long o_ts, int T, int H,
                                                    const uint8_t* __restrict__ flags, float scale) {
@@ -31,17 +34,36 @@ __global__ void __launch_bounds__(256) k_head_fwht(const __nv_bfloat16* __restri
   const int lane = threadIdx.x & 31;
   if (warp >= static_cast<long long>(T) * H) return;
   const int t = static_cast<int>(warp / H), h = static_cast<int>(warp % H);
-  const uint2 raw = *reinterpret_cast<const uint2*>(x + t * x_ts + h * HD + 4 * lane);
-  uint2 res = raw;
+  const __nv_bfloat16* src = x + t * x_ts + h * (HD * NH) + 4 * lane;
+  __nv_bfloat16* dst = out + t * o_ts + h * (HD * NH) + 4 * lane;
+  uint2 res[NH];
+#pragma unroll
+  for (int s = 0; s < NH; ++s) res[s] = *reinterpret_cast<const uint2*>(src + HD * s);
   if (flags[h]) {
-    float v[4] = {bf16_lo(raw.x), bf16_hi(raw.x), bf16_lo(raw.y), bf16_hi(raw.y)};
-    fwht_row_stages(v, lane, 128);
-    const __nv_bfloat162 r0 = __floats2bfloat162_rn(__fmul_rn(v[0], scale), __fmul_rn(v[1], scale));
-    const __nv_bfloat162 r1 = __floats2bfloat162_rn(__fmul_rn(v[2], scale), __fmul_rn(v[3], scale));
-    res.x = *reinterpret_cast<const uint32_t*>(&r0);
-    res.y = *reinterpret_cast<const uint32_t*>(&r1);
+    float v[NH][4];
+#pragma unroll
+    for (int s = 0; s < NH; ++s) {
+      v[s][0] = bf16_lo(res[s].x); v[s][1] = bf16_hi(res[s].x); v[s][2] = bf16_lo(res[s].y); v[s][3] = bf16_hi(res[s].y);
+      fwht_row_stages(v[s], lane, 128);
+    }
+    if (NH == 2) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float a = v[0][i], b = v[NH - 1][i];
+        v[0][i] = __fadd_rn(a, b);
+        v[NH - 1][i] = __fsub_rn(a, b);
+      }
+    }
+#pragma unroll
+    for (int s = 0; s < NH; ++s) {
+      const __nv_bfloat162 r0 = __floats2bfloat162_rn(__fmul_rn(v[s][0], scale), __fmul_rn(v[s][1], scale));
+      const __nv_bfloat162 r1 = __floats2bfloat162_rn(__fmul_rn(v[s][2], scale), __fmul_rn(v[s][3], scale));
+      res[s].x = *reinterpret_cast<const uint32_t*>(&r0);
+      res[s].y = *reinterpret_cast<const uint32_t*>(&r1);
+    }
   }
-  *reinterpret_cast<uint2*>(out + t * o_ts + h * HD + 4 * lane) = res;
+#pragma unroll
+  for (int s = 0; s < NH; ++s) *reinterpret_cast<uint2*>(dst + HD * s) = res[s];
 }
 
 // ------------------------------------------------------------------------------------------------ page stores
@@ -408,11 +430,13 @@ __global__ void __launch_bounds__(128) k_dyn_keys(const DynParams p, const RowPa
 static int check_launch() { return cudaPeekAtLastError() == cudaSuccess ? 0 : -1; }
 
 int head_fwht_launch(const void* x, long long x_ts, void* out, long long o_ts, int T, int H, const uint8_t* flags,
-                     float scale, cudaStream_t st) {
+                     float scale, cudaStream_t st, int D) {
   const long long warps = static_cast<long long>(T) * H;
   const unsigned blocks = static_cast<unsigned>((warps * 32 + 255) / 256);
-  k_head_fwht<<<blocks, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), x_ts, static_cast<__nv_bfloat16*>(out), o_ts,
-                                      T, H, flags, scale);
+  const auto* xi = static_cast<const __nv_bfloat16*>(x);
+  auto* xo = static_cast<__nv_bfloat16*>(out);
+  if (D == 256) k_head_fwht<2><<<blocks, 256, 0, st>>>(xi, x_ts, xo, o_ts, T, H, flags, scale);
+  else k_head_fwht<1><<<blocks, 256, 0, st>>>(xi, x_ts, xo, o_ts, T, H, flags, scale);
   return check_launch();
 }
 

@@ -293,7 +293,8 @@ def _rows_ok(kv):
 
 
 def v2_write(kv, slots, mask, rb, pool, page, fmt="int4a", kmu=None):
-    """kv bf16 [T, 2*Hkv, 128] -> pool at slots int64 [T] (< 0 skipped); mask uint8 [2*Hkv, 4] (K rows first)."""
+    """kv bf16 [T, 2*Hkv, Dh] (Dh 128 | 256) -> pool [num_pages, Hkv, chunk * Dh / 128] at slots int64 [T] (< 0 skipped);
+    mask uint8 [2*Hkv, Dh / 32] (K rows first).  Dh 256: every head is stored as two 128-d half chunks."""
     T = kv.shape[0]
     if T == 0:
         return
@@ -367,7 +368,8 @@ def cb_write3(kv, slots, CT, co, C1, beta, kind, pool, page, split=None, kmu=Non
 
 
 def head_fwht(x, flags, scale, out=None):
-    """x bf16 [T, H, 128] -> out: scale * H_128 x for the heads with flags[h] != 0, a copy otherwise; out may alias x."""
+    """x bf16 [T, H, D] (D = 128 or 256) -> out: scale * H_D x for the heads with flags[h] != 0, a copy otherwise; out may
+    alias x."""
     T, H, Dh = x.shape
     assert x.dtype == torch.bfloat16 and x.stride(2) == 1 and x.stride(1) == Dh
     if out is None:

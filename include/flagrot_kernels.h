@@ -41,9 +41,10 @@ int fr_v2_attn(int fmt, const void* q, long long q_bs, const uint8_t* pool, cons
                const int* tail_len, const int* tail_idx, long long tail_bs, long long tail_ts, void* stream, int gqa,
                int kv_start);
 
-/* Static writer: kv bf16 [T, 2*Hkv, 128] (token stride kv_ts elements, 8-byte aligned rows) -> pool at slots int64 [T]
- * (slot = page_id * page + offset; < 0 skipped); mask uint8 [2*Hkv, 4] (K rows first) or null; kmu fp32 [Hkv, 128] or null.
- * replaces flagrot_capi.cu:68-77 */
+/* Static writer: kv bf16 [T, 2*Hkv, hd] (token stride kv_ts elements, 8-byte aligned rows) -> pool at slots int64 [T]
+ * (slot = page_id * page + offset; < 0 skipped); mask uint8 [2*Hkv, hd/32] (K rows first) or null; kmu fp32 [Hkv, hd] or
+ * null.  hd = 128 (or 0), or 256: a (page, kv head) chunk is then two 128-d half chunks, dims 0-127 first.
+ * replaces flagrot_capi.cu:66-77 */
 int fr_v2_write(int fmt, const void* kv, long long kv_ts, const long long* slots, int T, int Hkv, int page,
                 const uint8_t* mask, int rb, uint8_t* pool, void* stream, int hd, const float* kmu);
 
@@ -89,8 +90,9 @@ int fr_cb_write_smem(int kind, int tg, int hd);
 /* text of the last CUDA error of the calling thread; replaces flagrot_capi.cu:155 */
 const char* fr_last_error(void);
 
-/* out[t, h, :] = flags[h] ? bf16(scale * H_128 x[t, h, :]) : x[t, h, :] (unnormalised Sylvester matrix, fp32
- * butterflies, one rounding); x and out may alias; D must be 128.  replaces flagrot_capi.cu:250-265 */
+/* out[t, h, :] = flags[h] ? bf16(scale * H_D x[t, h, :]) : x[t, h, :] (unnormalised Sylvester matrix, fp32
+ * butterflies in ascending stride order, one rounding); x and out may alias; D = 128 or 256, anything else -8.
+ * replaces flagrot_capi.cu:160-265 */
 int fr_head_fwht(const void* x, long long x_ts, void* out, long long o_ts, int T, int H, const uint8_t* flags,
                  float scale, void* stream, int D);
 

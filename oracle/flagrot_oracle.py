@@ -259,6 +259,21 @@ def static_rows(kv_bits: np.ndarray, mask: np.ndarray | None, hfull: np.ndarray 
     return codes, words
 
 
+def static_rows_256(kv_bits: np.ndarray, mask: np.ndarray | None, hfull: np.ndarray | None, bits: int = 4,
+                    kmu: np.ndarray | None = None, recip: bool = True):
+    """static writer for head dim 256: the whole-head step is H256 / 16 over the full head
+    (integrations/vllm_flagrot/csrc/flagrot_capi.cu:200-245); after it the two 128-d halves of a head are written as two
+    half heads, kv [T, 2 Hkv, 256] = [T, 4 Hkv, 128], mask [2 Hkv, 8] = [4 Hkv, 4], kmu [Hkv, 256] = [2 Hkv, 128], pool
+    [., Hkv, 2 chunk] = [., 2 Hkv, chunk] (kernels/csrc/attn_decode_v2.cu:2050-2055).  Returns codes [T, 2 Hkv, 2, 128] and
+    words [T, 2 Hkv, 2, 4] over the half heads h' = 2 h + half."""
+    T, H2, Dh = kv_bits.shape
+    assert Dh == 256
+    if hfull is not None:
+        kv_bits = head_fwht(kv_bits, hfull, 1.0 / 16.0)
+    return static_rows(kv_bits.reshape(T, 2 * H2, D), None if mask is None else np.asarray(mask).reshape(2 * H2, 4), None, bits,
+                       None if kmu is None else np.asarray(kmu, dtype=F32).reshape(H2, D), recip)
+
+
 # ------------------------------------------------------------------------------------------------ page layouts
 def chunk_bytes(bits: int, page: int) -> int:
     """bytes per (page, kv head): 144 P (INT4) / 80 P (INT2) (kernels/csrc/attn_decode_v2.cuh:14-46)."""

@@ -123,3 +123,20 @@ def test_recip_mode_differs_only_through_the_scale():
         assert np.abs(q0.astype(int) - q1.astype(int)).max() <= 1
         assert (q0 != q1).mean() < 0.02
         assert np.abs((w0 >> bits) - (w1 >> bits)).max() <= 1
+
+
+@pytest.mark.parametrize("D", [128, 256])
+def test_head_fwht_is_the_sylvester_matrix(D):
+    """small integers: every partial sum is exact in fp32, so the butterflies must equal the matrix product, and the
+    bf16 rounding of scale * y is exact for |y| / 16 below 2^8"""
+    rs = np.random.RandomState(D)
+    x = rs.randint(-1, 2, (5, 3, D)).astype(np.float32)
+    H = np.array([[1.0]])
+    while H.shape[0] < D:
+        H = np.block([[H, H], [H, -H]])
+    assert np.array_equal(O.fwht_unnorm(x, D), x.astype(np.float64) @ H)
+    xb = O.f32_to_bf16_bits(x)
+    flags = np.array([1, 0, 1], np.uint8)
+    y = O.bf16_bits_to_f32(O.head_fwht(xb, flags, 1.0 / 16.0))
+    exp = O.bf16_bits_to_f32(O.f32_to_bf16_bits((x.astype(np.float64) @ H / 16).astype(np.float32)))
+    assert np.array_equal(y[:, 0], exp[:, 0]) and np.array_equal(y[:, 2], exp[:, 2]) and np.array_equal(y[:, 1], x[:, 1])

@@ -22,13 +22,14 @@ def K():
     return kernels
 
 
-def test_head_fwht_bit_exact(K):
+@pytest.mark.parametrize("D", [128, 256])
+def test_head_fwht_bit_exact(K, D):
     g = torch.Generator().manual_seed(7)
     for T, H in ((1, 32), (5, 16), (300, 8)):
-        base = torch.randn(T, H + 3, 128, generator=g).bfloat16().to(DEV)
+        base = torch.randn(T, H + 3, D, generator=g).bfloat16().to(DEV)
         x = base[:, 1:H + 1]
         flags = (torch.rand(H, generator=g) < 0.5).to(torch.uint8)
-        y = K.head_fwht(x, flags.to(DEV), 1 / 16)
+        y = K.head_fwht(x, flags.to(DEV), 1 / 16)                            # (1 / 16: the orthonormal scale of D = 256)
         exp = O.head_fwht(bits(x), flags.numpy(), 1 / 16)
         assert np.array_equal(bits(y), exp)
         xc = x.contiguous()
@@ -177,7 +178,7 @@ def test_writer_error_codes(K):
     z = torch.zeros(64, dtype=torch.uint8, device=DEV)
     assert L.fr_v2_write(6, z.data_ptr(), 0, z.data_ptr(), 1, 1, 16, None, 32, z.data_ptr(), None, 128, None) == -4
     assert L.fr_v2_write(5, z.data_ptr(), 0, z.data_ptr(), 1, 1, 8, None, 32, z.data_ptr(), None, 128, None) == -5
-    assert L.fr_v2_write(5, z.data_ptr(), 0, z.data_ptr(), 1, 1, 16, None, 32, z.data_ptr(), None, 256, None) == -8
+    assert L.fr_v2_write(5, z.data_ptr(), 0, z.data_ptr(), 1, 1, 16, None, 32, z.data_ptr(), None, 64, None) == -8    # head dims other than 128 and 256
     assert L.fr_v2_write(5, z.data_ptr(), 0, z.data_ptr(), 0, 1, 16, None, 32, z.data_ptr(), None, 128, None) == 0   # T = 0
     assert L.fr_cb_write(z.data_ptr(), 0, z.data_ptr(), 0, 1, 1, 16, 1, z.data_ptr(), z.data_ptr(), K.sign_words(), 3,
                          z.data_ptr(), None, 128, None) == -4
@@ -288,3 +289,47 @@ def test_static_writer_vs_reference_library(K, T):
                     K.w3_static_write(kv, slots, mask, hfull, b, P, fmt=fmt, kmu=km)
                     torch.cuda.synchronize()
                     assert torch.equal(a, b), (fmt, smode, hm, km is not None, int((a != b).sum()))
+
+
+@pytest.mark.parametrize("D", [128, 256])
+def test_head_fwht_vs_reference_library(K, D):
+    """the whole-head Hadamard against the reference's own kernels (k_head_fwht / k_head_fwht256), strided rows included"""
+    R = _ref()
+    g = torch.Generator().manual_seed(500 + D)
+    st = torch.cuda.current_stream().cuda_stream
+    for T, H in ((1, 4), (33, 16), (1000, 8)):
+        base = (torch.randn(T, H + 2, D, generator=g) * torch.exp2(torch.randint(-6, 7, (T, H + 2, 1), generator=g).float())).bfloat16().to(DEV)
+        x = base[:, 1:H + 1]
+        flags = (torch.rand(H, generator=g) < 0.6).to(torch.uint8).to(DEV)
+        a = torch.empty(T, H, D, dtype=torch.bfloat16, device=DEV)
+        assert R.fr_head_fwht(x.data_ptr(), x.stride(0), a.data_ptr(), a.stride(0), T, H, flags.data_ptr(), 1 / 16, st, D) == 0
+        b = K.head_fwht(x, flags, 1 / 16)
+        torch.cuda.synchronize()
+        assert torch.equal(a.view(torch.int16), b.view(torch.int16)), (T, H)
+
+
+@pytest.mark.parametrize("fmt,nb", [("int4a", 4), ("int2a", 2)])
+@pytest.mark.parametrize("page", [16, 32])
+def test_static_writer_head_dim_256(K, fmt, nb, page):
+    """head dim 256: fr_head_fwht (H256 / 16 on flagged heads) + fr_v2_write(hd = 256), two 128-d half chunks per (page,
+    kv head), against the oracle's bytes; untouched bytes stay untouched"""
+    g = torch.Generator().manual_seed(2560 + nb + page)
+    for T in (1, 45, 300):
+        kv = torch.cat([edge_rows(T, HKV, g), edge_rows(T, HKV, g)], -1).to(DEV)            # [T, 2 Hkv, 256]
+        npg = (T + page - 1) // page + 3
+        mask = (torch.rand(2 * HKV, 8, generator=g) < 0.5).to(torch.uint8)
+        hfull = (torch.rand(2 * HKV, generator=g) < 0.5).to(torch.uint8)
+        kmu = (torch.randn(HKV, 256, generator=g) * 0.5).float()
+        slots = torch.randperm(npg * page, generator=g)[:T].long()
+        slots[torch.rand(T, generator=g) < 0.1] = -1
+        pool0 = torch.randint(0, 256, (npg, HKV, K.v2_chunk_bytes(page, 256, fmt)), dtype=torch.uint8, generator=g)
+        for km in (None, kmu):
+            pool = pool0.clone().to(DEV)
+            x = K.head_fwht(kv, hfull.to(DEV), 1 / 16)
+            K.v2_write(x, slots.to(DEV), mask.to(DEV), 32, pool, page, fmt=fmt, kmu=None if km is None else km.to(DEV))
+            torch.cuda.synchronize()
+            codes, words = O.static_rows_256(bits(kv), mask.numpy(), hfull.numpy(), nb, None if km is None else km.numpy())
+            exp = pool0.numpy().copy()
+            O.write_pool(exp.reshape(npg, 2 * HKV, -1), slots.numpy(), codes, words, nb, page)
+            got = pool.cpu().numpy()
+            assert np.array_equal(got, exp), (T, km is not None, int((got != exp).sum()))
