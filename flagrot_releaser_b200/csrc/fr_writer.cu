@@ -426,6 +426,210 @@ __global__ void __launch_bounds__(128) k_dyn_keys(const DynParams p, const RowPa
   if (STAGED && stage_lost) tc5::mbar_wait(wsmem_u32(&ctbar), 0);
 }
 
+// ------------------------------------------------------------------------------------------------ dynamic key writer, bulk
+// Same arithmetic as k_dyn_keys, arranged for many tokens: 8 tokens per CTA share every C_q^T value read, and the two
+// candidates of a choice (I / H32 of a 32-vector, base / F of the head) ride in the halves of packed fp32 pairs
+// (mul.f32x2 / add.f32x2 round each half like the scalar instruction, so the sequential sums are unchanged), which halves
+// the arithmetic instructions and lets one 16-byte shared load feed four products.  CTAs are numbered head-major, so the
+// CTAs resident on an SM at one time read the same 64 KB of C_q^T through L1.
+FR_DEVI float2 tree32x2(float2 v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1)
+    v = __fadd2_rn(v, make_float2(__shfl_xor_sync(FULLMASK, v.x, o), __shfl_xor_sync(FULLMASK, v.y, o)));
+  return v;
+}
+
+// one quantizer evaluation for both forms of the dynamic writer: the error form (unwidened range) gives the
+// dequantized value of the criterion, the stored form (range widened to include 0) the code and the scale word.  When
+// the group's range already contains 0 the two forms have the same parameters, so the second evaluation is skipped.
+template <int NB, bool SYM> struct DynQ {
+  float s, z, s2, z2;
+  bool same;
+  FR_DEVI DynQ(float mn, float mx) {
+    if (SYM) {
+      s = mn; z = mx; same = true; s2 = z2 = 0.f;     // (the symmetric quantizer has a single form; keeps the range)
+    } else {
+      asym_params<NB>(mn, mx, s, z);
+      same = mn <= 0.f && mx >= 0.f;
+      s2 = s; z2 = z;
+      if (!same) asym_params<NB>(fminf(mn, 0.f), fmaxf(mx, 0.f), s2, z2);
+    }
+  }
+  FR_DEVI void element(float y, float& deq, unsigned& code) const {
+    if (SYM) {
+      unsigned word;
+      quant_store_sym(y, fmaxf(-s, z), code, word);
+      deq = sym_deq(code, word);
+    } else {
+      const float q = asym_code<NB>(y, s, z);
+      deq = __fmul_rn(__fsub_rn(q, z), s);
+      code = static_cast<unsigned>(same ? q : asym_code<NB>(y, s2, z2));
+    }
+  }
+  FR_DEVI unsigned word() const {
+    if (SYM) return __half_as_ushort(__float2half_rn(__fmul_rn(fmaxf(-s, z), 1.0f / 7.0f)));
+    return scale_word<NB>(s2, static_cast<unsigned>(z2));
+  }
+};
+
+template <int NB, bool SYM>
+__global__ void __launch_bounds__(128) k_dyn_keys_bulk(const DynParams p, int groups) {
+  constexpr int TG = 8;
+  __shared__ __align__(16) float2 es[TG][HD];        // reconstruction errors of the head candidates (x: base, y: F)
+  __shared__ __align__(16) float2 ps[TG][HD];        // first the errors of the local candidates (x: I, y: H32), then e * u
+  __shared__ __align__(4) uint8_t cs[TG][2][HD];     // stored codes of the head candidates
+  __shared__ __align__(8) uint16_t lc[TG][HD];       // stored codes of the local candidates (low byte I, high byte H32)
+  __shared__ uint16_t lw[TG][2][4];                  // and their scale words
+  __shared__ uint16_t ws[TG][2][4];                  // stored scale words of the head candidates (base: with the H32 flag)
+  const int i = threadIdx.x, lane = i & 31, j = i >> 5;
+  const int h = blockIdx.x / groups, t0 = (blockIdx.x % groups) * TG;
+  const int ntok = min(TG, p.T - t0);
+  const float* CT = p.CT + static_cast<size_t>(h) * HD * HD;
+
+  // ---- A: candidates of every token in the row mapping (warp j takes tokens j, j + 4; lane l holds d = 4 l .. 4 l + 3,
+  //         32-vector = 8 lanes): both local candidates I / H32 (errors, stored codes, words) and the whole-head candidate F
+  for (int t = j; t < TG; t += 4) {
+    float x[4] = {0.f, 0.f, 0.f, 0.f};
+    if (t < ntok) {
+      const uint2 raw = *reinterpret_cast<const uint2*>(p.kv + (t0 + t) * p.kv_ts + h * HD + 4 * lane);
+      x[0] = bf16_lo(raw.x); x[1] = bf16_hi(raw.x); x[2] = bf16_lo(raw.y); x[3] = bf16_hi(raw.y);
+    }
+    if (p.kmu != nullptr) {
+      const float4 m = __ldg(reinterpret_cast<const float4*>(p.kmu + h * HD + 4 * lane));
+      x[0] = __fsub_rn(x[0], m.x); x[1] = __fsub_rn(x[1], m.y); x[2] = __fsub_rn(x[2], m.z); x[3] = __fsub_rn(x[3], m.w);
+    }
+    float e0[4], e1[4];
+    unsigned c0 = 0, c1 = 0;
+    {   // I
+      const DynQ<NB, SYM> q(group_min8(fminf(fminf(x[0], x[1]), fminf(x[2], x[3]))),
+                            group_max8(fmaxf(fmaxf(x[0], x[1]), fmaxf(x[2], x[3]))));
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        float d; unsigned c;
+        q.element(x[k], d, c);
+        e0[k] = __fsub_rn(d, x[k]);
+        c0 |= c << (8 * k);
+      }
+      if ((lane & 7) == 0) lw[t][0][lane >> 3] = static_cast<uint16_t>(q.word());
+    }
+    {   // H32
+      float y[4] = {x[0], x[1], x[2], x[3]};
+      fwht_row_stages(y, lane, 32);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) y[k] = __fmul_rn(y[k], C32);
+      const DynQ<NB, SYM> q(group_min8(fminf(fminf(y[0], y[1]), fminf(y[2], y[3]))),
+                            group_max8(fmaxf(fmaxf(y[0], y[1]), fmaxf(y[2], y[3]))));
+      float d[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        unsigned c;
+        q.element(y[k], d[k], c);
+        c1 |= c << (8 * k);
+      }
+      fwht_row_stages(d, lane, 32);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) e1[k] = __fsub_rn(__fmul_rn(d[k], C32), x[k]);
+      if ((lane & 7) == 0) lw[t][1][lane >> 3] = static_cast<uint16_t>(q.word());
+    }
+    *reinterpret_cast<float4*>(&ps[t][4 * lane]) = make_float4(e0[0], e1[0], e0[1], e1[1]);
+    *reinterpret_cast<float4*>(&ps[t][4 * lane + 2]) = make_float4(e0[2], e1[2], e0[3], e1[3]);
+    {   // byte k of c0 / c1 -> 16-bit cells (I low, H32 high)
+      const unsigned lo = __byte_perm(c0, c1, 0x5140), hi = __byte_perm(c0, c1, 0x7362);
+      *reinterpret_cast<uint2*>(&lc[t][4 * lane]) = make_uint2(lo, hi);
+    }
+    {   // F = H128
+      float y[4] = {x[0], x[1], x[2], x[3]};
+      fwht_row_stages(y, lane, 128);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) y[k] = __fmul_rn(y[k], C128);
+      const DynQ<NB, SYM> q(group_min8(fminf(fminf(y[0], y[1]), fminf(y[2], y[3]))),
+                            group_max8(fmaxf(fmaxf(y[0], y[1]), fmaxf(y[2], y[3]))));
+      float d[4];
+      unsigned cf = 0;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        unsigned c;
+        q.element(y[k], d[k], c);
+        cf |= c << (8 * k);
+      }
+      fwht_row_stages(d, lane, 128);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) es[t][4 * lane + k].y = __fsub_rn(__fmul_rn(d[k], C128), x[k]);
+      *reinterpret_cast<uint32_t*>(&cs[t][1][4 * lane]) = cf;
+      if ((lane & 7) == 0) ws[t][1][lane >> 3] = static_cast<uint16_t>(q.word());
+    }
+  }
+  __syncthreads();
+  {   // ---- A1 (dim mapping, thread i = dim i, 32-vector j = warp j): block-diagonal weighted error u_i = seq_k C[i][32 j + k] e_k
+    //      of both local candidates, first argmin
+    float2 U[TG];
+#pragma unroll
+    for (int k = 0; k < 32; k += 2) {
+      const float ca = __ldg(CT + (32 * j + k) * HD + i), cb = __ldg(CT + (32 * j + k + 1) * HD + i);
+#pragma unroll
+      for (int t = 0; t < TG; ++t) {
+        const float4 e = *reinterpret_cast<const float4*>(&ps[t][32 * j + k]);
+        const float2 pa = __fmul2_rn(make_float2(ca, ca), make_float2(e.x, e.y));
+        U[t] = k == 0 ? pa : __fadd2_rn(U[t], pa);
+        U[t] = __fadd2_rn(U[t], __fmul2_rn(make_float2(cb, cb), make_float2(e.z, e.w)));
+      }
+    }
+#pragma unroll
+    for (int t = 0; t < TG; ++t) {
+      const float2 own = ps[t][i];
+      const float2 err = tree32x2(__fmul2_rn(own, U[t]));
+      const bool ch = err.y < err.x;
+      es[t][i].x = ch ? own.y : own.x;
+      const unsigned c = lc[t][i];
+      cs[t][0][i] = static_cast<uint8_t>(ch ? c >> 8 : c & 0xFFu);
+      if (lane == 0) ws[t][0][j] = static_cast<uint16_t>(ch ? (lw[t][1][j] | 0x8000u) : lw[t][0][j]);
+    }
+  }
+  __syncthreads();
+  // ---- B: u_i = ((U0 + U1) + U2) + U3, U_b = seq_{k in block b} C[i][k] e_k, for every (token, head candidate)
+  {
+    float2 u[TG];
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+      float2 U[TG];
+#pragma unroll 8
+      for (int k = 0; k < 32; k += 2) {
+        const float ca = __ldg(CT + (32 * b + k) * HD + i), cb = __ldg(CT + (32 * b + k + 1) * HD + i);
+#pragma unroll
+        for (int t = 0; t < TG; ++t) {
+          const float4 e = *reinterpret_cast<const float4*>(&es[t][32 * b + k]);
+          const float2 pa = __fmul2_rn(make_float2(ca, ca), make_float2(e.x, e.y));
+          U[t] = k == 0 ? pa : __fadd2_rn(U[t], pa);
+          U[t] = __fadd2_rn(U[t], __fmul2_rn(make_float2(cb, cb), make_float2(e.z, e.w)));
+        }
+      }
+#pragma unroll
+      for (int t = 0; t < TG; ++t) u[t] = b == 0 ? U[t] : __fadd2_rn(u[t], U[t]);
+    }
+#pragma unroll
+    for (int t = 0; t < TG; ++t) ps[t][i] = __fmul2_rn(es[t][i], u[t]);
+  }
+  __syncthreads();
+  // ---- C + D: halving tree of e * u over the 128 dims, head choice and page write (warp j takes tokens j, j + 4)
+  for (int t = j; t < ntok; t += 4) {
+    const float2 a = __fadd2_rn(ps[t][lane], ps[t][lane + 64]), b = __fadd2_rn(ps[t][lane + 32], ps[t][lane + 96]);
+    const float2 herr = tree32x2(__fadd2_rn(a, b));
+    const long long slot = p.slot_ph ? p.slots[static_cast<long long>(t0 + t) * p.Hkv + h] : p.slots[t0 + t];
+    if (slot < 0) continue;
+    const bool F = herr.y < herr.x;
+    const int c = F ? 1 : 0;
+    const int P = p.page;
+    const long long page = slot / P;
+    const int pos = static_cast<int>(slot % P);
+    uint8_t* chunk = p.pool + (page * p.Hkv + h) * static_cast<long long>(Lay<NB>::chunk(P));
+    const unsigned cw = *reinterpret_cast<const uint32_t*>(&cs[t][c][4 * lane]);
+    const unsigned code[4] = {cw & 0xFFu, (cw >> 8) & 0xFFu, (cw >> 16) & 0xFFu, cw >> 24};
+    store_k_row<NB, SYM>(chunk, P, pos, lane, code, ws[t][c][lane >> 3]);
+    if (lane == 0)   // the key's whole-head flag rides in bit 15 of the token's V group-0 scale word
+      put_word_bit15(chunk, Lay<NB>::vs_off(P) + 2 * (8 * (pos >> 3) + vslot8(pos)), F);
+  }
+}
+
 // ------------------------------------------------------------------------------------------------ launchers
 static int check_launch() { return cudaPeekAtLastError() == cudaSuccess ? 0 : -1; }
 
@@ -503,11 +707,15 @@ static int dyn_keys_nb(const DynParams& p, const RowParams& rows, cudaStream_t s
   RowParams none = rows;
   none.T = 0;
   // many tokens: C_q^T through L1 / L2 (coalesced rows), more resident CTAs, groups of up to 4 tokens share every value read
-  const int tg = items <= 1024 ? 1 : items <= 4096 ? 2 : 4;
+  const int tg = items <= 1024 ? 1 : items <= 4096 ? 2 : 8;
   const dim3 grid(p.Hkv, (p.T + tg - 1) / tg);
   if (tg == 1) k_dyn_keys<NB, 1, false, SYM><<<grid, 128, 0, st>>>(p, none);
   else if (tg == 2) k_dyn_keys<NB, 2, false, SYM><<<grid, 128, 0, st>>>(p, none);
-  else k_dyn_keys<NB, 4, false, SYM><<<grid, 128, 0, st>>>(p, none);
+  else {
+    const long long groups = (p.T + 7) / 8;
+    if (groups * p.Hkv > 0x7FFFFFFFll) return -3;
+    k_dyn_keys_bulk<NB, SYM><<<static_cast<unsigned>(groups * p.Hkv), 128, 0, st>>>(p, static_cast<int>(groups));
+  }
   return check_launch();
 }
 

@@ -81,7 +81,7 @@ def test_static_writer_vs_oracle(K, fmt, nb, T):
 
 
 @pytest.mark.parametrize("kind,nb", [("konlya", 4), ("konlya2", 2), ("konly", 4)])
-@pytest.mark.parametrize("T", [1, 7, 64, 129, 300])
+@pytest.mark.parametrize("T", [1, 7, 64, 129, 300, 521])
 def test_dynamic_writer_vs_oracle(K, kind, nb, T):
     g = torch.Generator().manual_seed(200 + T + nb)
     kvb = edge_rows(T, HKV, g)
@@ -237,7 +237,7 @@ def ref_writer_tables(Cq):
     return tab.contiguous(), aux.float().contiguous()
 
 
-@pytest.mark.parametrize("T", [1, 64, 257, 1000, 4097])
+@pytest.mark.parametrize("T", [1, 64, 257, 700, 1000, 4097])
 def test_dynamic_writer_vs_reference_library(K, T):
     R = _ref()
     g = torch.Generator().manual_seed(300 + T)
