@@ -205,6 +205,11 @@ int fr_dequant_pages(int fmt, const uint8_t* pool, const int* bt_row, int start,
                                   ko >> 1);
 }
 
+// bulk key writer of fr_cb_write / fr_cb_write3: counters {(token, head) pairs, pairs whose head choice took the exact sums}
+// since the last reset (device-wide), and a test switch that makes every choice take the exact sums (same bytes)
+int fr_dyn_writer_stats(unsigned long long* out2, int reset) { return fr::dyn_writer_stats(out2, reset); }
+void fr_dyn_writer_exact_only(int on) { fr::dyn_writer_exact_only(on); }
+
 int fr_device_status() {
   const int d = fr::decode_status();
   if (d != 0) return d;

@@ -46,6 +46,8 @@ size_t xchg_bytes(int rows);
 int xchg_launch(const float* part, void* const* bufs, int rank, int R, int rows, void* out, int out_fp32, cudaStream_t st);
 int xchg_selftest_launch(const float* const* parts, void* const* bufs, int R, int rows, void* const* outs, int out_fp32, cudaStream_t st);
 int xchg_status();     // 0, or the source line of the peer wait that gave up (sticky)
+void dyn_writer_exact_only(int on);                          // test switch of the bulk key writer (host state, not per stream)
+int dyn_writer_stats(unsigned long long* out2, int reset);   // {(token, head) pairs, pairs that took the exact sums} of the bulk key writer
 int writer_status();   // 0, or the source line of the staging wait that gave up (sticky; results stay correct)
 int decode_status();   // 0, or the source line of a bounded wait that gave up (sticky)
 

@@ -472,10 +472,25 @@ template <int NB, bool SYM> struct DynQ {
   }
 };
 
+// counters of the bulk key writer: [0] (token, head) pairs written, [1] those whose head choice needed the exact sums
+__device__ unsigned long long g_dynstat[2];
+// relative half-width of the estimate's error bar, in units of sum |e_i| |C_ik| |e_k| (see the kernel's phase B)
+constexpr float DYN_DELTA = 0.005f;
+
+FR_DEVI void mma_tf32(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
 template <int NB, bool SYM>
-__global__ void __launch_bounds__(128) k_dyn_keys_bulk(const DynParams p, int groups) {
+__global__ void __launch_bounds__(128) k_dyn_keys_bulk(const DynParams p, int groups, int exact_only) {
   constexpr int TG = 8;
-  __shared__ __align__(16) float2 es[TG][HD];        // reconstruction errors of the head candidates (x: base, y: F)
+  // reconstruction errors of the head candidates (x: base, y: F); rows padded by 8 floats: the 16 (token, candidate)
+  // rows of an MMA operand then fall into different banks
+  __shared__ __align__(16) float2 es[TG][HD + 4];
+  __shared__ float est[4][2 * TG][2];                // per warp: partial (estimate, bound) of row 2 t + c
+  __shared__ int hsel[TG];                           // head choice of token t: 0 base, 1 F, 2 undecided (exact sums needed)
   __shared__ __align__(16) float2 ps[TG][HD];        // first the errors of the local candidates (x: I, y: H32), then e * u
   __shared__ __align__(4) uint8_t cs[TG][2][HD];     // stored codes of the head candidates
   __shared__ __align__(8) uint16_t lc[TG][HD];       // stored codes of the local candidates (low byte I, high byte H32)
@@ -586,37 +601,110 @@ __global__ void __launch_bounds__(128) k_dyn_keys_bulk(const DynParams p, int gr
     }
   }
   __syncthreads();
-  // ---- B: u_i = ((U0 + U1) + U2) + U3, U_b = seq_{k in block b} C[i][k] e_k, for every (token, head candidate)
+  // ---- B: head choice.  The criterion is herr_c = fl(sum_i e_i u_i), u_i = fl(sum_k C[i][k] e_k), summed in a fixed fp32
+  //      order; F is chosen when herr_1 < herr_0.  First an estimate on the tensor cores: with T_c = e^T C e and
+  //      S_c = sum_ik |e_i| |C_ik| |e_k| in real arithmetic, the fixed-order value satisfies |herr_c - T_c| <= 2^-18 S_c (43
+  //      roundings on the path of a term), and E_c = sum_i e_i (C~ e~)_i with TF32 operands (each within 2^-10 of its
+  //      value) and fp32 accumulation satisfies |E_c - T_c| <= 0.0020 S_c; B_c = sum_i |e_i| (|C~| |e~|)_i >= 0.9979 S_c.
+  //      So |herr_c - E_c| < DYN_DELTA B_c with a margin of 2.5, and the choice is certain whenever the two error bars do
+  //      not overlap.  Only the undecided tokens (non-finite values included: every comparison is then false) take the
+  //      exact sums u_i = ((U0 + U1) + U2) + U3, U_b = seq_{k in block b} C[i][k] e_k.
   {
-    float2 u[TG];
+    const int g = lane >> 2, q = lane & 3;
+    // MMA rows: row g = (token g >> 1, candidate g & 1), row g + 8 = (token (g >> 1) + 4, same candidate): row = 2 t + c
+    const float* ea = reinterpret_cast<const float*>(&es[g >> 1][0]) + (g & 1);
+    const float* eb = reinterpret_cast<const float*>(&es[(g >> 1) + 4][0]) + (g & 1);
+    float acc[4][4], bnd[4][4];
 #pragma unroll
-    for (int b = 0; b < 4; ++b) {
-      float2 U[TG];
-#pragma unroll 8
-      for (int k = 0; k < 32; k += 2) {
-        const float ca = __ldg(CT + (32 * b + k) * HD + i), cb = __ldg(CT + (32 * b + k + 1) * HD + i);
+    for (int n = 0; n < 4; ++n)
 #pragma unroll
-        for (int t = 0; t < TG; ++t) {
-          const float4 e = *reinterpret_cast<const float4*>(&es[t][32 * b + k]);
-          const float2 pa = __fmul2_rn(make_float2(ca, ca), make_float2(e.x, e.y));
-          U[t] = k == 0 ? pa : __fadd2_rn(U[t], pa);
-          U[t] = __fadd2_rn(U[t], __fmul2_rn(make_float2(cb, cb), make_float2(e.z, e.w)));
+      for (int r = 0; r < 4; ++r) { acc[n][r] = 0.f; bnd[n][r] = 0.f; }
+    if (!exact_only) {
+#pragma unroll 4
+      for (int k0 = 0; k0 < HD; k0 += 8) {
+        uint32_t a[4], aa[4];
+        a[0] = __float_as_uint(ea[2 * (k0 + q)]); a[1] = __float_as_uint(eb[2 * (k0 + q)]);
+        a[2] = __float_as_uint(ea[2 * (k0 + q + 4)]); a[3] = __float_as_uint(eb[2 * (k0 + q + 4)]);
+#pragma unroll
+        for (int r = 0; r < 4; ++r) aa[r] = a[r] & 0x7FFFFFFFu;
+#pragma unroll
+        for (int n = 0; n < 4; ++n) {     // B[k][n] = C[i = 32 j + 8 n + g][k0 + q (+ 4)]
+          const float* cp = CT + (k0 + q) * HD + 32 * j + 8 * n + g;
+          const uint32_t b0 = __float_as_uint(__ldg(cp)), b1 = __float_as_uint(__ldg(cp + 4 * HD));
+          mma_tf32(acc[n], a, b0, b1);
+          mma_tf32(bnd[n], aa, b0 & 0x7FFFFFFFu, b1 & 0x7FFFFFFFu);
         }
       }
+    }
+    float E0 = 0.f, B0 = 0.f, E1 = 0.f, B1 = 0.f;    // rows g and g + 8 over this thread's 8 columns
 #pragma unroll
-      for (int t = 0; t < TG; ++t) u[t] = b == 0 ? U[t] : __fadd2_rn(u[t], U[t]);
+    for (int n = 0; n < 4; ++n) {
+      const int i0 = 32 * j + 8 * n + 2 * q;
+      const float x0 = ea[2 * i0], x1 = ea[2 * i0 + 2], y0 = eb[2 * i0], y1 = eb[2 * i0 + 2];
+      E0 = fmaf(x0, acc[n][0], fmaf(x1, acc[n][1], E0));
+      B0 = fmaf(fabsf(x0), bnd[n][0], fmaf(fabsf(x1), bnd[n][1], B0));
+      E1 = fmaf(y0, acc[n][2], fmaf(y1, acc[n][3], E1));
+      B1 = fmaf(fabsf(y0), bnd[n][2], fmaf(fabsf(y1), bnd[n][3], B1));
     }
 #pragma unroll
-    for (int t = 0; t < TG; ++t) ps[t][i] = __fmul2_rn(es[t][i], u[t]);
+    for (int o = 1; o < 4; o <<= 1) {
+      E0 += __shfl_xor_sync(FULLMASK, E0, o); B0 += __shfl_xor_sync(FULLMASK, B0, o);
+      E1 += __shfl_xor_sync(FULLMASK, E1, o); B1 += __shfl_xor_sync(FULLMASK, B1, o);
+    }
+    if (q == 0) { est[j][g][0] = E0; est[j][g][1] = B0; est[j][g + 8][0] = E1; est[j][g + 8][1] = B1; }
   }
   __syncthreads();
-  // ---- C + D: halving tree of e * u over the 128 dims, head choice and page write (warp j takes tokens j, j + 4)
+  if (i < TG) {
+    float E[2], D[2];
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+      E[c] = (est[0][2 * i + c][0] + est[1][2 * i + c][0]) + (est[2][2 * i + c][0] + est[3][2 * i + c][0]);
+      D[c] = (est[0][2 * i + c][1] + est[1][2 * i + c][1]) + (est[2][2 * i + c][1] + est[3][2 * i + c][1]);
+    }
+    // (bounds below 1e-20: products may have been flushed on the way, no estimate)
+    const bool usable = !exact_only && D[0] > 1e-20f && D[1] > 1e-20f;
+    const bool surelyF = usable && E[1] + DYN_DELTA * D[1] < E[0] - DYN_DELTA * D[0];
+    const bool surelyBase = usable && E[1] - DYN_DELTA * D[1] > E[0] + DYN_DELTA * D[0];
+    hsel[i] = surelyF ? 1 : surelyBase ? 0 : 2;
+  }
+  __syncthreads();
+  {
+    int nexact = 0;
+    for (int t = 0; t < ntok; ++t) {
+      if (hsel[t] != 2) continue;
+      ++nexact;
+      float2 u;
+#pragma unroll
+      for (int b = 0; b < 4; ++b) {
+        float2 U;
+#pragma unroll 8
+        for (int k = 0; k < 32; k += 2) {
+          const float ca = __ldg(CT + (32 * b + k) * HD + i), cb = __ldg(CT + (32 * b + k + 1) * HD + i);
+          const float4 e = *reinterpret_cast<const float4*>(&es[t][32 * b + k]);
+          const float2 pa = __fmul2_rn(make_float2(ca, ca), make_float2(e.x, e.y));
+          U = k == 0 ? pa : __fadd2_rn(U, pa);
+          U = __fadd2_rn(U, __fmul2_rn(make_float2(cb, cb), make_float2(e.z, e.w)));
+        }
+        u = b == 0 ? U : __fadd2_rn(u, U);
+      }
+      ps[t][i] = __fmul2_rn(es[t][i], u);
+    }
+    if (i == 0) {
+      atomicAdd(&g_dynstat[0], static_cast<unsigned long long>(ntok));
+      if (nexact) atomicAdd(&g_dynstat[1], static_cast<unsigned long long>(nexact));
+    }
+  }
+  __syncthreads();
+  // ---- C + D: undecided tokens: halving tree of e * u over the 128 dims; page write (warp j takes tokens j, j + 4)
   for (int t = j; t < ntok; t += 4) {
-    const float2 a = __fadd2_rn(ps[t][lane], ps[t][lane + 64]), b = __fadd2_rn(ps[t][lane + 32], ps[t][lane + 96]);
-    const float2 herr = tree32x2(__fadd2_rn(a, b));
+    bool F = hsel[t] == 1;
+    if (hsel[t] == 2) {
+      const float2 a = __fadd2_rn(ps[t][lane], ps[t][lane + 64]), b = __fadd2_rn(ps[t][lane + 32], ps[t][lane + 96]);
+      const float2 herr = tree32x2(__fadd2_rn(a, b));
+      F = herr.y < herr.x;
+    }
     const long long slot = p.slot_ph ? p.slots[static_cast<long long>(t0 + t) * p.Hkv + h] : p.slots[t0 + t];
     if (slot < 0) continue;
-    const bool F = herr.y < herr.x;
     const int c = F ? 1 : 0;
     const int P = p.page;
     const long long page = slot / P;
@@ -695,6 +783,17 @@ static int dyn_keys_staged(const DynParams& p, const RowParams& rows, cudaStream
   return check_launch();
 }
 
+static int g_dyn_exact_only = 0;          // test switch: the bulk writer skips the tensor-core estimate (same bytes, slower)
+void dyn_writer_exact_only(int on) { g_dyn_exact_only = on ? 1 : 0; }
+int dyn_writer_stats(unsigned long long* out2, int reset) {
+  if (out2 != nullptr && cudaMemcpyFromSymbol(out2, g_dynstat, 2 * sizeof(unsigned long long)) != cudaSuccess) return -1;
+  if (reset) {
+    const unsigned long long z[2] = {0ull, 0ull};
+    if (cudaMemcpyToSymbol(g_dynstat, z, sizeof(z)) != cudaSuccess) return -1;
+  }
+  return 0;
+}
+
 // rows.T > 0: also write those value rows (in the same launch when the append path takes it, else in a second launch)
 template <int NB, bool SYM = false>
 static int dyn_keys_nb(const DynParams& p, const RowParams& rows, cudaStream_t st) {
@@ -714,7 +813,7 @@ static int dyn_keys_nb(const DynParams& p, const RowParams& rows, cudaStream_t s
   else {
     const long long groups = (p.T + 7) / 8;
     if (groups * p.Hkv > 0x7FFFFFFFll) return -3;
-    k_dyn_keys_bulk<NB, SYM><<<static_cast<unsigned>(groups * p.Hkv), 128, 0, st>>>(p, static_cast<int>(groups));
+    k_dyn_keys_bulk<NB, SYM><<<static_cast<unsigned>(groups * p.Hkv), 128, 0, st>>>(p, static_cast<int>(groups), g_dyn_exact_only);
   }
   return check_launch();
 }

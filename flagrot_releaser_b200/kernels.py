@@ -82,6 +82,8 @@ def lib():
     L.fr_xchg_free.argtypes = [P]
     L.fr_xchg_merge.argtypes = [P, ctypes.POINTER(P), I, I, I, P, I, P]
     L.fr_xchg_selftest.argtypes = [ctypes.POINTER(P), ctypes.POINTER(P), I, I, ctypes.POINTER(P), I, P]
+    L.fr_dyn_writer_stats.argtypes, L.fr_dyn_writer_stats.restype = [ctypes.POINTER(ctypes.c_ulonglong), I], I
+    L.fr_dyn_writer_exact_only.argtypes, L.fr_dyn_writer_exact_only.restype = [I], None
     for n in ("fr_v2_attn", "fr_v2_write", "fr_v2_occupancy", "fr_v2_chunk_bytes", "fr_cb_write", "fr_cb_attn",
               "fr_cb_occupancy", "fr_cb_chunk_bytes", "fr_cb_nsg", "fr_head_fwht", "fr_cb_write3",
               "fr_w3_static_write", "fr_cb_write_smem", "fr_attn_partial", "fr_device_status", "fr_cb_attn_noalloc", "fr_merge_partials",
@@ -90,6 +92,14 @@ def lib():
         getattr(L, n).restype = I
     _LIB = L
     return L
+
+
+def dyn_writer_stats(reset=False):
+    """(pairs written, pairs whose head choice took the exact sums) of the bulk dynamic key writer since the last reset."""
+    out = (ctypes.c_ulonglong * 2)()
+    if lib().fr_dyn_writer_stats(out, int(reset)) != 0:
+        raise RuntimeError("fr_dyn_writer_stats failed")
+    return int(out[0]), int(out[1])
 
 
 def _check(rc: int, what: str):

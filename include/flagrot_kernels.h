@@ -146,6 +146,14 @@ int fr_xchg_selftest(const float* const* parts, void* const* bufs, int R, int ro
 /* 0, or the source line of a bounded device-side wait that gave up (sticky; synchronises the device). */
 int fr_device_status(void);
 
+/* Bulk key writer of fr_cb_write / fr_cb_write3 (more than 4096 (token, kv head) pairs per call): the head choice
+ * base / H128 is first estimated on the tensor cores with a rigorous error bar and only the undecided pairs evaluate the
+ * criterion's fixed-order fp32 sums, so the pages are the same bytes either way.  out2 = {pairs written, pairs that took
+ * the exact sums} since the last reset, on the current device (synchronises it); reset != 0 clears the counters.
+ * fr_dyn_writer_exact_only(1) makes every pair take the exact sums (a test switch: process-wide host state). */
+int fr_dyn_writer_stats(unsigned long long* out2, int reset);
+void fr_dyn_writer_exact_only(int on);
+
 /* No counterpart in the reference.  fr_cb_attn (GQA 4, kinds 10 / 11) for a caller that cannot supply a workspace
  * because it cannot allocate device memory: a serving worker whose memory pool is frozen after start-up, or a plain C
  * host that only forwards the pointers it was handed.  The split partials and merge tickets live in a 16 MiB array

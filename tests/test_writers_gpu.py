@@ -333,3 +333,37 @@ def test_static_writer_head_dim_256(K, fmt, nb, page):
             O.write_pool(exp.reshape(npg, 2 * HKV, -1), slots.numpy(), codes, words, nb, page)
             got = pool.cpu().numpy()
             assert np.array_equal(got, exp), (T, km is not None, int((got != exp).sum()))
+
+
+@pytest.mark.parametrize("kind", ["konlya", "konlya2", "konly"])
+def test_bulk_key_writer_estimate_and_exact_sums_agree(K, kind):
+    """the bulk key writer decides most head choices from a tensor-core estimate with an error bar and the rest from the
+    exact fixed-order sums: both routes must give the same bytes, and the estimate must actually decide something"""
+    g = torch.Generator().manual_seed(77)
+    T = 3001
+    Cq, co = calib(HKV, g)
+    CT, cod = Cq.transpose(1, 2).contiguous().to(DEV), co.to(DEV)
+    npg = (T + P - 1) // P + 3
+    slots = torch.randperm(npg * P, generator=g)[:T].long().to(DEV)
+    rows = {"edge": edge_rows(T, HKV, g), "normal": torch.randn(T, 2 * HKV, 128, generator=g).bfloat16(),
+            "tiny": (torch.randn(T, 2 * HKV, 128, generator=g) * 1e-18).bfloat16(),
+            "huge": (torch.randn(T, 2 * HKV, 128, generator=g) * 1e18).bfloat16()}
+    try:
+        for name, kv in rows.items():
+            kv = kv.to(DEV)
+            pool0 = torch.randint(0, 256, (npg, HKV, K.cb_chunk_bytes(kind, P)), dtype=torch.uint8, generator=g).to(DEV)
+            a, b = pool0.clone(), pool0.clone()
+            K.lib().fr_dyn_writer_exact_only(0)
+            K.dyn_writer_stats(reset=True)
+            K.cb_write(kv, slots, CT, cod, kind, a, P)
+            pairs, exact = K.dyn_writer_stats()
+            assert pairs == T * HKV, (name, pairs)
+            if name in ("edge", "normal"):
+                assert exact < pairs // 2, (name, pairs, exact)
+            K.lib().fr_dyn_writer_exact_only(1)
+            K.dyn_writer_stats(reset=True)
+            K.cb_write(kv, slots, CT, cod, kind, b, P)
+            assert K.dyn_writer_stats() == (T * HKV, T * HKV)
+            assert torch.equal(a, b), (name, int((a != b).sum()))
+    finally:
+        K.lib().fr_dyn_writer_exact_only(0)
