@@ -475,7 +475,7 @@ template <int NB, bool SYM> struct DynQ {
 // counters of the bulk key writer: [0] (token, head) pairs written, [1] those whose head choice needed the exact sums
 __device__ unsigned long long g_dynstat[2];
 // relative half-width of the estimate's error bar, in units of sum |e_i| |C_ik| |e_k| (see the kernel's phase B)
-constexpr float DYN_DELTA = 0.005f;
+constexpr float DYN_DELTA = 0.003f;
 
 FR_DEVI void mma_tf32(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
   asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
@@ -486,9 +486,10 @@ FR_DEVI void mma_tf32(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32
 template <int NB, bool SYM>
 __global__ void __launch_bounds__(128) k_dyn_keys_bulk(const DynParams p, int groups, int exact_only) {
   constexpr int TG = 8;
-  // reconstruction errors of the head candidates (x: base, y: F); rows padded by 8 floats: the 16 (token, candidate)
-  // rows of an MMA operand then fall into different banks
-  __shared__ __align__(16) float2 es[TG][HD + 4];
+  // reconstruction errors of the head candidates (x: base, y: F); rows padded by 4 floats: the 8-byte operand loads of
+  // the MMA phase (a half warp = 2 tokens x 4 k) then fall into 16 different banks
+  __shared__ __align__(16) float2 es[TG][HD + 2];
+  __shared__ __align__(16) float ef[TG][HD];         // errors of the F candidate as the row mapping produces them
   __shared__ float est[4][2 * TG][2];                // per warp: partial (estimate, bound) of row 2 t + c
   __shared__ int hsel[TG];                           // head choice of token t: 0 base, 1 F, 2 undecided (exact sums needed)
   __shared__ __align__(16) float2 ps[TG][HD];        // first the errors of the local candidates (x: I, y: H32), then e * u
@@ -569,7 +570,8 @@ __global__ void __launch_bounds__(128) k_dyn_keys_bulk(const DynParams p, int gr
       }
       fwht_row_stages(d, lane, 128);
 #pragma unroll
-      for (int k = 0; k < 4; ++k) es[t][4 * lane + k].y = __fsub_rn(__fmul_rn(d[k], C128), x[k]);
+      for (int k = 0; k < 4; ++k) d[k] = __fsub_rn(__fmul_rn(d[k], C128), x[k]);
+      *reinterpret_cast<float4*>(&ef[t][4 * lane]) = make_float4(d[0], d[1], d[2], d[3]);
       *reinterpret_cast<uint32_t*>(&cs[t][1][4 * lane]) = cf;
       if ((lane & 7) == 0) ws[t][1][lane >> 3] = static_cast<uint16_t>(q.word());
     }
@@ -594,7 +596,7 @@ __global__ void __launch_bounds__(128) k_dyn_keys_bulk(const DynParams p, int gr
       const float2 own = ps[t][i];
       const float2 err = tree32x2(__fmul2_rn(own, U[t]));
       const bool ch = err.y < err.x;
-      es[t][i].x = ch ? own.y : own.x;
+      es[t][i] = make_float2(ch ? own.y : own.x, ef[t][i]);
       const unsigned c = lc[t][i];
       cs[t][0][i] = static_cast<uint8_t>(ch ? c >> 8 : c & 0xFFu);
       if (lane == 0) ws[t][0][j] = static_cast<uint16_t>(ch ? (lw[t][1][j] | 0x8000u) : lw[t][0][j]);
@@ -606,37 +608,49 @@ __global__ void __launch_bounds__(128) k_dyn_keys_bulk(const DynParams p, int gr
   //      S_c = sum_ik |e_i| |C_ik| |e_k| in real arithmetic, the fixed-order value satisfies |herr_c - T_c| <= 2^-18 S_c (43
   //      roundings on the path of a term), and E_c = sum_i e_i (C~ e~)_i with TF32 operands (each within 2^-10 of its
   //      value) and fp32 accumulation satisfies |E_c - T_c| <= 0.0020 S_c; B_c = sum_i |e_i| (|C~| |e~|)_i >= 0.9979 S_c.
-  //      So |herr_c - E_c| < DYN_DELTA B_c with a margin of 2.5, and the choice is certain whenever the two error bars do
+  //      So |herr_c - E_c| < DYN_DELTA B_c with a margin of 1.5, and the choice is certain whenever the two error bars do
   //      not overlap.  Only the undecided tokens (non-finite values included: every comparison is then false) take the
   //      exact sums u_i = ((U0 + U1) + U2) + U3, U_b = seq_{k in block b} C[i][k] e_k.
   {
     const int g = lane >> 2, q = lane & 3;
-    // MMA rows: row g = (token g >> 1, candidate g & 1), row g + 8 = (token (g >> 1) + 4, same candidate): row = 2 t + c
-    const float* ea = reinterpret_cast<const float*>(&es[g >> 1][0]) + (g & 1);
-    const float* eb = reinterpret_cast<const float*>(&es[(g >> 1) + 4][0]) + (g & 1);
+    // MMA rows: row g = (token g >> 1, candidate g & 1), row g + 8 = (token (g >> 1) + 4, same candidate): row = 2 t + c.
+    // The B operand is read as B[k][n] = CT[i][k] = C[k][i], i.e. the transpose of C: e^T C^T e = e^T C e and the bound
+    // is the same sum, while a thread's values for two MMA steps are then 16 contiguous bytes (k = 16 d + 4 q .. + 3:
+    // the k slots (q, q + 4) of step 0 stand for k, k + 1, those of step 1 for k + 2, k + 3).
+    const int t_lo = g >> 1, c = g & 1;
     float acc[4][4], bnd[4][4];
 #pragma unroll
     for (int n = 0; n < 4; ++n)
 #pragma unroll
       for (int r = 0; r < 4; ++r) { acc[n][r] = 0.f; bnd[n][r] = 0.f; }
     if (!exact_only) {
-#pragma unroll 4
-      for (int k0 = 0; k0 < HD; k0 += 8) {
-        uint32_t a[4], aa[4];
-        a[0] = __float_as_uint(ea[2 * (k0 + q)]); a[1] = __float_as_uint(eb[2 * (k0 + q)]);
-        a[2] = __float_as_uint(ea[2 * (k0 + q + 4)]); a[3] = __float_as_uint(eb[2 * (k0 + q + 4)]);
+#pragma unroll 2
+      for (int k0 = 0; k0 < HD; k0 += 16) {
+        uint32_t a[2][4], aa[2][4];
 #pragma unroll
-        for (int r = 0; r < 4; ++r) aa[r] = a[r] & 0x7FFFFFFFu;
+        for (int s2 = 0; s2 < 4; ++s2) {
+          const float2 lo = es[t_lo][k0 + 4 * q + s2], hi = es[t_lo + 4][k0 + 4 * q + s2];
+          a[s2 >> 1][2 * (s2 & 1)] = __float_as_uint(c ? lo.y : lo.x);
+          a[s2 >> 1][2 * (s2 & 1) + 1] = __float_as_uint(c ? hi.y : hi.x);
+        }
 #pragma unroll
-        for (int n = 0; n < 4; ++n) {     // B[k][n] = C[i = 32 j + 8 n + g][k0 + q (+ 4)]
-          const float* cp = CT + (k0 + q) * HD + 32 * j + 8 * n + g;
-          const uint32_t b0 = __float_as_uint(__ldg(cp)), b1 = __float_as_uint(__ldg(cp + 4 * HD));
-          mma_tf32(acc[n], a, b0, b1);
-          mma_tf32(bnd[n], aa, b0 & 0x7FFFFFFFu, b1 & 0x7FFFFFFFu);
+        for (int st = 0; st < 2; ++st)
+#pragma unroll
+          for (int r = 0; r < 4; ++r) aa[st][r] = a[st][r] & 0x7FFFFFFFu;
+#pragma unroll
+        for (int n = 0; n < 4; ++n) {
+          const float4 v = __ldg(reinterpret_cast<const float4*>(CT + (32 * j + 8 * n + g) * HD + k0 + 4 * q));
+          const uint32_t b[4] = {__float_as_uint(v.x), __float_as_uint(v.y), __float_as_uint(v.z), __float_as_uint(v.w)};
+          mma_tf32(acc[n], a[0], b[0], b[1]);
+          mma_tf32(bnd[n], aa[0], b[0] & 0x7FFFFFFFu, b[1] & 0x7FFFFFFFu);
+          mma_tf32(acc[n], a[1], b[2], b[3]);
+          mma_tf32(bnd[n], aa[1], b[2] & 0x7FFFFFFFu, b[3] & 0x7FFFFFFFu);
         }
       }
     }
     float E0 = 0.f, B0 = 0.f, E1 = 0.f, B1 = 0.f;    // rows g and g + 8 over this thread's 8 columns
+    const float* ea = reinterpret_cast<const float*>(&es[t_lo][0]) + c;
+    const float* eb = reinterpret_cast<const float*>(&es[t_lo + 4][0]) + c;
 #pragma unroll
     for (int n = 0; n < 4; ++n) {
       const int i0 = 32 * j + 8 * n + 2 * q;
