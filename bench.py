@@ -14,7 +14,7 @@ Workloads (the configurations of the baseline; all inputs seeded synthetic, cach
          are dealt over the ranks).
   cfg5b  one sequence of 131072 tokens, INT4 konlya: the KV sequence is split over the ranks, every rank emits (o, m, l)
          rows (fr_attn_partial), an NCCL all-gather of 130 floats per (row, head) and fr_merge_partials finish the step.
-  writers  the cache writers against the reference's own sm_100a-capable kernels (oracle/_ref), T = 64 and T = 65536.
+  writers  the cache writers against the reference's own sm_100a-capable kernels (oracle/_ref), T = 64 and T = 65536 (scattered and consecutive slots).
 
 A step = one pass of the hot path over one batch: the writer appends one token per sequence and the decode attention reads
 every sequence's cache (prefill: q staging + attention + item merge).  `value` has every input resident in HBM (the
@@ -633,7 +633,8 @@ class PrefillWorkload:
 # ---------------------------------------------------------------------------------------------- writers vs the reference's kernels
 def writers_race(dev):
     """our writers against the reference's own kernels built for sm_100a (oracle/_ref): a bench leg only.  Per entry and
-    T: microseconds per call (CUDA events, 10 calls after 3 warm-up calls), identical arguments and pools."""
+    T: microseconds per call (CUDA events, 10 calls after 3 warm-up calls), identical arguments and pools, both libraries
+    called through their C entries directly (the same host cost per call on both sides)."""
     from flagrot_releaser_b200 import kernels as K
     from flagrot_releaser_b200 import kivi as KV
     res = {}
@@ -648,16 +649,23 @@ def writers_race(dev):
     mask = (torch.rand(2 * Hkv, 4, generator=g) < 0.5).to(torch.uint8).to(dev)
     hfull = (torch.rand(2 * Hkv, generator=g) < 0.4).to(torch.uint8).to(dev)
     st = lambda: torch.cuda.current_stream().cuda_stream  # noqa: E731
-    for T in (64, 65536):
+    # slots: a random permutation (every token on its own, the worst case for the value codes, whose words are shared by
+    # 8 tokens) and, for the bulk size, the consecutive slots a prefill actually writes (whole pages of one sequence)
+    for T, contiguous in ((64, False), (65536, False), (65536, True)):
         kv = torch.randn(T, 2 * Hkv, 128, generator=g)
         kv[:, :Hkv, :6] *= 10
         kv = kv.bfloat16().to(dev)
         npg = T // P + 64
-        slots = torch.randperm(npg * P, generator=g)[:T].to(torch.int64).to(dev)
+        slots = (torch.arange(T) + 3 * P if contiguous else torch.randperm(npg * P, generator=g)[:T]).to(torch.int64).to(dev)
         pool = torch.zeros(npg, Hkv, 144 * P, dtype=torch.uint8, device=dev)
         row = {"ours": {}, "reference": {}}
-        row["ours"]["fr_cb_write3 konlya"] = timed(lambda i: K.cb_write3(kv, slots, CT, co, None, None, "konlya", pool, P, split=False), 10, 3) * 1e3
-        row["ours"]["fr_w3_static_write int4a"] = timed(lambda i: K.w3_static_write(kv, slots, mask, hfull, pool, P, fmt="int4a"), 10, 3) * 1e3
+        L, sg0 = K.lib(), K.sign_words()
+        row["ours"]["fr_cb_write3 konlya"] = timed(lambda i: L.fr_cb_write3(
+            kv.data_ptr(), kv.stride(0), slots.data_ptr(), 0, T, Hkv, P, CT.data_ptr(), co.data_ptr(), None, None, sg0, 10,
+            pool.data_ptr(), 1, 1, st(), None), 10, 3) * 1e3
+        row["ours"]["fr_w3_static_write int4a"] = timed(lambda i: L.fr_w3_static_write(
+            kv.data_ptr(), kv.stride(0), slots.data_ptr(), T, Hkv, P, mask.data_ptr(), hfull.data_ptr(), 1, pool.data_ptr(), 0,
+            st(), None), 10, 3) * 1e3
         rf = reference_front()
         if w3.exists():
             R = ctypes.CDLL(str(w3))
@@ -686,8 +694,12 @@ def writers_race(dev):
         gp = torch.arange(ng * GRP).view(ng, GRP) % T
         sidx = gp.contiguous().to(dev)
         dslot = slots[gp.reshape(-1)].view(ng, GRP).contiguous()
-        row["ours"]["kv_v_write"] = timed(lambda i: KV.v_write(kv, slots, co, None, kpool, Hkv, D), 10, 3) * 1e3
-        row["ours"]["kv_k_encode"] = timed(lambda i: KV.k_encode(kv, sidx, dslot, cqs, lz, SCALE, kpool, Hkv, D), 10, 3) * 1e3
+        LK = KV.lib()
+        row["ours"]["kv_v_write"] = timed(lambda i: LK.kv_v_write(kv.data_ptr(), kv.stride(0), T, Hkv, D, slots.data_ptr(),
+                                                                  co.data_ptr(), None, kpool.data_ptr(), 0, None, 0, st()), 10, 3) * 1e3
+        row["ours"]["kv_k_encode"] = timed(lambda i: LK.kv_k_encode(kv.data_ptr(), kv.stride(0), None, 0, sidx.data_ptr(),
+                                                                    dslot.data_ptr(), ng, Hkv, D, cqs.data_ptr(), lz.data_ptr(), 64,
+                                                                    SCALE, kpool.data_ptr(), 0, None, 0, st()), 10, 3) * 1e3
         if kr.exists():
             R = ctypes.CDLL(str(kr))
             R.kv_v_write.argtypes = [PP, LL, I, I, I, PP, PP, PP, PP, I, PP, I, PP]
@@ -697,7 +709,7 @@ def writers_race(dev):
             row["reference"]["kv_k_encode"] = timed(lambda i: R.kv_k_encode(kv.data_ptr(), kv.stride(0), None, 0, sidx.data_ptr(),
                                                                            dslot.data_ptr(), ng, Hkv, D, cqs.data_ptr(), lz.data_ptr(), 64,
                                                                            SCALE, kpool.data_ptr(), 0, None, 0, st()), 10, 3) * 1e3
-        res[f"T={T}"] = row
+        res[f"T={T}" + (" consecutive slots" if contiguous else "")] = row
     return res
 
 
