@@ -253,6 +253,229 @@ __global__ void __launch_bounds__(128) k_rows8(const RowParams p) {
   }
 }
 
+// rintf(__fdiv_rn(a, b)) for a whole vector with one multiplication per element where that is provably the same:
+// y = __frcp_rn(b), 1e-30 < b < 1e30, |a / b| < 2^20.  q0 = RN(a y) and RN(a / b) both lie within 3 * 2^-24 |a / b| of a / b,
+// so they round to the same integer unless q0 is within 2.4e-7 |q0| of a half-integer (`near` collects that; the caller
+// then redoes the vector with divisions).  The rounding itself is an addition of 1.5 * 2^23 (round to nearest even).
+constexpr float RMAGIC = 12582912.f;
+FR_DEVI float rint_mul(float a, float y, bool& near) {
+  const float q0 = __fmul_rn(a, y);
+  const float r = __fsub_rn(__fadd_rn(q0, RMAGIC), RMAGIC);
+  near |= !(fabsf(__fsub_rn(fabsf(__fsub_rn(q0, r)), 0.5f)) > fmaf(fabsf(q0), 2.4e-7f, 1e-30f));
+  return r;
+}
+
+// "vector" mapping of the bulk writer: a lane holds one whole 32-vector of a row in registers, so the H32 butterflies,
+// the range and the quantizer need no shuffles (lane = 4 * token + vector of a group of 8 tokens; the whole-head H128
+// takes its two outer stages from the neighbouring lanes).  Same operations in the same order as row_codes.
+// Out: the 32 stored codes as bytes (cw[r] = codes 4 r .. 4 r + 3) and the scale word of the vector.
+template <int NB, bool SYM>
+FR_DEVI void vec_codes(const RowParams& p, int t, bool live, int hr, int b, unsigned (&cw)[8], unsigned& word) {
+  float v[32];
+  if (live) {
+    const uint4* src = reinterpret_cast<const uint4*>(p.kv + t * p.kv_ts + hr * HD + 32 * b);
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      const uint4 w = src[r];
+      v[8 * r + 0] = bf16_lo(w.x); v[8 * r + 1] = bf16_hi(w.x); v[8 * r + 2] = bf16_lo(w.y); v[8 * r + 3] = bf16_hi(w.y);
+      v[8 * r + 4] = bf16_lo(w.z); v[8 * r + 5] = bf16_hi(w.z); v[8 * r + 6] = bf16_lo(w.w); v[8 * r + 7] = bf16_hi(w.w);
+    }
+  } else {
+#pragma unroll
+    for (int r = 0; r < 32; ++r) v[r] = 0.f;
+  }
+  const bool hf = p.hfull != nullptr && p.hfull[hr];                  // uniform over the warp
+  const bool rot = p.mask != nullptr && p.mask[hr * 4 + b];           // per lane
+  const bool ctr = p.kmu != nullptr && hr < p.Hkv;
+  // pass 0: whole-head H128 x / 16 rounded to bf16 once (if hf); pass 1: key centring, then H32 of a flagged vector.
+  // One copy of the 32-point butterflies serves both (the loop is kept rolled: the code stays small).
+#pragma unroll 1
+  for (int pass = 0; pass < 2; ++pass) {
+    if (pass == 1 && ctr) {
+      const float4* mu = reinterpret_cast<const float4*>(p.kmu + hr * HD + 32 * b);
+#pragma unroll
+      for (int r = 0; r < 8; ++r) {
+        const float4 m = __ldg(mu + r);
+        v[4 * r] = __fsub_rn(v[4 * r], m.x); v[4 * r + 1] = __fsub_rn(v[4 * r + 1], m.y);
+        v[4 * r + 2] = __fsub_rn(v[4 * r + 2], m.z); v[4 * r + 3] = __fsub_rn(v[4 * r + 3], m.w);
+      }
+    }
+    const bool act = pass == 0 ? hf : rot;
+    if (!__any_sync(FULLMASK, act)) continue;
+    float w[32];
+#pragma unroll
+    for (int r = 0; r < 32; ++r) w[r] = v[r];
+#pragma unroll
+    for (int h = 1; h < 32; h <<= 1)            // unnormalised butterflies h = 1 .. 16 inside the vector
+#pragma unroll
+      for (int r = 0; r < 32; ++r)
+        if (!(r & h)) {
+          const float x = w[r], y = w[r + h];
+          w[r] = __fadd_rn(x, y);
+          w[r + h] = __fsub_rn(x, y);
+        }
+    if (pass == 0) {                            // (uniform) h = 32, 64: the other vectors of the token sit in the lanes b ^ 1, b ^ 2
+#pragma unroll
+      for (int m = 1; m < 4; m <<= 1)
+#pragma unroll
+        for (int r = 0; r < 32; ++r) {
+          const float o = __shfl_xor_sync(FULLMASK, w[r], m);
+          w[r] = (b & m) ? __fsub_rn(o, w[r]) : __fadd_rn(w[r], o);
+        }
+#pragma unroll
+      for (int r = 0; r < 32; r += 2) {
+        const __nv_bfloat162 q = __floats2bfloat162_rn(__fmul_rn(w[r], 0.0625f), __fmul_rn(w[r + 1], 0.0625f));
+        const uint32_t u = *reinterpret_cast<const uint32_t*>(&q);
+        v[r] = bf16_lo(u);
+        v[r + 1] = bf16_hi(u);
+      }
+    } else {
+#pragma unroll
+      for (int r = 0; r < 32; ++r) v[r] = act ? __fmul_rn(w[r], C32) : v[r];
+    }
+  }
+  float mn = v[0], mx = v[0];
+#pragma unroll
+  for (int r = 1; r < 32; ++r) { mn = fminf(mn, v[r]); mx = fmaxf(mx, v[r]); }
+#pragma unroll
+  for (int r = 0; r < 8; ++r) cw[r] = 0u;
+  const float amax = fmaxf(-mn, mx);
+  if (SYM) {                                   // quant_store_sym
+    const __half sh = __float2half_rn(__fmul_rn(amax, 1.0f / 7.0f));
+    const float sf = __half2float(sh);
+    word = __half_as_ushort(sh);
+    if (sf == 0.f) return;                     // all codes 0
+    bool slow = !(sf > 1e-30f && sf < 1e30f && amax < __fmul_rn(sf, 1048576.f));
+    if (!slow) {
+      const float y = __frcp_rn(sf);
+#pragma unroll
+      for (int r = 0; r < 32; ++r) {
+        const float q = fminf(fmaxf(rint_mul(v[r], y, slow), -7.f), 7.f);
+        // sign-magnitude: 8 | |q| for q < 0; |q| <= 7 sits in the low bits of |q| + 1.5 * 2^23
+        const unsigned mag = __float_as_uint(__fadd_rn(fabsf(q), RMAGIC)) & 7u;
+        cw[r >> 2] |= (mag | (q < 0.f ? 8u : 0u)) << (8 * (r & 3));
+      }
+    }
+    if (slow) {                                // (rare) some quotient sits on a rounding boundary: every element by division
+#pragma unroll
+      for (int r = 0; r < 8; ++r) cw[r] = 0u;
+#pragma unroll
+      for (int r = 0; r < 32; ++r) {
+        unsigned c, w2;
+        quant_store_sym(v[r], amax, c, w2);
+        cw[r >> 2] |= c << (8 * (r & 3));
+      }
+    }
+    return;
+  }
+  float sc, z;                                 // quant_store: the range widened to include 0
+  asym_params<NB>(fminf(mn, 0.f), fmaxf(mx, 0.f), sc, z);
+  word = scale_word<NB>(sc, static_cast<unsigned>(z));
+  constexpr float LV = static_cast<float>((1 << NB) - 1);
+  bool slow = !(sc > 1e-30f && sc < 1e30f && amax < __fmul_rn(sc, 1048576.f));
+  if (!slow) {
+    const float y = __frcp_rn(sc);
+#pragma unroll
+    for (int r = 0; r < 32; ++r) {
+      const float q = fminf(fmaxf(__fadd_rn(rint_mul(v[r], y, slow), z), 0.f), LV);
+      cw[r >> 2] |= (__float_as_uint(__fadd_rn(q, RMAGIC)) & 0xFu) << (8 * (r & 3));
+    }
+  }
+  if (slow) {
+#pragma unroll
+    for (int r = 0; r < 8; ++r) cw[r] = 0u;
+#pragma unroll
+    for (int r = 0; r < 32; ++r) cw[r >> 2] |= static_cast<unsigned>(asym_code<NB>(v[r], sc, z)) << (8 * (r & 3));
+  }
+}
+
+// k_rows8 for rows that are transformed before they are quantised (static formats with block flags or whole-head flags):
+// warp = (8 consecutive tokens, row); the codes are computed in the vector mapping (vec_codes), handed over through shared
+// memory and stored in the row mapping (lane l: d = 4 l .. 4 l + 3 of one token) exactly as k_rows8 stores them.  A V^T code word holds ONE
+// dim of the 8 tokens of an aligned 8-slot run of a page (INT2: two dims), so when the group's slots are such a run the warp
+// assembles whole words in registers and stores them plainly (4 words per lane and 16 bytes of scale words per 32-group)
+// instead of flipping 128 four-bit fields per token with atomics.  Any other group (ragged end, holes, scattered slots) and
+// every K row are stored token by token.
+template <int NB, bool SYM = false>
+__global__ void __launch_bounds__(128) k_rows8v(const RowParams p) {
+  __shared__ __align__(16) uint8_t cs8[4][8][HD];     // per warp: stored codes [token][dim]
+  __shared__ uint16_t ws8[4][8][4];                   // and scale words [token][vector]
+  const int lane = threadIdx.x & 31, wp = threadIdx.x >> 5;
+  const long long item = static_cast<long long>(blockIdx.x) * 4 + wp;
+  const int groups = (p.T + 7) >> 3;
+  if (item >= static_cast<long long>(groups) * p.nrow) return;
+  const int g = static_cast<int>(item / p.nrow), hr = p.row0 + static_cast<int>(item % p.nrow);
+  const bool isv = hr >= p.Hkv;
+  const int head = isv ? hr - p.Hkv : hr;
+  const int t0 = 8 * g, nt = min(8, p.T - t0);
+  long long sl = -1;
+  if (lane < nt) sl = p.slot_ph ? p.slots[static_cast<long long>(t0 + lane) * p.Hkv + head] : p.slots[t0 + lane];
+  const long long s0 = __shfl_sync(FULLMASK, sl, 0);
+  const bool run = nt == 8 && s0 >= 0 && (s0 & 7) == 0 && __all_sync(FULLMASK, lane >= 8 || sl == s0 + lane);
+  {
+    const int tl = lane >> 2, b = lane & 3;
+    unsigned cw[8], word;
+    vec_codes<NB, SYM>(p, t0 + tl, tl < nt, hr, b, cw, word);
+    uint4* dst = reinterpret_cast<uint4*>(&cs8[wp][tl][32 * b]);
+    dst[0] = make_uint4(cw[0], cw[1], cw[2], cw[3]);
+    dst[1] = make_uint4(cw[4], cw[5], cw[6], cw[7]);
+    ws8[wp][tl][b] = static_cast<uint16_t>(word);
+  }
+  __syncwarp();
+  if (!isv || !run) {
+    const int P = p.page;
+    for (int i = 0; i < nt; ++i) {
+      const long long slot = __shfl_sync(FULLMASK, sl, i);
+      if (slot < 0) continue;
+      uint8_t* chunk = p.pool + ((slot / P) * p.Hkv + head) * static_cast<long long>(Lay<NB>::chunk(P));
+      const int pos = static_cast<int>(slot % P);
+      const unsigned c4 = *reinterpret_cast<const uint32_t*>(&cs8[wp][i][4 * lane]);
+      const unsigned code[4] = {c4 & 0xFFu, (c4 >> 8) & 0xFFu, (c4 >> 16) & 0xFFu, c4 >> 24};
+      const unsigned word = ws8[wp][i][lane >> 3];
+      if (!isv) store_k_row<NB, SYM>(chunk, P, pos, lane, code, word);
+      else store_v_row<NB, SYM>(chunk, P, pos, lane, code, word, p.shared15 != 0);
+    }
+    return;
+  }
+  const int P = p.page;
+  const int pos0 = static_cast<int>(s0 % P), c8 = pos0 >> 3;
+  uint8_t* chunk = p.pool + ((s0 / P) * p.Hkv + head) * static_cast<long long>(Lay<NB>::chunk(P));
+  unsigned acc[4] = {0u, 0u, 0u, 0u};       // per dim of the lane: the 8 tokens' codes (byte i >> 1, field i & 1)
+  unsigned sw[4] = {0u, 0u, 0u, 0u};        // the 8 scale words of the lane's 32-group in page order (tokens 0 2 4 6 1 3 5 7)
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const unsigned c4 = *reinterpret_cast<const uint32_t*>(&cs8[wp][i][4 * lane]);
+    const unsigned code[4] = {c4 & 0xFFu, (c4 >> 8) & 0xFFu, (c4 >> 16) & 0xFFu, c4 >> 24};
+    const unsigned word = ws8[wp][i][lane >> 3];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) acc[k] |= SYM ? sym_bits(code[k], (i & 1) != 0, i >> 1) : code[k] << (8 * (i >> 1) + NB * (i & 1));
+    const int idx = (i & 1) ? 4 + (i >> 1) : (i >> 1);
+    sw[idx >> 1] |= (word & 0xFFFFu) << (16 * (idx & 1));
+  }
+  const int w = (lane & 15) >> 2, r8 = (lane & 3) >> 1, m = lane >> 4;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const int gid = 4 * (lane & 1) + k;
+    const int e = (w * 8 + gid) * (P >> 3) + c8;
+    if (NB == 4) {
+      *reinterpret_cast<uint32_t*>(chunk + Lay<4>::v_off(P) + 16 * e + 4 * (2 * m + r8)) = acc[k];
+    } else {                                  // dims d (r8 = 0, this lane) and d + 8 (lane + 2) share the word
+      const unsigned hi = __shfl_down_sync(FULLMASK, acc[k], 2);
+      if (r8 == 0) *reinterpret_cast<uint32_t*>(chunk + Lay<2>::v_off(P) + 8 * e + 4 * m) = acc[k] | (hi << 4);
+    }
+  }
+  if ((lane & 7) == 0) {
+    const int j = lane >> 3;
+    const int off = Lay<NB>::vs_off(P) + 2 * (j * P + 8 * c8);
+    if (p.shared15 && j == 0) {               // bit 15 of these words belongs to the key writer
+#pragma unroll
+      for (int x = 0; x < 8; ++x) put_word_low15(chunk, off + 2 * x, (sw[x >> 1] >> (16 * (x & 1))) & 0xFFFFu);
+    } else {
+      *reinterpret_cast<uint4*>(chunk + off) = make_uint4(sw[0], sw[1], sw[2], sw[3]);
+    }
+  }
+}
+
 // ------------------------------------------------------------------------------------------------ dynamic key writer
 struct DynParams {
   const __nv_bfloat16* kv; long long kv_ts;
@@ -751,7 +974,10 @@ template <int NB, bool SYM = false>
 static void rows_kernel_launch(const RowParams& p, cudaStream_t st) {
   if (p.T >= 256) {                            // bulk write: groups of 8 tokens, whole V^T words where the slots allow
     const long long items = static_cast<long long>((p.T + 7) / 8) * p.nrow;
-    k_rows8<NB, SYM><<<static_cast<unsigned>((items + 3) / 4), 128, 0, st>>>(p);
+    // rows with transforms in front of the quantizer: a lane per 32-vector (322 against 385 us for 65 536 tokens x 16 rows on
+    // consecutive slots); plain rows (the values of the key-only kinds): a warp per row is faster (233 against 308 us)
+    if (p.mask != nullptr || p.hfull != nullptr) k_rows8v<NB, SYM><<<static_cast<unsigned>((items + 3) / 4), 128, 0, st>>>(p);
+    else k_rows8<NB, SYM><<<static_cast<unsigned>((items + 3) / 4), 128, 0, st>>>(p);
   } else {
     const long long items = static_cast<long long>(p.T) * p.nrow;
     k_rows<NB, SYM><<<static_cast<unsigned>((items + 3) / 4), 128, 0, st>>>(p);
