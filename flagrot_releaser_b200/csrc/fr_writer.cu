@@ -6,15 +6,20 @@
 // and k_head_fwht256 (integrations/vllm_flagrot/csrc/flagrot_capi.cu:167-245), k_cb_write (kernels/csrc/attn_codebook.cu:46-361) and the
 // fused v3 writers (kernels/csrc/attn_cb_write3.cuh) for the kinds konlya / konlya2 and the formats int4a / int2a.
 //
-// Structure: two kernels.
+// Structure: two kernels for appends and small writes, three more for bulk writes.
 //   k_rows      one warp per (token, K or V row): load 4 bf16 per lane, optional whole-head H128 (+ bf16 rounding),
 //               key centring, per-block H32, group quantizer, scatter into the page.  Used for the static formats
 //               (all rows) and for the value rows of the dynamic kinds.
 //   k_dyn_keys  one CTA of 128 threads per (kv head, TG tokens).  Thread i owns dimension i, so the 32 x 32 and
 //               128 x 128 weighted-error products read C_q^T rows fully coalesced (L1 / L2 resident, 64 KB per head; for a
 //               decode append of a few tokens the head's C_q^T is first staged in shared memory by a bulk copy, which
-//               takes the L2 latency out of the 128-step sums) and accumulate in the reference's sequential fp32 order; the whole-head candidate is evaluated by one warp
-//               per token in the row mapping.  No tensor cores: the criterion is defined by its fp32 operation order.
+//               takes the L2 latency out of the 128-step sums) and accumulate in the reference's sequential fp32 order;
+//               the whole-head candidate is evaluated by one warp per token in the row mapping.  No tensor cores here:
+//               the criterion is defined by its fp32 operation order.
+//   k_rows8 / k_rows8v   bulk rows: a warp per (8 consecutive tokens, row), whole V^T words where the slots allow;
+//               k_rows8v computes transformed rows with a lane per 32-vector.
+//   k_dyn_keys_bulk      bulk keys: 8 tokens per CTA; the head choice is first estimated on the tensor cores with a
+//               rigorous error bar, and only the undecided tokens take the fixed-order fp32 sums (same bytes).
 // V^T code words are shared by 8 tokens; a token only ever flips the bits of its own field (fr::put_field), so tokens
 // of one word may be written by different warps, kernels or streams in any order.
 #include "fr_common.cuh"
